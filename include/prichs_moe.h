@@ -1,0 +1,194 @@
+/*
+ * prichs_moe.h -- C ABI of the B200 (sm_100a) MoE-layer forward library, libprichs_moe.so.
+ *
+ * The library replaces ONE path of DanyaStark553/PRICHS: the forward pass of `MoELayer`
+ * (crates/prichs-model/src/moe.rs:58-246) and the kernels and engine calls the reference's GPU path uses
+ * for it (crates/prichs-cuda/src/kernels.cu:444-457,888-924; crates/prichs-cuda/src/engine.rs:1917-2239).
+ * The convention follows the reference's own FFI (crates/prichs-cuda/src/engine.rs:89-272): plain
+ * pointers, size_t/int dimensions, the CUDA stream passed as `void*`. Unlike the reference's `launch_*`
+ * wrappers, which return void and drop every error, each function here returns an int status.
+ *
+ * Data layout. Every matrix is row-major. Weights are handed over in the reference's "x . W" layout:
+ * router [d,E], gate_proj and up_proj [d,f], down_proj [f,d] (moe.rs:16-18,73-74). Activations are [T,d].
+ *
+ * There is no CPU fallback: without a CUDA device every call that touches the device returns
+ * PRICHS_ERR_CUDA.
+ */
+#ifndef PRICHS_MOE_H_
+#define PRICHS_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PRICHS_API __attribute__((visibility("default")))
+#else
+#define PRICHS_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------------------- */
+#define PRICHS_OK 0
+#define PRICHS_ERR_BAD_SHAPE (-1) /* the reference bails on shape mismatch in matmul_2d, ops.rs:11-18    */
+#define PRICHS_ERR_CAPACITY (-2)  /* more tokens / rows than the handle was created for                   */
+#define PRICHS_ERR_CUDA (-3)      /* a CUDA runtime or driver call failed (or no device)                  */
+#define PRICHS_ERR_COMM (-4)      /* expert-parallel exchange failed or is not initialised                */
+#define PRICHS_ERR_TIMEOUT (-5)   /* a bounded device-side wait gave up (status word set by a kernel)     */
+#define PRICHS_ERR_BAD_ARG (-6)   /* null pointer, unknown dtype, weights not uploaded, ...               */
+
+/* element types at the boundary (activations x / residual / y) */
+#define PRICHS_DTYPE_F32 0
+#define PRICHS_DTYPE_BF16 1
+
+/* compute modes */
+#define PRICHS_MODE_BF16 0 /* bf16 operands, fp32 accumulate on the tensor cores                        */
+#define PRICHS_MODE_F32 1  /* fp32 fidelity: every operand split into bf16 hi+lo parts, three products   */
+
+typedef struct prichs_moe prichs_moe_t;
+
+/* Mirrors the arguments of MoELayer::new(hidden_dim, intermediate_dim, num_experts, top_k)
+ * (moe.rs:67-72) plus what a device handle needs to size its buffers once. */
+typedef struct prichs_moe_config {
+    int hidden_dim;       /* d; multiple of 256                                                        */
+    int intermediate_dim; /* f; multiple of 128                                                        */
+    int num_experts;      /* E routed experts, 1..8 (one shared expert is always present, moe.rs:76)   */
+    int top_k;            /* 1 or 2, <= num_experts                                                    */
+    int max_tokens;       /* largest T a forward call may pass                                         */
+    int mode;             /* PRICHS_MODE_*                                                             */
+    int device;           /* CUDA device ordinal, or -1 for the current device                         */
+    int ep_world;         /* expert-parallel ranks (1 = all experts local); must divide num_experts    */
+    int ep_rank;          /* this rank, 0..ep_world-1; owns experts [rank*E/world, (rank+1)*E/world)   */
+    int ep_max_recv_rows; /* capacity of the receive side in rows (0 = worst case ep_world*max_tokens*top_k) */
+} prichs_moe_config_t;
+
+/* ---- lifetime ------------------------------------------------------------------------------------ */
+
+/* Replaces MoELayer::new (moe.rs:67-90) and the engine's buffer set-up (engine.rs:363-649): allocates the
+ * weights, the workspace for max_tokens and the TMA descriptors. Weights start undefined, the router bias
+ * at zero (moe.rs:75). */
+PRICHS_API int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle);
+
+/* Replaces Drop for GpuModelEngine (engine.rs:2792-2854). */
+PRICHS_API int prichs_moe_destroy(prichs_moe_t* h);
+
+/* Replaces GpuModelEngine::upload_weights (engine.rs:668-689) for the layer's tensors. `host_ptrs` holds
+ * 1 + 3*(1+E) fp32 host arrays in the reference's parameter order (model.rs:353-361): router [d,E]; shared
+ * gate [d,f], up [d,f], down [f,d]; then for each routed expert gate, up, down. In expert-parallel mode
+ * the pointers of experts this rank does not own may be null. The arrays are repacked once on the device
+ * (transposed to K-major, gate and up interleaved in 128-column blocks, rounded to bf16 -- or split into
+ * bf16 hi/lo parts in PRICHS_MODE_F32). */
+PRICHS_API int prichs_moe_upload_weights(prichs_moe_t* h, const float* const* host_ptrs, int n_ptrs);
+
+/* The public field MoELayer::router_bias (moe.rs:60): read and write, host side, length E. */
+PRICHS_API int prichs_moe_set_bias(prichs_moe_t* h, const float* host_bias, int n);
+PRICHS_API int prichs_moe_get_bias(prichs_moe_t* h, float* host_bias, int n);
+
+/* ---- forward ------------------------------------------------------------------------------------- */
+
+/* Replaces MoELayer::forward / forward_with_memory (moe.rs:214-225) and the engine call sequence
+ * gpu_moe_forward_shared + forward_gemm(router) + host top-k + gpu_moe_forward_expert (per expert) +
+ * gpu_moe_finalize_forward (engine.rs:1917-2239, model.rs:1327-1408) with device-resident activations.
+ *   x_dev        [T,d] device pointer, element type x_dtype
+ *   resid_dev    optional [T,d] device pointer (same element type as x): when non-null the caller's
+ *                residual add of block.rs:67 is fused, y = resid + moe(x); when null y = moe(x)
+ *   concept_bias optional HOST array (the reference's Option<&[f32]>, moe.rs:96,128-132): added to the
+ *                selection logit of expert e for e < n_concept; copied by value, no device pointer needed
+ *   y_dev        [T,d] device pointer, element type y_dtype
+ * All work is enqueued on `stream` (a cudaStream_t; null = legacy default stream, as in the reference).
+ * No allocation and no host synchronisation happen inside. One handle is one stream-ordered context: calls
+ * on the same handle must not overlap; independent handles are independent. */
+PRICHS_API int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* resid_dev,
+                       const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T,
+                       void* stream);
+
+/* The same call with HOST buffers, the shape in which the reference's MoELayer::forward(&Tensor) -> Tensor
+ * is used (f32 row-major slices, tensor.rs:14-29): copies x (and resid) to the device, runs the forward,
+ * copies y back and waits for it. Pinned host memory makes the copies asynchronous; pageable memory works. */
+PRICHS_API int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host,
+                            const float* concept_bias, int n_concept, float* y_host, int T);
+
+/* Waits for the handle's last stream and returns the device status word of the work enqueued so far:
+ * PRICHS_OK, PRICHS_ERR_CAPACITY (an expert's segment did not fit) or PRICHS_ERR_TIMEOUT (a bounded wait
+ * inside a kernel gave up). The reference has no counterpart: its launches report nothing. */
+PRICHS_API int prichs_moe_sync_status(prichs_moe_t* h);
+
+/* ---- routing results of the last forward (the MoEStash fields, moe.rs:44-53) ---------------------- */
+
+/* counts[e] = number of (token, slot) assignments expert e received in the last forward on this rank
+ * (the lengths of expert_assignments, moe.rs:121,140). Waits for the handle's last stream. */
+PRICHS_API int prichs_moe_get_counts(prichs_moe_t* h, int64_t* counts_host, int n);
+
+/* router_logits [T,E] fp32, selected_experts [T,k] int32, gating_weights [T,k] fp32 of the last forward;
+ * any pointer may be null. Waits for the handle's last stream. */
+PRICHS_API int prichs_moe_get_routing(prichs_moe_t* h, float* logits_host, int32_t* selected_host, float* gating_host,
+                           int T);
+
+/* ---- aux-loss-free bias update ------------------------------------------------------------------- */
+
+/* MoELayer::update_aux_free_bias(expert_token_counts, total_tokens, gamma) (moe.rs:228-245) with host
+ * counts, as the reference's call sites pass them (model.rs:786-792,1541-1548):
+ *   b_i += gamma * (top_k/E - counts[i]/total_tokens);   no-op when total_tokens == 0. */
+PRICHS_API int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* expert_token_counts, int n,
+                                    size_t total_tokens, float gamma);
+
+/* The same update taken from the counts of the last forward without leaving the device (enqueued on
+ * `stream`). total_tokens == 0 means "the T of the last forward". In expert-parallel mode the counts and
+ * total_tokens are the sums over all ranks, so every rank applies the identical update. */
+PRICHS_API int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_tokens, void* stream);
+
+/* ---- expert parallelism (no counterpart in the reference, which is single-GPU) --------------------- */
+
+/* Rank 0 fills a 128-byte id, the host passes it to every rank (any channel), then each rank calls init.
+ * Experts are partitioned evenly; the shared expert, router and bias are replicated. */
+PRICHS_API int prichs_moe_ep_unique_id(void* id128);
+PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id128);
+
+/* Rows this rank's experts received in the last forward (expert-parallel load), host value. */
+PRICHS_API int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows);
+
+/* ---- diagnostics --------------------------------------------------------------------------------- */
+
+/* Message of the last error on the calling thread ("" if none). */
+PRICHS_API const char* prichs_last_error(void);
+
+/* Number of kernels this library has launched since it was loaded (all handles). */
+PRICHS_API int64_t prichs_kernel_launches(void);
+
+/* Device-time breakdown of the last forward on this handle, in milliseconds, measured with CUDA events
+ * recorded on the forward's stream when timing was enabled: router, scan, dispatch, gate_up, down,
+ * combine (6 floats). Enabling timing adds event records only. */
+PRICHS_API int prichs_moe_enable_timing(prichs_moe_t* h, int on);
+PRICHS_API int prichs_moe_get_stage_ms(prichs_moe_t* h, float* ms6);
+
+/* Copies `bytes` bytes at `offset_bytes` of one internal device buffer of the last forward to the host (waits
+ * for the handle's last stream). For tests and diagnostics of the intermediate stages; the reference exposes
+ * the same intermediates as the stash vectors of forward_train (moe.rs:32-53).
+ *   which: 0 converted activations [T,K1] bf16   1 permuted rows [Rcap,K1] bf16   2 hidden H [Tcap+Rcap,K2] bf16
+ *          3 expert outputs [Tcap+Rcap,d] (bf16; fp32 in PRICHS_MODE_F32)          4 row map pos [T,2] int32
+ *          5 routing summary (struct of ints: counts[8], seg_base[8], src_off[8], total[8], n_mtiles,
+ *            recv_rows, overflow, pad, cmat[64])   6 per-tile histograms [ceil(T/16),8] int32
+ *          7 their exclusive prefix sums           8 m-tile -> weight slot table int32
+ *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 128. */
+PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes);
+
+/* ---- stand-alone kernels with the reference's signatures ----------------------------------------- */
+
+/* Same symbols, arguments and semantics as the reference's wrappers, so engine.rs links unchanged:
+ *   launch_moe_gather       kernels.cu:993-1007   out[i,:] = in[idx[i],:]
+ *   launch_moe_scatter_add  kernels.cu:1009-1024  acc[idx[i],:] += w[i] * exp_out[i,:]
+ *   launch_swiglu_forward   kernels.cu:482-496    out = silu(gate) * up
+ * fp32 device pointers, `stream` a cudaStream_t, zero sizes return at once, no status (as there). */
+PRICHS_API void launch_moe_gather(const float* dev_in, const int* dev_token_indices, float* dev_out, size_t n_tokens,
+                       size_t hidden_dim, void* stream);
+PRICHS_API void launch_moe_scatter_add(const float* dev_exp_out, const int* dev_token_indices, const float* dev_weights,
+                            float* dev_accum_out, size_t n_tokens, size_t hidden_dim, void* stream);
+PRICHS_API void launch_swiglu_forward(const float* dev_gate, const float* dev_up, float* dev_out, size_t total_elements,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRICHS_MOE_H_ */

@@ -1,0 +1,761 @@
+// libprichs_moe.so -- C ABI (include/prichs_moe.h) over the sm_100a kernels of the PRICHS MoE-layer forward.
+//
+// One handle = the device state of one MoELayer (crates/prichs-model/src/moe.rs:58-64): repacked weights,
+// router bias, workspace for max_tokens, TMA descriptors. A forward is six launches on the caller's stream:
+//   router -> scan/plan -> dispatch -> grouped gate|up GEMM (+SwiGLU) -> grouped down GEMM -> combine.
+// There is no CPU fallback: every entry point that needs the device fails with PRICHS_ERR_CUDA without one.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <type_traits>
+#include <vector>
+
+#include "../../include/prichs_moe.h"
+#include "expert_gemm_sm100.cuh"
+#include "route_sm100.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (expr);                                                                   \
+        if (e__ != cudaSuccess)                                                                     \
+            return fail(PRICHS_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                        __FILE__, __LINE__);                                                        \
+    } while (0)
+
+#define LAUNCH_CHECK(name)                                                                    \
+    do {                                                                                      \
+        g_launches.fetch_add(1, std::memory_order_relaxed);                                   \
+        cudaError_t e__ = cudaGetLastError();                                                 \
+        if (e__ != cudaSuccess)                                                               \
+            return fail(PRICHS_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+using bf16 = __nv_bfloat16;
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, cols] -> tensor map with a (64 x box_rows) box and the 128-byte swizzle.
+int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(PRICHS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * 2) % 16 != 0)
+        return fail(PRICHS_ERR_BAD_ARG, "tensor map base and row pitch must be 16-byte aligned");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)egemm::BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PRICHS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return PRICHS_OK;
+}
+
+// ---- weight repacking (once, at upload) -------------------------------------------------------------
+// gate/up [d,f] fp32 (x.W layout) -> rows of the stacked K-major B operand of the first GEMM:
+// row n of a slot, n = blk*256 + r, holds hidden unit blk*128 + (r % 128) of gate (r < 128) or up (r >= 128).
+// kw = d (bf16 mode) or 2d ([hi | lo], fp32-fidelity mode).
+__global__ void repack_gate_up_kernel(const float* __restrict__ wg, const float* __restrict__ wu,
+                                      bf16* __restrict__ dst, int d, int f, int split) {
+    const int kw = split ? 2 * d : d;
+    const size_t total = (size_t)2 * f * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i / d), k = (int)(i % d);
+        const int blk = n / 256, r = n % 256;
+        const int col = blk * 128 + (r & 127);
+        const float v = (r < 128 ? wg : wu)[(size_t)k * f + col];
+        const bf16 hi = __float2bfloat16_rn(v);
+        dst[(size_t)n * kw + k] = hi;
+        if (split) dst[(size_t)n * kw + d + k] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
+}
+
+// down [f,d] fp32 -> rows n < d of the K-major B operand of the second GEMM, K = f (or [hi | lo] = 2f).
+__global__ void repack_down_kernel(const float* __restrict__ wd, bf16* __restrict__ dst, int d, int f, int split) {
+    const int kw = split ? 2 * f : f;
+    const size_t total = (size_t)d * f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i / f), k = (int)(i % f);
+        const float v = wd[(size_t)k * d + n];
+        const bf16 hi = __float2bfloat16_rn(v);
+        dst[(size_t)n * kw + k] = hi;
+        if (split) dst[(size_t)n * kw + f + k] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
+}
+
+// router [d,E] fp32 -> transposed bf16 parts [3][8][d] (hi, mid, lo; rows >= E zero) and the padded fp32
+// copy [d][8] used by the fp32-fidelity router.
+__global__ void repack_router_kernel(const float* __restrict__ wr, bf16* __restrict__ wrt, float* __restrict__ wr8,
+                                     int d, int E) {
+    const int total = d * route::MAX_E;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int e = i / d, k = i % d;
+        const float v = e < E ? wr[(size_t)k * E + e] : 0.f;
+        const bf16 p0 = __float2bfloat16_rn(v);
+        const float r1 = v - __bfloat162float(p0);
+        const bf16 p1 = __float2bfloat16_rn(r1);
+        const bf16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+        wrt[i] = p0;
+        wrt[total + i] = p1;
+        wrt[2 * total + i] = p2;
+        wr8[(size_t)k * route::MAX_E + e] = v;
+    }
+}
+
+// ---- the reference's stand-alone kernels, same semantics (kernels.cu:444-457,888-924) -----------------
+__global__ void compat_gather_kernel(const float* __restrict__ in, const int* __restrict__ idx, float* __restrict__ out,
+                                     size_t n, size_t d) {
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n) return;
+    const float* src = in + (size_t)idx[warp] * d;
+    float* dst = out + warp * d;
+    if ((d & 3) == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (size_t c = lane; c < d / 4; c += 32)
+            reinterpret_cast<float4*>(dst)[c] = reinterpret_cast<const float4*>(src)[c];
+    } else {
+        for (size_t c = lane; c < d; c += 32) dst[c] = src[c];
+    }
+}
+
+__global__ void compat_scatter_add_kernel(const float* __restrict__ exp_out, const int* __restrict__ idx,
+                                          const float* __restrict__ w, float* __restrict__ acc, size_t n, size_t d) {
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n) return;
+    const float wi = w[warp];
+    const float* src = exp_out + warp * d;
+    float* dst = acc + (size_t)idx[warp] * d;
+    // rows of one call may repeat an index, so the accumulation stays atomic like the reference's
+    for (size_t c = lane; c < d; c += 32) atomicAdd(dst + c, wi * src[c]);
+}
+
+__global__ void compat_swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                     float* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float g = gate[i];
+        out[i] = (g * (1.0f / (1.0f + __expf(-g)))) * up[i];
+    }
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+}  // namespace
+
+// =====================================================================================================
+struct prichs_moe {
+    prichs_moe_config_t cfg;
+    int d, f, E, k, Tmax, mode, device;
+    int world, rank, El;   // expert-parallel group, local routed experts
+    int n_slots;           // weight slots held locally: shared + El
+    int K1, K2;            // K extent of the A operands (d, f; doubled in the fp32-fidelity mode)
+    int Tcap;              // max_tokens rounded up to 128: row where the permuted region starts in H / Y
+    int Rcap;              // rows of the permuted region (multiple of 128)
+    int sm_count;
+    bool weights_ready;
+    int rt_nsplit;
+
+    bf16 *w_gu, *w_dn, *w_rt;
+    float *w_r8, *bias;
+    bf16 *xs, *xp, *hbuf;
+    void* ybuf;
+    float *logits, *gates;
+    int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
+    route::RouteMeta* meta;
+    CUtensorMap tm_xp, tm_wgu, tm_h, tm_wdn;
+
+    // host-buffer path
+    float *stage_x, *stage_r, *stage_y;
+    cudaStream_t own_stream;
+
+    cudaStream_t last_stream;
+    int last_T;
+    bool timing;
+    cudaEvent_t ev[7];
+    bool ev_valid;
+};
+
+namespace {
+
+template <class T>
+int dalloc(T** p, size_t n) {
+    *p = nullptr;
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(T)));
+    return PRICHS_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+int translate_status(int s) {
+    switch (s) {
+        case 0: return PRICHS_OK;
+        case -2: return fail(PRICHS_ERR_CAPACITY, "an expert received more rows than the permuted region holds");
+        case -5: return fail(PRICHS_ERR_TIMEOUT, "a bounded device-side wait gave up in the expert GEMM");
+        default: return fail(PRICHS_ERR_CUDA, "device status word %d", s);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* prichs_last_error(void) { return g_err; }
+int64_t prichs_kernel_launches(void) { return (int64_t)g_launches.load(); }
+
+int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle) {
+    if (!cfg || !out_handle) return fail(PRICHS_ERR_BAD_ARG, "null config or handle pointer");
+    *out_handle = nullptr;
+    const int d = cfg->hidden_dim, f = cfg->intermediate_dim, E = cfg->num_experts, k = cfg->top_k;
+    if (d <= 0 || f <= 0 || d % 256 != 0 || f % 128 != 0)
+        return fail(PRICHS_ERR_BAD_SHAPE, "hidden_dim must be a multiple of 256 and intermediate_dim of 128 (got %d, %d)", d, f);
+    if (E < 1 || E > route::MAX_E) return fail(PRICHS_ERR_BAD_SHAPE, "num_experts must be in 1..8 (got %d)", E);
+    if (k < 1 || k > 2 || k > E) return fail(PRICHS_ERR_BAD_SHAPE, "k must be <= logits length and at most 2 (got %d)", k);
+    if (cfg->max_tokens < 1) return fail(PRICHS_ERR_BAD_SHAPE, "max_tokens must be positive");
+    if (cfg->mode != PRICHS_MODE_BF16 && cfg->mode != PRICHS_MODE_F32) return fail(PRICHS_ERR_BAD_ARG, "unknown mode %d", cfg->mode);
+    const int world = cfg->ep_world <= 0 ? 1 : cfg->ep_world;
+    if (world > route::MAX_RANKS || E % world != 0 || cfg->ep_rank < 0 || cfg->ep_rank >= world)
+        return fail(PRICHS_ERR_BAD_ARG, "ep_world must divide num_experts and ep_rank lie in [0, ep_world)");
+
+    int dev = cfg->device;
+    if (dev < 0) CUDA_TRY(cudaGetDevice(&dev));
+    int ndev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&ndev));
+    if (dev >= ndev) return fail(PRICHS_ERR_CUDA, "device %d does not exist", dev);
+    DeviceGuard guard(dev);
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) return fail(PRICHS_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+
+    prichs_moe* h = new prichs_moe();
+    memset(h, 0, sizeof(*h));
+    h->cfg = *cfg;
+    h->d = d; h->f = f; h->E = E; h->k = k; h->Tmax = cfg->max_tokens; h->mode = cfg->mode; h->device = dev;
+    h->world = world; h->rank = cfg->ep_rank; h->El = E / world; h->n_slots = 1 + h->El;
+    const int mul = h->mode == PRICHS_MODE_F32 ? 2 : 1;
+    h->K1 = d * mul; h->K2 = f * mul;
+    h->Tcap = round_up(h->Tmax, 128);
+    long long recv = cfg->ep_max_recv_rows > 0 ? cfg->ep_max_recv_rows : (long long)world * h->Tmax * k;
+    if (world == 1) recv = (long long)h->Tmax * k;
+    const long long rcap = (recv + (long long)h->El * 127 + 127) / 128 * 128;
+    if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30))
+        return fail(PRICHS_ERR_CAPACITY, "workspace for max_tokens=%d is too large", h->Tmax);
+    h->Rcap = (int)rcap;
+    h->sm_count = prop.multiProcessorCount;
+
+    int rc = PRICHS_OK;
+    auto A = [&](int r) { if (rc == PRICHS_OK) rc = r; };
+    const size_t rows_all = (size_t)h->Tcap + h->Rcap;
+    const size_t ntiles = ((size_t)h->Tmax + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    A(dalloc(&h->w_gu, (size_t)h->n_slots * 2 * f * h->K1));
+    A(dalloc(&h->w_dn, (size_t)h->n_slots * d * h->K2));
+    A(dalloc(&h->w_rt, (size_t)3 * route::MAX_E * d));
+    A(dalloc(&h->w_r8, (size_t)d * route::MAX_E));
+    A(dalloc(&h->bias, route::MAX_E));
+    A(dalloc(&h->xs, (size_t)h->Tmax * h->K1));
+    A(dalloc(&h->xp, (size_t)h->Rcap * h->K1));
+    A(dalloc(&h->hbuf, rows_all * h->K2));
+    {
+        void* p = nullptr;
+        if (rc == PRICHS_OK && cudaMalloc(&p, rows_all * d * (h->mode == PRICHS_MODE_F32 ? 4 : 2)) != cudaSuccess)
+            rc = fail(PRICHS_ERR_CUDA, "cudaMalloc of the expert-output buffer failed");
+        h->ybuf = p;
+    }
+    A(dalloc(&h->logits, (size_t)h->Tmax * route::MAX_E));
+    A(dalloc(&h->gates, (size_t)h->Tmax * 2));
+    A(dalloc(&h->sel, (size_t)h->Tmax * 2));
+    A(dalloc(&h->pos, (size_t)h->Tmax * 2));
+    A(dalloc(&h->tile_counts, ntiles * route::MAX_E));
+    A(dalloc(&h->tile_prefix, ntiles * route::MAX_E));
+    A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
+    A(dalloc(&h->status, 1));
+    A(dalloc(&h->meta, 1));
+    if (rc != PRICHS_OK) {
+        prichs_moe_destroy(h);
+        return rc;
+    }
+    cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
+    cudaMemset(h->status, 0, sizeof(int));
+    cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
+    cudaMemset(h->xp, 0, (size_t)h->Rcap * h->K1 * sizeof(bf16));
+    cudaMemset(h->hbuf, 0, rows_all * h->K2 * sizeof(bf16));
+
+    A(make_tmap(&h->tm_xp, h->xp, h->Rcap, h->K1, egemm::BM));
+    A(make_tmap(&h->tm_wgu, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, egemm::BN));
+    A(make_tmap(&h->tm_h, h->hbuf, rows_all, h->K2, egemm::BM));
+    A(make_tmap(&h->tm_wdn, h->w_dn, (size_t)h->n_slots * d, h->K2, egemm::BN));
+    if (rc == PRICHS_OK) {
+        if (cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess)
+            rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the expert GEMM", egemm::SMEM_BYTES);
+    }
+    for (int i = 0; i < 7 && rc == PRICHS_OK; ++i)
+        if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "cudaEventCreate failed");
+    if (rc == PRICHS_OK && cudaDeviceSynchronize() != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "device set-up failed");
+    if (rc != PRICHS_OK) {
+        prichs_moe_destroy(h);
+        return rc;
+    }
+    *out_handle = h;
+    return PRICHS_OK;
+}
+
+int prichs_moe_destroy(prichs_moe_t* h) {
+    if (!h) return PRICHS_OK;
+    DeviceGuard guard(h->device);
+    cudaDeviceSynchronize();
+    void* ptrs[] = {h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
+                    h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
+                    h->stage_r, h->stage_y};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    for (int i = 0; i < 7; ++i)
+        if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+    if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    delete h;
+    return PRICHS_OK;
+}
+
+int prichs_moe_upload_weights(prichs_moe_t* h, const float* const* host_ptrs, int n_ptrs) {
+    if (!h || !host_ptrs) return fail(PRICHS_ERR_BAD_ARG, "null handle or pointer array");
+    if (n_ptrs != 1 + 3 * (1 + h->E))
+        return fail(PRICHS_ERR_BAD_SHAPE, "expected %d weight arrays (router, shared g/u/d, then g/u/d per expert), got %d",
+                    1 + 3 * (1 + h->E), n_ptrs);
+    DeviceGuard guard(h->device);
+    const int d = h->d, f = h->f, E = h->E;
+    const int split = h->mode == PRICHS_MODE_F32;
+    const size_t nmat = (size_t)d * f;
+    float* stage = nullptr;
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&stage), 3 * nmat * sizeof(float)));
+    int rc = PRICHS_OK;
+    auto bail = [&](int r) { cudaFree(stage); return r; };
+
+    // router
+    if (!host_ptrs[0]) return bail(fail(PRICHS_ERR_BAD_ARG, "router weights are null"));
+    {
+        const float* wr = host_ptrs[0];
+        bool exact = true;
+        for (size_t i = 0; i < (size_t)d * E && exact; ++i) {
+            uint32_t bits;
+            memcpy(&bits, &wr[i], 4);
+            exact = (bits & 0xffffu) == 0;
+        }
+        h->rt_nsplit = exact ? 1 : 3;
+        if (cudaMemcpy(stage, wr, (size_t)d * E * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+            return bail(fail(PRICHS_ERR_CUDA, "copy of the router weights failed"));
+        repack_router_kernel<<<64, 256>>>(stage, h->w_rt, h->w_r8, d, E);
+        g_launches.fetch_add(1);
+    }
+    for (int slot = 0; slot < h->n_slots && rc == PRICHS_OK; ++slot) {
+        // slot 0 = shared expert, slot 1 + le = routed expert rank*El + le
+        const int base = slot == 0 ? 1 : 4 + 3 * (h->rank * h->El + (slot - 1));
+        const float *wg = host_ptrs[base], *wu = host_ptrs[base + 1], *wd = host_ptrs[base + 2];
+        if (!wg || !wu || !wd) return bail(fail(PRICHS_ERR_BAD_ARG, "weights of a locally owned expert are null (slot %d)", slot));
+        if (cudaMemcpy(stage, wg, nmat * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(stage + nmat, wu, nmat * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(stage + 2 * nmat, wd, nmat * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+            return bail(fail(PRICHS_ERR_CUDA, "copy of expert weights failed (slot %d)", slot));
+        repack_gate_up_kernel<<<1024, 256>>>(stage, stage + nmat, h->w_gu + (size_t)slot * 2 * f * h->K1, d, f, split);
+        repack_down_kernel<<<1024, 256>>>(stage + 2 * nmat, h->w_dn + (size_t)slot * d * h->K2, d, f, split);
+        g_launches.fetch_add(2);
+        if (cudaDeviceSynchronize() != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "weight repack failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    cudaFree(stage);
+    if (rc == PRICHS_OK) h->weights_ready = true;
+    return rc;
+}
+
+int prichs_moe_set_bias(prichs_moe_t* h, const float* host_bias, int n) {
+    if (!h || !host_bias) return fail(PRICHS_ERR_BAD_ARG, "null handle or bias");
+    if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "router_bias has %d entries, the layer has %d experts", n, h->E);
+    DeviceGuard guard(h->device);
+    float tmp[route::MAX_E] = {0};
+    memcpy(tmp, host_bias, n * sizeof(float));
+    CUDA_TRY(cudaMemcpy(h->bias, tmp, sizeof(tmp), cudaMemcpyHostToDevice));
+    return PRICHS_OK;
+}
+
+int prichs_moe_get_bias(prichs_moe_t* h, float* host_bias, int n) {
+    if (!h || !host_bias) return fail(PRICHS_ERR_BAD_ARG, "null handle or bias");
+    if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "router_bias has %d entries, the layer has %d experts", n, h->E);
+    DeviceGuard guard(h->device);
+    float tmp[route::MAX_E];
+    CUDA_TRY(cudaMemcpy(tmp, h->bias, sizeof(tmp), cudaMemcpyDeviceToHost));
+    memcpy(host_bias, tmp, n * sizeof(float));
+    return PRICHS_OK;
+}
+
+int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* resid_dev, const float* concept_bias,
+                       int n_concept, void* y_dev, int y_dtype, int T, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (!h->weights_ready) return fail(PRICHS_ERR_BAD_ARG, "weights have not been uploaded");
+    if (T < 0) return fail(PRICHS_ERR_BAD_SHAPE, "negative token count");
+    if (T > h->Tmax) return fail(PRICHS_ERR_CAPACITY, "T=%d exceeds max_tokens=%d of this handle", T, h->Tmax);
+    if ((x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) || (y_dtype != PRICHS_DTYPE_F32 && y_dtype != PRICHS_DTYPE_BF16))
+        return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    if (h->mode == PRICHS_MODE_F32 && x_dtype != PRICHS_DTYPE_F32)
+        return fail(PRICHS_ERR_BAD_ARG, "the fp32-fidelity mode takes fp32 activations");
+    if (n_concept < 0 || (n_concept > 0 && !concept_bias)) return fail(PRICHS_ERR_BAD_ARG, "concept bias length without data");
+    if (h->world > 1) return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not initialised");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+    h->last_stream = st;
+    h->last_T = T;
+    if (T == 0) return PRICHS_OK;
+    if (!x_dev || !y_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation pointer");
+    const size_t xalign = x_dtype == PRICHS_DTYPE_F32 ? 15 : 15;
+    if ((reinterpret_cast<uintptr_t>(x_dev) & xalign) || (reinterpret_cast<uintptr_t>(y_dev) & 15) ||
+        (resid_dev && (reinterpret_cast<uintptr_t>(resid_dev) & 15)))
+        return fail(PRICHS_ERR_BAD_ARG, "activation pointers must be 16-byte aligned");
+    DeviceGuard guard(h->device);
+
+    const int d = h->d, f = h->f, E = h->E;
+    route::ConceptBias cb;
+    for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = (e < n_concept && e < E) ? concept_bias[e] : 0.0f;
+
+    const bool f32mode = h->mode == PRICHS_MODE_F32;
+    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    CUtensorMap tm_x;
+    int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
+    if (rc != PRICHS_OK) return rc;
+
+    const bool timing = h->timing;
+    int evi = 0;
+    auto mark = [&]() { if (timing) cudaEventRecord(h->ev[evi++], st); };
+    h->ev_valid = false;
+
+    const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    mark();
+    // 1. router
+    if (f32mode) {
+        route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
+                                                        h->logits, h->sel, h->gates, h->tile_counts);
+    } else {
+        const int grid = (ntiles + 1) / 2;
+        if (x_dtype == PRICHS_DTYPE_F32) {
+            if (h->rt_nsplit == 1)
+                route::router_mma_kernel<1, true><<<grid, 64, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+            else
+                route::router_mma_kernel<3, true><<<grid, 64, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+        } else {
+            if (h->rt_nsplit == 1)
+                route::router_mma_kernel<1, false><<<grid, 64, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+            else
+                route::router_mma_kernel<3, false><<<grid, 64, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+        }
+    }
+    LAUNCH_CHECK("router");
+    mark();
+    // 2. prefix sums + placement plan
+    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0, h->Rcap, 1, h->status);
+    LAUNCH_CHECK("scan");
+    mark();
+    // 3. dispatch
+    route::PeerPtrs xp_peers, y_peers;
+    for (int i = 0; i < route::MAX_RANKS; ++i) {
+        xp_peers.p[i] = h->xp;
+        y_peers.p[i] = h->ybuf;
+    }
+    route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, h->sel, h->tile_prefix, h->meta, xp_peers, h->El, h->pos);
+    LAUNCH_CHECK("dispatch");
+    mark();
+    // 4. gate|up GEMM + SwiGLU for the shared and all routed experts
+    egemm::Args a1;
+    memset(&a1, 0, sizeof(a1));
+    a1.nk = d / egemm::BK;
+    a1.split3 = f32mode;
+    a1.n_ntiles = f / 128;
+    a1.shared_mtiles = (T + 127) / 128;
+    a1.routed_base_tiles = h->Tcap / 128;
+    a1.a_routed_tile_off = 0;
+    a1.n_routed_mtiles = &h->meta->n_routed_mtiles;
+    a1.mtile_slot = h->mtile_slot;
+    a1.w_rows = 2 * f;
+    a1.out_split = f32mode;
+    a1.out_lo_off = f;
+    a1.out_f32 = 0;
+    a1.out = h->hbuf;
+    a1.ldo = h->K2;
+    a1.status = h->status;
+    egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, a1);
+    LAUNCH_CHECK("gate/up GEMM");
+    mark();
+    // 5. down GEMM
+    egemm::Args a2 = a1;
+    a2.nk = f / egemm::BK;
+    a2.n_ntiles = d / egemm::BN;
+    a2.a_routed_tile_off = h->Tcap / 128;
+    a2.w_rows = d;
+    a2.out_split = 0;
+    a2.out_f32 = f32mode;
+    a2.out = h->ybuf;
+    a2.ldo = d;
+    egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, a2);
+    LAUNCH_CHECK("down GEMM");
+    mark();
+    // 6. combine (+ residual)
+    {
+        const int grid = (T + 7) / 8;
+        const long long rb = h->Tcap;
+        const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
+        const bool of32 = y_dtype == PRICHS_DTYPE_F32;
+#define COMBINE(YF, OF, RS) \
+    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(h->ybuf, y_peers, rb, h->sel, h->gates, h->pos, resid_dev, y_dev, T, d, h->El)
+        if (f32mode) {
+            if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
+            else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
+        } else {
+            if (of32) { if (res == 0) COMBINE(false, true, 0); else if (res == 1) COMBINE(false, true, 1); else COMBINE(false, true, 2); }
+            else      { if (res == 0) COMBINE(false, false, 0); else if (res == 1) COMBINE(false, false, 1); else COMBINE(false, false, 2); }
+        }
+#undef COMBINE
+        LAUNCH_CHECK("combine");
+    }
+    mark();
+    h->ev_valid = timing;
+    return PRICHS_OK;
+}
+
+int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host, const float* concept_bias,
+                            int n_concept, float* y_host, int T) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (T < 0) return fail(PRICHS_ERR_BAD_SHAPE, "negative token count");
+    if (T > h->Tmax) return fail(PRICHS_ERR_CAPACITY, "T=%d exceeds max_tokens=%d of this handle", T, h->Tmax);
+    if (T == 0) return PRICHS_OK;
+    if (!x_host || !y_host) return fail(PRICHS_ERR_BAD_ARG, "null host buffer");
+    DeviceGuard guard(h->device);
+    const size_t n = (size_t)h->Tmax * h->d;
+    if (!h->stage_x) {
+        int rc = dalloc(&h->stage_x, n);
+        if (rc == PRICHS_OK) rc = dalloc(&h->stage_y, n);
+        if (rc != PRICHS_OK) return rc;
+        CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+    }
+    if (resid_host && !h->stage_r) {
+        int rc = dalloc(&h->stage_r, n);
+        if (rc != PRICHS_OK) return rc;
+    }
+    const size_t bytes = (size_t)T * h->d * sizeof(float);
+    cudaStream_t st = h->own_stream;
+    CUDA_TRY(cudaMemcpyAsync(h->stage_x, x_host, bytes, cudaMemcpyHostToDevice, st));
+    if (resid_host) CUDA_TRY(cudaMemcpyAsync(h->stage_r, resid_host, bytes, cudaMemcpyHostToDevice, st));
+    int rc = prichs_moe_forward(h, h->stage_x, PRICHS_DTYPE_F32, resid_host ? h->stage_r : nullptr, concept_bias, n_concept,
+                                h->stage_y, PRICHS_DTYPE_F32, T, st);
+    if (rc != PRICHS_OK) return rc;
+    CUDA_TRY(cudaMemcpyAsync(y_host, h->stage_y, bytes, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    int s = 0;
+    CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return translate_status(s);
+}
+
+int prichs_moe_sync_status(prichs_moe_t* h) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    DeviceGuard guard(h->device);
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    int s = 0;
+    CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return translate_status(s);
+}
+
+int prichs_moe_get_counts(prichs_moe_t* h, int64_t* counts_host, int n) {
+    if (!h || !counts_host) return fail(PRICHS_ERR_BAD_ARG, "null handle or output");
+    if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "counts has %d entries, the layer has %d experts", n, h->E);
+    DeviceGuard guard(h->device);
+    if (h->last_T == 0) {
+        for (int i = 0; i < n; ++i) counts_host[i] = 0;
+        return PRICHS_OK;
+    }
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    route::RouteMeta m;
+    CUDA_TRY(cudaMemcpy(&m, h->meta, sizeof(m), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; ++i) counts_host[i] = m.counts[i];
+    return PRICHS_OK;
+}
+
+int prichs_moe_get_routing(prichs_moe_t* h, float* logits_host, int32_t* selected_host, float* gating_host, int T) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (T != h->last_T) return fail(PRICHS_ERR_BAD_SHAPE, "T=%d differs from the last forward's T=%d", T, h->last_T);
+    if (T == 0) return PRICHS_OK;
+    DeviceGuard guard(h->device);
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    const int E = h->E, k = h->k;
+    if (logits_host) {
+        std::vector<float> tmp((size_t)T * route::MAX_E);
+        CUDA_TRY(cudaMemcpy(tmp.data(), h->logits, tmp.size() * sizeof(float), cudaMemcpyDeviceToHost));
+        for (int t = 0; t < T; ++t)
+            for (int e = 0; e < E; ++e) logits_host[(size_t)t * E + e] = tmp[(size_t)t * route::MAX_E + e];
+    }
+    if (selected_host) {
+        std::vector<int> tmp((size_t)T * 2);
+        CUDA_TRY(cudaMemcpy(tmp.data(), h->sel, tmp.size() * sizeof(int), cudaMemcpyDeviceToHost));
+        for (int t = 0; t < T; ++t)
+            for (int j = 0; j < k; ++j) selected_host[(size_t)t * k + j] = tmp[(size_t)t * 2 + j] & 0xff;
+    }
+    if (gating_host) {
+        std::vector<float> tmp((size_t)T * 2);
+        CUDA_TRY(cudaMemcpy(tmp.data(), h->gates, tmp.size() * sizeof(float), cudaMemcpyDeviceToHost));
+        for (int t = 0; t < T; ++t)
+            for (int j = 0; j < k; ++j) gating_host[(size_t)t * k + j] = tmp[(size_t)t * 2 + j];
+    }
+    return PRICHS_OK;
+}
+
+int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* expert_token_counts, int n, size_t total_tokens, float gamma) {
+    if (!h || !expert_token_counts) return fail(PRICHS_ERR_BAD_ARG, "null handle or counts");
+    if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "counts has %d entries, the layer has %d experts", n, h->E);
+    if (total_tokens == 0) return PRICHS_OK;  // the reference returns early (moe.rs:233-235)
+    DeviceGuard guard(h->device);
+    // Host-supplied counts: same arithmetic as the device kernel, applied through a scratch RouteMeta.
+    route::RouteMeta* tmp = nullptr;
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&tmp), sizeof(route::RouteMeta)));
+    route::RouteMeta m;
+    memset(&m, 0, sizeof(m));
+    for (int i = 0; i < n; ++i) m.total[i] = (int)expert_token_counts[i];
+    cudaError_t e = cudaMemcpy(tmp, &m, sizeof(m), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        route::bias_update_kernel<<<1, 32>>>(h->bias, tmp, h->E, h->k, gamma, (unsigned long long)total_tokens);
+        g_launches.fetch_add(1);
+        e = cudaDeviceSynchronize();
+    }
+    cudaFree(tmp);
+    if (e != cudaSuccess) return fail(PRICHS_ERR_CUDA, "bias update failed: %s", cudaGetErrorString(e));
+    return PRICHS_OK;
+}
+
+int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_tokens, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    DeviceGuard guard(h->device);
+    unsigned long long tot = total_tokens ? (unsigned long long)total_tokens : (unsigned long long)h->last_T * h->world;
+    if (tot == 0) return PRICHS_OK;
+    route::bias_update_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(h->bias, h->meta, h->E, h->k, gamma, tot);
+    LAUNCH_CHECK("bias update");
+    return PRICHS_OK;
+}
+
+int prichs_moe_ep_unique_id(void* id128) {
+    (void)id128;
+    return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not built into this library version");
+}
+int prichs_moe_ep_init(prichs_moe_t* h, const void* id128) {
+    (void)h; (void)id128;
+    return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not built into this library version");
+}
+int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows) {
+    if (!h || !rows) return fail(PRICHS_ERR_BAD_ARG, "null handle or output");
+    DeviceGuard guard(h->device);
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    route::RouteMeta m;
+    CUDA_TRY(cudaMemcpy(&m, h->meta, sizeof(m), cudaMemcpyDeviceToHost));
+    *rows = m.recv_rows;
+    return PRICHS_OK;
+}
+
+int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes) {
+    if (!h || !host_dst) return fail(PRICHS_ERR_BAD_ARG, "null handle or destination");
+    DeviceGuard guard(h->device);
+    const size_t rows_all = (size_t)h->Tcap + h->Rcap;
+    const size_t ntiles = ((size_t)h->Tmax + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    const void* base = nullptr;
+    size_t size = 0;
+    switch (which) {
+        case 0: base = h->xs; size = (size_t)h->Tmax * h->K1 * 2; break;
+        case 1: base = h->xp; size = (size_t)h->Rcap * h->K1 * 2; break;
+        case 2: base = h->hbuf; size = rows_all * h->K2 * 2; break;
+        case 3: base = h->ybuf; size = rows_all * h->d * (h->mode == PRICHS_MODE_F32 ? 4 : 2); break;
+        case 4: base = h->pos; size = (size_t)h->Tmax * 2 * 4; break;
+        case 5: base = h->meta; size = sizeof(route::RouteMeta); break;
+        case 6: base = h->tile_counts; size = ntiles * route::MAX_E * 4; break;
+        case 7: base = h->tile_prefix; size = ntiles * route::MAX_E * 4; break;
+        case 8: base = h->mtile_slot; size = ((size_t)h->Rcap / 128 + 1) * 4; break;
+        default: return fail(PRICHS_ERR_BAD_ARG, "unknown buffer id %d", which);
+    }
+    if (offset_bytes > size || bytes > size - offset_bytes) return fail(PRICHS_ERR_BAD_SHAPE, "range exceeds the buffer (%zu bytes)", size);
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    CUDA_TRY(cudaMemcpy(host_dst, static_cast<const char*>(base) + offset_bytes, bytes, cudaMemcpyDeviceToHost));
+    return PRICHS_OK;
+}
+
+int prichs_moe_enable_timing(prichs_moe_t* h, int on) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    h->timing = on != 0;
+    return PRICHS_OK;
+}
+
+int prichs_moe_get_stage_ms(prichs_moe_t* h, float* ms6) {
+    if (!h || !ms6) return fail(PRICHS_ERR_BAD_ARG, "null handle or output");
+    if (!h->ev_valid) return fail(PRICHS_ERR_BAD_ARG, "timing was not enabled for the last forward");
+    DeviceGuard guard(h->device);
+    CUDA_TRY(cudaEventSynchronize(h->ev[6]));
+    for (int i = 0; i < 6; ++i) CUDA_TRY(cudaEventElapsedTime(&ms6[i], h->ev[i], h->ev[i + 1]));
+    return PRICHS_OK;
+}
+
+void launch_moe_gather(const float* dev_in, const int* dev_token_indices, float* dev_out, size_t n_tokens, size_t hidden_dim, void* stream) {
+    if (n_tokens * hidden_dim == 0) return;
+    const size_t blocks = (n_tokens * 32 + 255) / 256;
+    compat_gather_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dev_in, dev_token_indices, dev_out, n_tokens, hidden_dim);
+    g_launches.fetch_add(1);
+}
+
+void launch_moe_scatter_add(const float* dev_exp_out, const int* dev_token_indices, const float* dev_weights, float* dev_accum_out,
+                            size_t n_tokens, size_t hidden_dim, void* stream) {
+    if (n_tokens * hidden_dim == 0) return;
+    const size_t blocks = (n_tokens * 32 + 255) / 256;
+    compat_scatter_add_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dev_exp_out, dev_token_indices, dev_weights,
+                                                                                                   dev_accum_out, n_tokens, hidden_dim);
+    g_launches.fetch_add(1);
+}
+
+void launch_swiglu_forward(const float* dev_gate, const float* dev_up, float* dev_out, size_t total_elements, void* stream) {
+    if (total_elements == 0) return;
+    size_t blocks = (total_elements + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    compat_swiglu_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dev_gate, dev_up, dev_out, total_elements);
+    g_launches.fetch_add(1);
+}
+
+}  // extern "C"

@@ -1,0 +1,554 @@
+// Routing-side kernels of the MoE layer: fused router (logits + bias + top-2 + gates + histogram),
+// prefix-sum / placement plan, token dispatch (permute), gate-weighted combine (+ residual), bias update.
+// All of them are bound by HBM traffic: 16-byte accesses, one warp per token row (or 16-token MMA tile),
+// no atomics on the data path, results independent of scheduling.
+//
+// Reference semantics restated here (and nowhere copied from):
+//   crates/prichs-model/src/moe.rs:114-142   router logits, bias add, per-token top-k, expert bins
+//   crates/prichs-core/src/ops.rs:219-248    top_k_gating_unbiased (selection on biased logits, gates
+//                                            from the raw logits of the selected experts)
+//   crates/prichs-model/src/moe.rs:146-184   combine: out = shared; experts ascending: out += w * row
+//   crates/prichs-model/src/block.rs:64-67   residual add around the layer
+//   crates/prichs-model/src/moe.rs:228-245   update_aux_free_bias
+#pragma once
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "ptx_sm100.cuh"
+
+namespace route {
+
+constexpr int MAX_E = 8;      // routed experts supported by the 8-column router MMA
+constexpr int MAX_RANKS = 8;  // expert-parallel group size limit
+constexpr int TILE_TOKENS = 16;
+
+// Optional per-expert additive term on the selection logit (moe.rs:128-132), passed by value.
+struct ConceptBias {
+    float v[MAX_E];
+};
+
+// Device-resident routing summary of one forward call.
+struct RouteMeta {
+    int counts[MAX_E];    // assignments this rank produced per expert (lengths of the bins, moe.rs:121,140)
+    int seg_base[MAX_E];  // row, in the owner's permuted buffer, where expert e's segment starts (x128)
+    int src_off[MAX_E];   // rows of lower ranks that precede this rank's rows inside that segment
+    int total[MAX_E];     // per-expert totals over all ranks
+    int n_routed_mtiles;  // 128-row tiles of the local permuted region
+    int recv_rows;        // rows this rank's experts receive (unpadded)
+    int overflow;         // 1 when the local permuted region would exceed its capacity
+    int pad;
+    int cmat[MAX_RANKS * MAX_E];  // counts of every rank, [rank][expert]
+};
+
+struct PeerPtrs {
+    void* p[MAX_RANKS];
+};
+
+// ---------------------------------------------------------------------------------------------------
+// Per-token selection shared by both router kernels. Called by all 32 lanes of a warp; `active` lanes own
+// one token row each, `lower_mask` has a bit for every lane whose token precedes this lane's token.
+//   selection logit  s_e = (L_e + bias_e) + concept_e          (moe.rs:126-134)
+//   top-k of s, ties to the lower index (stable descending sort, ops.rs:226-229); NaN logits are outside
+//   the contract (the reference's result then depends on its sort's internals)
+//   gates from the RAW logits of the selected experts: exp(L_i - max) / (sum + 1e-9)   (ops.rs:233-245)
+// Writes logits [T,8], sel [T,2] (expert | rank-in-tile << 8, or -1), gates [T,2] and the tile's histogram.
+__device__ __forceinline__ void route_finish(const float (&L)[MAX_E], bool active, uint32_t lower_mask, int row,
+                                             int tile, int lane, const float* __restrict__ bias,
+                                             const ConceptBias& cb, int E, int top_k, float* __restrict__ logits,
+                                             int* __restrict__ sel, float* __restrict__ gates,
+                                             int* __restrict__ tile_counts) {
+    int i1 = 0, i2 = -1;
+    float l1 = 0.f, l2 = 0.f;
+    if (active) {
+        float s[MAX_E];
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) s[e] = (L[e] + bias[e]) + cb.v[e];
+        float v1 = s[0];
+#pragma unroll
+        for (int e = 1; e < MAX_E; ++e) {
+            if (e < E && s[e] > v1) {
+                v1 = s[e];
+                i1 = e;
+            }
+        }
+        if (top_k > 1) {
+            float v2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < MAX_E; ++e) {
+                if (e < E && e != i1 && (i2 < 0 || s[e] > v2)) {
+                    v2 = s[e];
+                    i2 = e;
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) {
+            l1 = (e == i1) ? L[e] : l1;
+            l2 = (e == i2) ? L[e] : l2;
+        }
+        float4* lo = reinterpret_cast<float4*>(logits + (size_t)row * MAX_E);
+        lo[0] = make_float4(L[0], L[1], L[2], L[3]);
+        lo[1] = make_float4(L[4], L[5], L[6], L[7]);
+    }
+    // histogram of the tile and rank of each assignment among the tile's earlier tokens
+    int r1 = 0, r2 = 0, my_count = 0;
+#pragma unroll
+    for (int e = 0; e < MAX_E; ++e) {
+        const uint32_t m = __ballot_sync(0xffffffffu, active && (i1 == e || i2 == e));
+        if (i1 == e) r1 = __popc(m & lower_mask);
+        if (i2 == e) r2 = __popc(m & lower_mask);
+        if (lane == e) my_count = __popc(m);
+    }
+    if (lane < MAX_E) tile_counts[(size_t)tile * MAX_E + lane] = my_count;
+    if (active) {
+        float g1, g2 = 0.f;
+        if (i2 >= 0) {
+            const float mx = fmaxf(l1, l2);
+            const float e1 = expf(l1 - mx);
+            const float e2 = expf(l2 - mx);
+            float sum = 0.0f;
+            sum = __fadd_rn(sum, e1);
+            sum = __fadd_rn(sum, e2);
+            const float inv = 1.0f / (sum + 1e-9f);
+            g1 = e1 * inv;
+            g2 = e2 * inv;
+        } else {
+            const float e1 = expf(l1 - l1);
+            const float inv = 1.0f / (e1 + 1e-9f);
+            g1 = e1 * inv;
+        }
+        *reinterpret_cast<int2*>(sel + (size_t)row * 2) = make_int2(i1 | (r1 << 8), i2 >= 0 ? (i2 | (r2 << 8)) : -1);
+        *reinterpret_cast<float2*>(gates + (size_t)row * 2) = make_float2(g1, g2);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Router for bf16 operands. One warp owns a tile of 16 tokens and computes their 8 logits with
+// mma.sync m16n8k16 (N = 8 is exactly the expert count): lane (g = lane/4, q = lane%4) reads 16 contiguous
+// bytes of token row g (and g+8) and 16 contiguous bytes of row g of the transposed router weight. The
+// dot product does not care in which order k is visited, so those 8 consecutive elements are fed to two
+// MMAs as the fragment slots (2q, 2q+1, 2q+8, 2q+9) of A and B alike -- every global access is a full
+// 16-byte vector and no shared memory is needed.
+// wrt: [NSPLIT][8][d] bf16; NSPLIT = 3 holds hi/mid/lo parts of fp32 router weights (their sum is exact to
+// 2^-24), NSPLIT = 1 is used when the weights are bf16 values already.
+// XF32: x is fp32 [T,d]; it is rounded to bf16 (RNE) for the product and the bf16 copy is written to `xs`
+// for the expert GEMMs (saves a separate conversion pass).
+template <int NSPLIT, bool XF32>
+__global__ void __launch_bounds__(64)
+router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ wrt,
+                  const float* __restrict__ bias, const ConceptBias cb, int T, int d, int E, int top_k,
+                  float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
+                  int* __restrict__ tile_counts) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x * 2 + warp;
+    if (tile * TILE_TOKENS >= T) return;
+    const int g = lane >> 2, q = lane & 3;
+    const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
+    const size_t r0c = (size_t)min(r0, T - 1), r1c = (size_t)min(r1, T - 1);
+
+    float acc[NSPLIT][2][4];
+#pragma unroll
+    for (int s = 0; s < NSPLIT; ++s)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[s][h][i] = 0.f;
+
+    const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
+    const size_t wsplit = (size_t)MAX_E * d;
+
+#pragma unroll 4
+    for (int kk = 0; kk < d; kk += 32) {
+        uint4 a0, a1;
+        if (XF32) {
+            const float* x0 = reinterpret_cast<const float*>(x) + r0c * d + kk + 8 * q;
+            const float* x1 = reinterpret_cast<const float*>(x) + r1c * d + kk + 8 * q;
+            const uint4 p0 = ptx::ld_stream_16(x0), p1 = ptx::ld_stream_16(x0 + 4);
+            const uint4 p2 = ptx::ld_stream_16(x1), p3 = ptx::ld_stream_16(x1 + 4);
+            auto pk = [](uint32_t lo, uint32_t hi) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+                return *reinterpret_cast<uint32_t*>(&v);
+            };
+            a0 = make_uint4(pk(p0.x, p0.y), pk(p0.z, p0.w), pk(p1.x, p1.y), pk(p1.z, p1.w));
+            a1 = make_uint4(pk(p2.x, p2.y), pk(p2.z, p2.w), pk(p3.x, p3.y), pk(p3.z, p3.w));
+            if (r0 < T) *reinterpret_cast<uint4*>(xs + (size_t)r0 * d + kk + 8 * q) = a0;
+            if (r1 < T) *reinterpret_cast<uint4*>(xs + (size_t)r1 * d + kk + 8 * q) = a1;
+        } else {
+            const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+            a0 = ptx::ld_stream_16(xb + r0c * d + kk + 8 * q);
+            a1 = ptx::ld_stream_16(xb + r1c * d + kk + 8 * q);
+        }
+#pragma unroll
+        for (int s = 0; s < NSPLIT; ++s) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(wl + s * wsplit + kk));
+            ptx::mma_m16n8k16_bf16(acc[s][0], a0.x, a1.x, a0.y, a1.y, w.x, w.y);
+            ptx::mma_m16n8k16_bf16(acc[s][1], a0.z, a1.z, a0.w, a1.w, w.z, w.w);
+        }
+    }
+    // c[0..1]: row g, experts 2q, 2q+1; c[2..3]: row g+8. Small parts are summed first.
+    float c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float v = 0.f;
+#pragma unroll
+        for (int s = NSPLIT - 1; s >= 0; --s) v += acc[s][0][i] + acc[s][1][i];
+        c[i] = v;
+    }
+    // lanes q = 0 / q = 1 of each quad take row g / g + 8; gather the row's 8 logits from the quad
+    float L[MAX_E];
+    const int qbase = lane & ~3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
+        const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
+        const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
+        const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
+        L[2 * j] = (q == 0) ? t0 : t2;
+        L[2 * j + 1] = (q == 0) ? t1 : t3;
+    }
+    const int row = (q == 0) ? r0 : r1;
+    const bool active = (q < 2) && (row < T);
+    // tokens that precede this lane's token inside the tile: q=0 lanes hold rows 0..7, q=1 lanes rows 8..15
+    const uint32_t below = (1u << (4 * g)) - 1u;
+    const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
+    route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Router of the fp32-fidelity mode: x and W_r stay fp32 (FMA accumulation), one warp per token, one CTA
+// (16 warps) per 16-token tile. Also writes the bf16 hi/lo split of x, [T, 2d] = [hi | lo], which the
+// expert GEMMs consume.  wr8: [d][8] fp32 (columns >= E are zero).
+__global__ void __launch_bounds__(512)
+router_f32_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, const float* __restrict__ wr8,
+                  const float* __restrict__ bias, const ConceptBias cb, int T, int d, int E, int top_k,
+                  float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
+                  int* __restrict__ tile_counts) {
+    __shared__ float sl[TILE_TOKENS][MAX_E];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x;
+    const int row = tile * TILE_TOKENS + warp;
+    if (row < T) {
+        float acc[MAX_E];
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) acc[e] = 0.f;
+        const float* xr = x + (size_t)row * d;
+        __nv_bfloat16* xo = xs + (size_t)row * 2 * d;
+        for (int k = lane * 4; k < d; k += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + k);
+            const float xv[4] = {v.x, v.y, v.z, v.w};
+            __nv_bfloat16 hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                hi[j] = __float2bfloat16_rn(xv[j]);
+                lo[j] = __float2bfloat16_rn(xv[j] - __bfloat162float(hi[j]));
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(wr8 + (size_t)(k + j) * MAX_E));
+                const float4 w1 = __ldg(reinterpret_cast<const float4*>(wr8 + (size_t)(k + j) * MAX_E + 4));
+                acc[0] = fmaf(xv[j], w0.x, acc[0]);
+                acc[1] = fmaf(xv[j], w0.y, acc[1]);
+                acc[2] = fmaf(xv[j], w0.z, acc[2]);
+                acc[3] = fmaf(xv[j], w0.w, acc[3]);
+                acc[4] = fmaf(xv[j], w1.x, acc[4]);
+                acc[5] = fmaf(xv[j], w1.y, acc[5]);
+                acc[6] = fmaf(xv[j], w1.z, acc[6]);
+                acc[7] = fmaf(xv[j], w1.w, acc[7]);
+            }
+            *reinterpret_cast<uint2*>(xo + k) = *reinterpret_cast<const uint2*>(hi);
+            *reinterpret_cast<uint2*>(xo + d + k) = *reinterpret_cast<const uint2*>(lo);
+        }
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int e = 0; e < MAX_E; ++e) sl[warp][e] = acc[e];
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int r = tile * TILE_TOKENS + lane;
+        const bool active = lane < TILE_TOKENS && r < T;
+        float L[MAX_E];
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) L[e] = active ? sl[lane][e] : 0.f;
+        route_finish(L, active, (1u << lane) - 1u, r, tile, lane, bias, cb, E, top_k, logits, sel, gates,
+                     tile_counts);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Placement plan from the counts matrix (one CTA). For every expert e, owned by rank e / El:
+//   total[e] = sum_s cmat[s][e],  src_off[e] = sum_{s < rank} cmat[s][e],
+//   seg_base[e] = sum of the 128-padded totals of the owner's lower experts.
+// For the local experts it also fills the m-tile -> weight-slot table the grouped GEMM walks.
+__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El,
+                                               int world, int rank, int cap_rows, int* __restrict__ status) {
+    __shared__ int s_total[MAX_E], s_base[MAX_E + 1];
+    const int tid = threadIdx.x;
+    if (tid < MAX_E) {
+        int tot = 0, off = 0;
+        if (tid < E) {
+            for (int s = 0; s < world; ++s) {
+                const int c = meta->cmat[s * MAX_E + tid];
+                tot += c;
+                if (s < rank) off += c;
+            }
+        }
+        s_total[tid] = tot;
+        meta->total[tid] = tot;
+        meta->src_off[tid] = off;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int recv = 0, local_rows = 0;
+        for (int o = 0; o < world; ++o) {
+            int base = 0;
+            for (int le = 0; le < El; ++le) {
+                const int e = o * El + le;
+                meta->seg_base[e] = base;
+                if (o == rank) {
+                    s_base[le] = base;
+                    recv += s_total[e];
+                }
+                base += (s_total[e] + 127) & ~127;
+            }
+            if (o == rank) {
+                s_base[El] = base;
+                local_rows = base;
+            }
+        }
+        const int over = local_rows > cap_rows;
+        meta->overflow = over;
+        meta->recv_rows = recv;
+        meta->n_routed_mtiles = over ? 0 : local_rows / 128;
+        if (over) atomicExch(status, -2);
+    }
+    __syncthreads();
+    const int ntiles = meta->overflow ? 0 : s_base[El] / 128;
+    for (int i = tid; i < ntiles; i += blockDim.x) {
+        int le = 0;
+        while (le + 1 < El && i * 128 >= s_base[le + 1]) ++le;
+        mtile_slot[i] = le;
+    }
+}
+
+// Exclusive prefix sum of the per-tile histograms over tiles (one CTA of 1024 threads; each thread owns a
+// contiguous run of tiles), totals into meta->counts and row `rank` of meta->cmat. With `fuse_plan` (single
+// rank) the placement plan follows in the same launch.
+__global__ void __launch_bounds__(1024)
+scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, int ntiles, RouteMeta* meta,
+            int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
+            int* __restrict__ status) {
+    __shared__ int warp_tot[32][MAX_E];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (ntiles + 1023) / 1024;
+    const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
+    int tot[MAX_E];
+#pragma unroll
+    for (int e = 0; e < MAX_E; ++e) tot[e] = 0;
+    for (int t = t0; t < t1; ++t) {
+        const int4 a = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E);
+        const int4 b = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4);
+        tot[0] += a.x; tot[1] += a.y; tot[2] += a.z; tot[3] += a.w;
+        tot[4] += b.x; tot[5] += b.y; tot[6] += b.z; tot[7] += b.w;
+    }
+    int inc[MAX_E];
+#pragma unroll
+    for (int e = 0; e < MAX_E; ++e) {
+        int v = tot[e];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += n;
+        }
+        inc[e] = v;
+        if (lane == 31) warp_tot[warp][e] = v;
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int e = 0; e < MAX_E; ++e) {
+            int v = warp_tot[lane][e];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += n;
+            }
+            warp_tot[lane][e] = v;  // inclusive over warps
+        }
+    }
+    __syncthreads();
+    int run[MAX_E];
+#pragma unroll
+    for (int e = 0; e < MAX_E; ++e) run[e] = inc[e] - tot[e] + (warp > 0 ? warp_tot[warp - 1][e] : 0);
+    for (int t = t0; t < t1; ++t) {
+        const int4 a = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E);
+        const int4 b = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4);
+        *reinterpret_cast<int4*>(tile_prefix + (size_t)t * MAX_E) = make_int4(run[0], run[1], run[2], run[3]);
+        *reinterpret_cast<int4*>(tile_prefix + (size_t)t * MAX_E + 4) = make_int4(run[4], run[5], run[6], run[7]);
+        run[0] += a.x; run[1] += a.y; run[2] += a.z; run[3] += a.w;
+        run[4] += b.x; run[5] += b.y; run[6] += b.z; run[7] += b.w;
+    }
+    if (tid < MAX_E) {
+        const int c = warp_tot[31][tid];
+        meta->counts[tid] = c;
+        meta->cmat[rank * MAX_E + tid] = c;
+    }
+    if (fuse_plan) {
+        __syncthreads();
+        plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, status);
+    }
+}
+
+// Placement plan as its own launch (expert-parallel mode, after the counts of all ranks were gathered).
+__global__ void __launch_bounds__(256)
+plan_kernel(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows,
+            int* __restrict__ status) {
+    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, status);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Dispatch (token permute): one warp per token. The token's row (row_elems bf16, a multiple of 256) is read
+// once and written to the segment of each selected expert, tokens in ascending order inside a segment, as in
+// the reference's bins (moe.rs:140,155-164). The destination buffer belongs to the expert's owner rank: a
+// plain pointer for local experts, a peer-mapped pointer over NVLink otherwise. pos[t,j] keeps the row.
+__global__ void __launch_bounds__(256)
+dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, const int* __restrict__ sel,
+                const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
+                int* __restrict__ pos) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T || meta->overflow) return;
+    int my_row = -1, my_owner = 0;
+    if (lane < 2) {
+        const int s = sel[(size_t)t * 2 + lane];
+        if (s >= 0) {
+            const int e = s & 0xff, lr = s >> 8;
+            my_row = meta->seg_base[e] + meta->src_off[e] + tile_prefix[(size_t)(t / TILE_TOKENS) * MAX_E + e] + lr;
+            my_owner = e / El;
+            pos[(size_t)t * 2 + lane] = my_row;
+        } else {
+            pos[(size_t)t * 2 + lane] = -1;
+        }
+    }
+    const int row0 = __shfl_sync(0xffffffffu, my_row, 0), row1 = __shfl_sync(0xffffffffu, my_row, 1);
+    const int own0 = __shfl_sync(0xffffffffu, my_owner, 0), own1 = __shfl_sync(0xffffffffu, my_owner, 1);
+    const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)t * row_elems);
+    uint4* d0 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[own0]) + (size_t)max(row0, 0) * row_elems);
+    uint4* d1 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.p[own1]) + (size_t)max(row1, 0) * row_elems);
+    const int nvec = row_elems / 8;
+#pragma unroll 6
+    for (int c = lane; c < nvec; c += 32) {
+        const uint4 v = ptx::ld_stream_16(src + c);
+        if (row0 >= 0) d0[c] = v;
+        if (row1 >= 0) d1[c] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Combine: one warp per token, gather-based (no atomics; the reference's GPU path uses atomicAdd,
+// crates/prichs-cuda/src/kernels.cu:906-924). Follows the CPU order: out = shared row; then the selected
+// experts in ascending expert index, out += gate * row (multiply and add rounded separately, moe.rs:178-184);
+// finally the optional residual, resid + out (block.rs:67).
+// Y rows: the shared expert's at row t of the local buffer, a routed expert's at (routed_base + pos) of its
+// owner's buffer. YF32: expert outputs are fp32 (fp32-fidelity mode) else bf16. RES: 0 none, 1 bf16, 2 fp32.
+template <bool YF32, bool OUTF32, int RES>
+__global__ void __launch_bounds__(256)
+combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtrs y_peers, long long routed_base_rows,
+               const int* __restrict__ sel, const float* __restrict__ gates, const int* __restrict__ pos,
+               const void* __restrict__ resid, void* __restrict__ out, int T, int d, int El) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    const int2 s = *reinterpret_cast<const int2*>(sel + (size_t)t * 2);
+    const float2 gw = *reinterpret_cast<const float2*>(gates + (size_t)t * 2);
+    const int2 p = *reinterpret_cast<const int2*>(pos + (size_t)t * 2);
+    int ea = s.x & 0xff, eb = (s.y >= 0) ? (s.y & 0xff) : -1;
+    float ga = gw.x, gb = gw.y;
+    int pa = p.x, pb = p.y;
+    if (eb >= 0 && eb < ea) {
+        int ti = ea; ea = eb; eb = ti;
+        ti = pa; pa = pb; pb = ti;
+        const float tf = ga; ga = gb; gb = tf;
+    }
+    const bool has_b = eb >= 0;
+    using YT = typename std::conditional<YF32, float, __nv_bfloat16>::type;
+    const YT* ys = reinterpret_cast<const YT*>(y_local) + (size_t)t * d;
+    const YT* ya = reinterpret_cast<const YT*>(y_peers.p[ea / El]) + (size_t)(routed_base_rows + pa) * d;
+    const YT* yb = has_b ? reinterpret_cast<const YT*>(y_peers.p[eb / El]) + (size_t)(routed_base_rows + pb) * d : ys;
+
+    auto load8 = [](const YT* ptr, float (&v)[8]) {
+        if constexpr (YF32) {
+            const uint4 a = ptx::ld_stream_16(ptr), b = ptx::ld_stream_16(ptr + 4);
+            v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+            v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+        } else {
+            const uint4 a = ptx::ld_stream_16(ptr);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        }
+    };
+
+#pragma unroll 2
+    for (int c = lane * 8; c < d; c += 256) {
+        float o[8], a[8], b[8];
+        load8(ys + c, o);
+        load8(ya + c, a);
+        if (has_b) load8(yb + c, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j] = __fadd_rn(o[j], __fmul_rn(ga, a[j]));
+            if (has_b) o[j] = __fadd_rn(o[j], __fmul_rn(gb, b[j]));
+        }
+        if (RES == 1) {
+            const uint4 r = ptx::ld_stream_16(reinterpret_cast<const __nv_bfloat16*>(resid) + (size_t)t * d + c);
+            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                o[2 * j] = __fadd_rn(__uint_as_float(w[j] << 16), o[2 * j]);
+                o[2 * j + 1] = __fadd_rn(__uint_as_float(w[j] & 0xffff0000u), o[2 * j + 1]);
+            }
+        } else if (RES == 2) {
+            const float* rp = reinterpret_cast<const float*>(resid) + (size_t)t * d + c;
+            const uint4 r0 = ptx::ld_stream_16(rp), r1 = ptx::ld_stream_16(rp + 4);
+            const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __fadd_rn(__uint_as_float(w[j]), o[j]);
+        }
+        if (OUTF32) {
+            float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * d + c);
+            op[0] = make_float4(o[0], o[1], o[2], o[3]);
+            op[1] = make_float4(o[4], o[5], o[6], o[7]);
+        } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * d + c) =
+                make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// b_i += gamma * (top_k / E - count_i / total_tokens), each operation rounded on its own like the
+// reference's f32 arithmetic (moe.rs:237-244). count_i is the total over all ranks.
+__global__ void bias_update_kernel(float* __restrict__ bias, const RouteMeta* __restrict__ meta, int E, int top_k,
+                                   float gamma, unsigned long long total_tokens) {
+    const int i = threadIdx.x;
+    if (i >= E || total_tokens == 0ull) return;
+    const float target_load = __fdiv_rn((float)top_k, (float)E);
+    const float actual_load = __fdiv_rn((float)(unsigned long long)meta->total[i], (float)total_tokens);
+    const float diff = __fsub_rn(target_load, actual_load);
+    bias[i] = __fadd_rn(bias[i], __fmul_rn(gamma, diff));
+}
+
+}  // namespace route

@@ -1,0 +1,289 @@
+"""Host-side mirror of the reference's MoE layer API over the C-ABI library.
+
+Same names, argument order and meaning as crates/prichs-model/src/moe.rs:
+    Expert(hidden_dim, intermediate_dim)                 moe.rs:6-29   fields gate_proj, up_proj, down_proj
+    MoELayer(hidden_dim, intermediate_dim, num_experts, top_k)         moe.rs:58-90
+        .router [d,E], .router_bias [E], .shared_expert, .experts, .top_k   (public fields, moe.rs:59-63)
+        .forward(x)                                      moe.rs:223-225
+        .forward_with_memory(x, starkdb_concept_bias)    moe.rs:214-221
+        .forward_train(x, starkdb_concept_bias) -> (out, MoEStash)    moe.rs:93-211
+        .update_aux_free_bias(expert_token_counts, total_tokens, gamma)   moe.rs:228-245
+`x` is a 2-D [T, d] array: a numpy float32 array (host buffers, like the reference's Tensor) or a CUDA torch
+tensor (float32 or bfloat16; the result then stays on the device). Errors: shape mismatches raise
+PrichsError like the reference's `bail!` (ops.rs:11-18); `top_k > num_experts` raises like its assert.
+
+All arithmetic runs in libprichs_moe.so on the GPU. Nothing here computes the layer on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import _capi
+
+
+class PrichsError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+def _check(rc: int):
+    if rc != _capi.OK:
+        raise PrichsError(rc, _capi.last_error())
+
+
+def _randn(rng, shape, std):
+    # Tensor::randn (crates/prichs-core/src/tensor.rs:49-63): N(0, std); the reference draws from an unseeded
+    # thread_rng, here the generator is the caller's.
+    return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+
+
+class Expert:
+    """SwiGLU expert weights in the reference's x.W layout (moe.rs:6-20)."""
+
+    def __init__(self, hidden_dim: int, intermediate_dim: int, rng=None):
+        rng = rng or np.random.default_rng()
+        std = (2.0 / (hidden_dim + intermediate_dim)) ** 0.5
+        self.gate_proj = _randn(rng, (hidden_dim, intermediate_dim), std)
+        self.up_proj = _randn(rng, (hidden_dim, intermediate_dim), std)
+        self.down_proj = _randn(rng, (intermediate_dim, hidden_dim), std)
+
+
+@dataclass
+class MoEStash:
+    """Routing part of the reference's MoEStash (moe.rs:44-53). The activation stashes that only the backward
+    pass reads (shared_gate/up/act/out, routed_stashes) are not produced by this forward-only library."""
+    router_logits: np.ndarray          # [T, E] fp32
+    selected_experts: np.ndarray       # [T*k] int64, slot order = descending selection logit
+    gating_weights: np.ndarray         # [T*k] fp32
+    expert_token_counts: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int64))  # [E]
+
+
+class MoELayer:
+    def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int, top_k: int, *, seed=None,
+                 mode: str = "bf16", max_tokens: int = 0, device: int = -1, ep_world: int = 1, ep_rank: int = 0,
+                 ep_max_recv_rows: int = 0, init: bool = True):
+        rng = np.random.default_rng(seed)
+        self.hidden_dim, self.intermediate_dim = int(hidden_dim), int(intermediate_dim)
+        self.top_k = int(top_k)
+        self._num_experts = int(num_experts)
+        if init:
+            std = (2.0 / (hidden_dim + num_experts)) ** 0.5
+            self.router = _randn(rng, (hidden_dim, num_experts), std)
+            self.shared_expert = Expert(hidden_dim, intermediate_dim, rng)
+            self.experts: List[Expert] = [Expert(hidden_dim, intermediate_dim, rng) for _ in range(num_experts)]
+        else:
+            self.router = None
+            self.shared_expert = None
+            self.experts = []
+        self._bias_host = np.zeros(num_experts, np.float32)
+        self.mode = {"bf16": _capi.MODE_BF16, "f32": _capi.MODE_F32}[mode]
+        self._device, self._ep_world, self._ep_rank, self._ep_max_recv = device, ep_world, ep_rank, ep_max_recv_rows
+        self._h = C.c_void_p()
+        self._max_tokens = 0
+        self._want_max_tokens = int(max_tokens)
+        self._weights_dirty = True
+        self._T_last = 0
+
+    # ---- construction helpers -------------------------------------------------------------------
+    @classmethod
+    def from_weights(cls, weights: Sequence[np.ndarray], top_k: int, **kw) -> "MoELayer":
+        """Build from the flat list [router, shared g/u/d, e0 g/u/d, ...] (model.rs:353-361 order)."""
+        d, E = weights[0].shape
+        f = weights[1].shape[1]
+        if len(weights) != 1 + 3 * (1 + E):
+            raise PrichsError(_capi.ERR_BAD_SHAPE, f"expected {1 + 3 * (1 + E)} weight arrays, got {len(weights)}")
+        self = cls(d, f, E, top_k, init=False, **kw)
+        self.router = np.ascontiguousarray(weights[0], np.float32)
+
+        def mk(i):
+            e = Expert.__new__(Expert)
+            e.gate_proj, e.up_proj, e.down_proj = (np.ascontiguousarray(w, np.float32) for w in weights[i:i + 3])
+            return e
+        self.shared_expert = mk(1)
+        self.experts = [mk(4 + 3 * i) for i in range(E)]
+        return self
+
+    def parameter_list(self) -> List[np.ndarray]:
+        out = [self.router, self.shared_expert.gate_proj, self.shared_expert.up_proj, self.shared_expert.down_proj]
+        for e in self.experts:
+            out += [e.gate_proj, e.up_proj, e.down_proj]
+        return out
+
+    # ---- router_bias: public field of the reference, kept on the device between calls -------------
+    @property
+    def router_bias(self) -> np.ndarray:
+        if self._h:
+            b = np.empty(self._num_experts, np.float32)
+            _check(_capi.lib().prichs_moe_get_bias(self._h, b.ctypes.data_as(C.POINTER(C.c_float)), b.size))
+            self._bias_host = b
+        return self._bias_host.copy()
+
+    @router_bias.setter
+    def router_bias(self, value):
+        b = np.ascontiguousarray(value, np.float32).reshape(-1)
+        if b.size != self._num_experts:
+            raise PrichsError(_capi.ERR_BAD_SHAPE, f"router_bias has {b.size} entries, the layer has {self._num_experts} experts")
+        self._bias_host = b.copy()
+        if self._h:
+            _check(_capi.lib().prichs_moe_set_bias(self._h, b.ctypes.data_as(C.POINTER(C.c_float)), b.size))
+
+    # ---- device handle ----------------------------------------------------------------------------
+    def mark_weights_changed(self):
+        """Call after editing the public weight fields so the next forward uploads them again."""
+        self._weights_dirty = True
+
+    def _ensure(self, T: int):
+        L = _capi.lib()
+        if not self._h or T > self._max_tokens:
+            bias = self.router_bias if self._h else self._bias_host
+            self.close()
+            cap = max(T, self._want_max_tokens, 1)
+            cfg = _capi.Config(self.hidden_dim, self.intermediate_dim, self._num_experts, self.top_k, cap, self.mode,
+                               self._device, self._ep_world, self._ep_rank, self._ep_max_recv)
+            h = C.c_void_p()
+            _check(L.prichs_moe_create(C.byref(cfg), C.byref(h)))
+            self._h, self._max_tokens, self._weights_dirty = h, cap, True
+            _check(L.prichs_moe_set_bias(self._h, bias.ctypes.data_as(C.POINTER(C.c_float)), bias.size))
+        if self._weights_dirty:
+            ws = [np.ascontiguousarray(w, np.float32) for w in self.parameter_list()]
+            shapes = [(self.hidden_dim, self._num_experts)] + [(self.hidden_dim, self.intermediate_dim)] * 2 + \
+                     [(self.intermediate_dim, self.hidden_dim)]
+            for i, w in enumerate(ws):
+                want = shapes[0] if i == 0 else shapes[1 + (i - 1) % 3]
+                if w.shape != want:
+                    raise PrichsError(_capi.ERR_BAD_SHAPE, f"weight {i} has shape {w.shape}, expected {want}")
+            fp = C.POINTER(C.c_float)
+            arr = (fp * len(ws))(*[w.ctypes.data_as(fp) for w in ws])
+            _check(L.prichs_moe_upload_weights(self._h, arr, len(ws)))
+            self._weights_dirty = False
+
+    def close(self):
+        if self._h:
+            _capi.lib().prichs_moe_destroy(self._h)
+            self._h = C.c_void_p()
+            self._max_tokens = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- forward ----------------------------------------------------------------------------------
+    @staticmethod
+    def _cb(concept_bias):
+        if concept_bias is None:
+            return None, 0, None
+        cb = np.ascontiguousarray(concept_bias, np.float32).reshape(-1)
+        return cb.ctypes.data_as(C.POINTER(C.c_float)), cb.size, cb  # cb kept alive by the caller's tuple
+
+    def forward_with_memory(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, residual=None, out=None,
+                            stream=None):
+        """y = MoE(x) (+ residual when given: the caller's add of block.rs:67, fused)."""
+        cbt = self._cb(starkdb_concept_bias)
+        cb_ptr, cb_n = cbt[0], cbt[1]
+        L = _capi.lib()
+        if isinstance(x, np.ndarray):
+            if x.ndim != 2 or x.shape[1] != self.hidden_dim:
+                raise PrichsError(_capi.ERR_BAD_SHAPE, f"Incompatible shapes for matmul: {list(x.shape)} x [{self.hidden_dim}, ...]")
+            xh = np.ascontiguousarray(x, np.float32)
+            T = xh.shape[0]
+            self._ensure(T)
+            y = out if out is not None else np.empty((T, self.hidden_dim), np.float32)
+            rp = None
+            if residual is not None:
+                rh = np.ascontiguousarray(residual, np.float32)
+                if rh.shape != xh.shape:
+                    raise PrichsError(_capi.ERR_BAD_SHAPE, "Tensor length mismatch in addition")
+                rp = rh.ctypes.data
+            _check(L.prichs_moe_forward_host(self._h, xh.ctypes.data, rp, cb_ptr, cb_n, y.ctypes.data, T))
+            self._T_last = T
+            return y
+        import torch  # device path: torch is only the owner of the caller's device memory and stream
+        if not (isinstance(x, torch.Tensor) and x.is_cuda):
+            raise PrichsError(_capi.ERR_BAD_ARG, "x must be a numpy float32 array or a CUDA torch tensor")
+        if x.dim() != 2 or x.shape[1] != self.hidden_dim:
+            raise PrichsError(_capi.ERR_BAD_SHAPE, f"Incompatible shapes for matmul: {list(x.shape)} x [{self.hidden_dim}, ...]")
+        dt = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}.get(x.dtype)
+        if dt is None:
+            raise PrichsError(_capi.ERR_BAD_ARG, "x must be float32 or bfloat16")
+        x = x.contiguous()
+        T = x.shape[0]
+        if self._device < 0:
+            self._device = x.device.index
+        self._ensure(T)
+        y = out if out is not None else torch.empty_like(x)
+        ydt = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}[y.dtype]
+        rp = None
+        if residual is not None:
+            if residual.shape != x.shape or residual.dtype != x.dtype:
+                raise PrichsError(_capi.ERR_BAD_SHAPE, "Tensor length mismatch in addition")
+            residual = residual.contiguous()
+            rp = residual.data_ptr()
+        st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
+        _check(L.prichs_moe_forward(self._h, x.data_ptr(), dt, rp, cb_ptr, cb_n, y.data_ptr(), ydt, T, st))
+        self._T_last = T
+        return y
+
+    def forward(self, x, **kw):
+        return self.forward_with_memory(x, None, **kw)
+
+    def forward_train(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, **kw):
+        out = self.forward_with_memory(x, starkdb_concept_bias, **kw)
+        return out, self.last_stash()
+
+    def last_stash(self) -> MoEStash:
+        """Routing results of the last forward (waits for its stream)."""
+        L = _capi.lib()
+        cnt = self.last_counts()
+        T = self._T_last
+        E, k = self._num_experts, self.top_k
+        lo = np.empty((T, E), np.float32)
+        sel = np.empty((T, k), np.int32)
+        gw = np.empty((T, k), np.float32)
+        if T:
+            _check(L.prichs_moe_get_routing(self._h, lo.ctypes.data_as(C.POINTER(C.c_float)),
+                                            sel.ctypes.data_as(C.POINTER(C.c_int32)),
+                                            gw.ctypes.data_as(C.POINTER(C.c_float)), T))
+        return MoEStash(lo, sel.astype(np.int64).reshape(-1), gw.reshape(-1), cnt)
+
+    def last_counts(self) -> np.ndarray:
+        c = np.zeros(self._num_experts, np.int64)
+        if self._h:
+            _check(_capi.lib().prichs_moe_get_counts(self._h, c.ctypes.data_as(C.POINTER(C.c_int64)), c.size))
+        return c
+
+    def debug_buffer(self, which: int, nbytes: int, offset: int = 0) -> np.ndarray:
+        """Raw bytes of one internal buffer of the last forward (see prichs_moe_debug_copy in the header)."""
+        out = np.empty(nbytes, np.uint8)
+        _check(_capi.lib().prichs_moe_debug_copy(self._h, which, offset, out.ctypes.data, nbytes))
+        return out
+
+    @property
+    def token_capacity(self) -> int:
+        """max_tokens of the device handle (0 before the first forward)."""
+        return self._max_tokens
+
+    def sync_status(self):
+        if self._h:
+            _check(_capi.lib().prichs_moe_sync_status(self._h))
+
+    # ---- aux-loss-free load balancing ---------------------------------------------------------------
+    def update_aux_free_bias(self, expert_token_counts: Sequence[int], total_tokens: int, gamma: float):
+        counts = np.ascontiguousarray(expert_token_counts, np.uintp)
+        if counts.size != self._num_experts:
+            raise PrichsError(_capi.ERR_BAD_SHAPE, "expert_token_counts length differs from the number of experts")
+        self._ensure(1)
+        _check(_capi.lib().prichs_moe_update_aux_free_bias(self._h, counts.ctypes.data_as(C.POINTER(C.c_size_t)),
+                                                           counts.size, int(total_tokens), C.c_float(gamma)))
+
+    def update_bias_from_last(self, gamma: float, total_tokens: int = 0, stream=None):
+        """Device-side variant: uses the counts of the last forward without a host round trip."""
+        if not self._h:
+            return
+        _check(_capi.lib().prichs_moe_update_bias_from_last(self._h, C.c_float(gamma), int(total_tokens), stream))
