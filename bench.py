@@ -164,6 +164,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override T (profiling of a small case only; the line is then not the baseline's config)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -189,7 +191,7 @@ def main():
     L = _capi.lib()
 
     if n_gpus == 1:
-        seed, T = 1, 16384
+        seed, T = 1, (args.tokens or 16384)
         ws = synth.layer_weights(seed, D, F, E, bf16=True)
         bias = synth.router_bias(seed, E, -0.1, 0.1)
         layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank)
@@ -285,7 +287,8 @@ def main():
     line = {
         "metric": "MoE-layer tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(n_gpus),
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(n_gpus) if not args.tokens else {"workload": f"NOT the baseline config: T={T} override for profiling"},
         "e2e": {"value": tokens * e2e_steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 4,
                 "d2h_bytes_per_step": T * D * 4, "steps": e2e_steps,
                 "api": "MoELayer.forward(numpy fp32 [T,d]) -> prichs_moe_forward_host, pinned host buffers"},
