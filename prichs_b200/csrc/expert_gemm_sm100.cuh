@@ -20,6 +20,11 @@
 // 128 * (routed_base_tiles + j), a base that does not depend on T (peers of an expert-parallel group
 // address each other's buffers with it).
 //
+// Epilogue data path: TMEM -> registers (tcgen05.ld, 32 columns at a time) -> a per-warp 32-row x 128-byte
+// staging box in shared memory (128-byte swizzle, conflict-free 16-byte stores) -> TMA tiled store. Each warp
+// owns two boxes and alternates, so the store of one box overlaps the conversion of the next; global memory
+// sees full 128-byte row segments instead of 16-byte pieces.
+//
 // Epilogues:
 //   EPI_SWIGLU  B rows of a tile are [128 gate columns | 128 up columns] of the same 128 hidden units, so one
 //               thread owns matching g and u: h = silu(g) * u, written as bf16 (optionally as a bf16 hi/lo
@@ -46,8 +51,11 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-// dynamic shared memory: stages (1024-byte aligned) + barriers + TMEM base + abort flag
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_WARPS = 4;
+constexpr int BOX_BYTES = 32 * 128;                      // one staging box: 32 rows x 128 bytes
+constexpr int STAGING_BYTES = EPI_WARPS * 2 * BOX_BYTES;  // two boxes per epilogue warp
+// dynamic shared memory: stages (1024-byte aligned) + staging boxes + barriers + TMEM base + abort flag
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
 // Every wait gives up after this many clock cycles (~2 s at 1.9 GHz) and the kernel reports a timeout.
 constexpr long long WAIT_CYCLES = 4000000000LL;
 
@@ -66,9 +74,7 @@ struct Args {
     int w_rows;                // B rows per weight slot
     int out_split;             // SwiGLU only: also write the bf16 residual (lo) at column offset `out_lo_off`
     int out_lo_off;
-    int out_f32;               // plain only: write fp32 instead of bf16
-    void* out;                 // row-major output
-    long long ldo;             // leading dimension of out, in elements
+    int out_f32;               // plain only: the output tensor map is fp32 (32-column boxes) instead of bf16
     int* status;               // device status word; set to -5 on a bounded-wait timeout
 };
 
@@ -85,11 +91,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid_constant__ CUtensorMap tm_a_routed,
-                   const __grid_constant__ CUtensorMap tm_b, const Args args) {
+                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_out,
+                   const Args args) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle atoms.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* staging = smem + STAGES * STAGE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full = empty_bar + STAGES;
     uint64_t* tmem_empty = tmem_full + 2;
@@ -223,6 +231,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
     } else {
         // ---------------------------------------------------------------- epilogue warps
         const int quarter = warp & 3;  // TMEM lanes [32 q, 32 q + 32) are the ones this warp may read
+        uint8_t* box0 = staging + (warp - 2) * 2 * BOX_BYTES;
+        uint8_t* my_row = box0 + lane * 128;      // this lane's row inside box 0 (box 1 is BOX_BYTES further)
+        const int sw = lane & 7;                  // 128-byte swizzle: 16-byte chunk j of row r sits at j ^ (r & 7)
+        if (lane == 0) ptx::prefetch_tmap(&tm_out);
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -234,9 +246,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
             const int ut = mt < args.shared_mtiles ? mt : args.routed_base_tiles + mt - args.shared_mtiles;
-            const long long row = (long long)ut * BM + quarter * 32 + lane;
+            const int row0 = ut * BM + quarter * 32;  // first output row of this warp's boxes
             if constexpr (EPI == EPI_SWIGLU) {
-                __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(args.out) + row * args.ldo + (long long)nt * 128;
 #pragma unroll 1
                 for (int c = 0; c < 128; c += 32) {
                     uint32_t g[32], u[32];
@@ -249,6 +260,15 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
                     }
+                    const int sub = (c >> 5) & 1;                      // which half of the 64-column box
+                    const int buf = args.out_split ? 0 : (c >> 6) & 1; // split mode: box 0 = hi, box 1 = lo
+                    if (sub == 0) {
+                        // the box is free once the store that last read it has fetched its data
+                        if (lane == 0) {
+                            if (args.out_split) ptx::bulk_wait_read<0>(); else ptx::bulk_wait_read<1>();
+                        }
+                        __syncwarp();
+                    }
                     uint32_t hi[16], lo[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -256,18 +276,26 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         const float h1 = silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]));
                         const __nv_bfloat162 hb = __floats2bfloat162_rn(h0, h1);
                         hi[j] = *reinterpret_cast<const uint32_t*>(&hb);
-                        if (args.out_split) {
-                            lo[j] = pack_bf16(h0 - __low2float(hb), h1 - __high2float(hb));
-                        }
+                        if (args.out_split) lo[j] = pack_bf16(h0 - __low2float(hb), h1 - __high2float(hb));
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
-                    if (args.out_split) {
-                        uint4* dlo = reinterpret_cast<uint4*>(orow + args.out_lo_off + c);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            dlo[j] = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = ((sub * 4 + j) ^ sw) << 4;
+                        *reinterpret_cast<uint4*>(my_row + buf * BOX_BYTES + chunk) =
+                            make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+                        if (args.out_split)
+                            *reinterpret_cast<uint4*>(my_row + BOX_BYTES + chunk) =
+                                make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+                    }
+                    if (sub == 1) {
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int col = nt * 128 + (c >> 6) * 64;
+                            ptx::tma_store_2d(&tm_out, col, row0, box0 + buf * BOX_BYTES);
+                            if (args.out_split) ptx::tma_store_2d(&tm_out, args.out_lo_off + col, row0, box0 + BOX_BYTES);
+                            ptx::bulk_commit();
+                        }
                     }
                 }
             } else {
@@ -282,20 +310,42 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
                     }
                     if (args.out_f32) {
-                        float* orow = reinterpret_cast<float*>(args.out) + row * args.ldo + (long long)nt * BN + c;
-                        uint4* dst = reinterpret_cast<uint4*>(orow);
+                        // 32 fp32 columns fill one 128-byte box row
+                        const int buf = (c >> 5) & 1;
+                        if (lane == 0) ptx::bulk_wait_read<1>();
+                        __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) dst[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4*>(my_row + buf * BOX_BYTES + ((j ^ sw) << 4)) =
+                                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_2d(&tm_out, nt * BN + c, row0, box0 + buf * BOX_BYTES);
+                            ptx::bulk_commit();
+                        }
                     } else {
-                        __nv_bfloat16* orow =
-                            reinterpret_cast<__nv_bfloat16*>(args.out) + row * args.ldo + (long long)nt * BN + c;
+                        const int sub = (c >> 5) & 1, buf = (c >> 6) & 1;
+                        if (sub == 0) {
+                            if (lane == 0) ptx::bulk_wait_read<1>();
+                            __syncwarp();
+                        }
                         uint32_t p[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             p[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                        uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(my_row + buf * BOX_BYTES + (((sub * 4 + j) ^ sw) << 4)) =
+                                make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+                        if (sub == 1) {
+                            ptx::fence_proxy_async();
+                            __syncwarp();
+                            if (lane == 0) {
+                                ptx::tma_store_2d(&tm_out, nt * BN + (c >> 6) * 64, row0, box0 + buf * BOX_BYTES);
+                                ptx::bulk_commit();
+                            }
+                        }
                     }
                 }
             }
@@ -304,6 +354,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                 acc_phase ^= 1;
             }
         }
+        // the stores read shared memory of this CTA and write global memory: both must be finished before exit
+        if (lane == 0) ptx::bulk_wait_all();
     }
 
     ptx::tc_fence_before();

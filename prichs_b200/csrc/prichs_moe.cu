@@ -68,17 +68,20 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// Row-major bf16 matrix [rows, cols] -> tensor map with a (64 x box_rows) box and the 128-byte swizzle.
-int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int box_rows) {
+// Row-major matrix [rows, cols] of bf16 (or fp32) -> tensor map whose box is 128 bytes wide (64 bf16 or 32
+// fp32 elements) and box_rows tall, with the 128-byte swizzle.
+int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int box_rows, bool f32 = false) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(PRICHS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * 2) % 16 != 0)
+    const size_t esz = f32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * esz) % 16 != 0)
         return fail(PRICHS_ERR_BAD_ARG, "tensor map base and row pitch must be 16-byte aligned");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)egemm::BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(cols * esz)};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(PRICHS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -197,6 +200,7 @@ struct prichs_moe {
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
     route::RouteMeta* meta;
     CUtensorMap tm_xp, tm_wgu, tm_h, tm_wdn;
+    CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
 
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
@@ -328,6 +332,8 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(make_tmap(&h->tm_wgu, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, egemm::BN));
     A(make_tmap(&h->tm_h, h->hbuf, rows_all, h->K2, egemm::BM));
     A(make_tmap(&h->tm_wdn, h->w_dn, (size_t)h->n_slots * d, h->K2, egemm::BN));
+    A(make_tmap(&h->tm_h_out, h->hbuf, rows_all, h->K2, 32));
+    A(make_tmap(&h->tm_y_out, h->ybuf, rows_all, d, 32, h->mode == PRICHS_MODE_F32));
     if (rc == PRICHS_OK) {
         if (cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess)
@@ -474,17 +480,18 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
                                                         h->logits, h->sel, h->gates, h->tile_counts);
     } else {
-        const int grid = (ntiles + 1) / 2;
+        const int grid = ntiles;
+        constexpr int RT = route::ROUTER_WARPS * 32;
         if (x_dtype == PRICHS_DTYPE_F32) {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, true><<<grid, 64, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<1, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
             else
-                route::router_mma_kernel<3, true><<<grid, 64, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<3, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
         } else {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, false><<<grid, 64, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<1, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
             else
-                route::router_mma_kernel<3, false><<<grid, 64, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<3, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
         }
     }
     LAUNCH_CHECK("router");
@@ -517,10 +524,8 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     a1.out_split = f32mode;
     a1.out_lo_off = f;
     a1.out_f32 = 0;
-    a1.out = h->hbuf;
-    a1.ldo = h->K2;
     a1.status = h->status;
-    egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, a1);
+    egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
     LAUNCH_CHECK("gate/up GEMM");
     mark();
     // 5. down GEMM
@@ -531,9 +536,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     a2.w_rows = d;
     a2.out_split = 0;
     a2.out_f32 = f32mode;
-    a2.out = h->ybuf;
-    a2.ldo = d;
-    egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, a2);
+    egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
     LAUNCH_CHECK("down GEMM");
     mark();
     // 6. combine (+ residual)
@@ -759,3 +762,4 @@ void launch_swiglu_forward(const float* dev_gate, const float* dev_up, float* de
 }
 
 }  // extern "C"
+

@@ -124,25 +124,30 @@ __device__ __forceinline__ void route_finish(const float (&L)[MAX_E], bool activ
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Router for bf16 operands. One warp owns a tile of 16 tokens and computes their 8 logits with
-// mma.sync m16n8k16 (N = 8 is exactly the expert count): lane (g = lane/4, q = lane%4) reads 16 contiguous
-// bytes of token row g (and g+8) and 16 contiguous bytes of row g of the transposed router weight. The
-// dot product does not care in which order k is visited, so those 8 consecutive elements are fed to two
-// MMAs as the fragment slots (2q, 2q+1, 2q+8, 2q+9) of A and B alike -- every global access is a full
-// 16-byte vector and no shared memory is needed.
+// Router for bf16 operands. One CTA of 8 warps owns a tile of 16 tokens; the warps split K between them
+// (warp w takes the 32-element slices w, w+8, w+16, ... so that the CTA reads 512 contiguous bytes of every
+// row per step) and each computes partial logits with mma.sync m16n8k16 (N = 8 is exactly the expert count):
+// lane (g = lane/4, q = lane%4) reads 16 contiguous bytes of token row g (and g+8) and 16 contiguous bytes of
+// row g of the transposed router weight. The dot product does not care in which order k is visited, so those
+// 8 consecutive elements are fed to two MMAs as the fragment slots (2q, 2q+1, 2q+8, 2q+9) of A and B alike --
+// every global access is a full 16-byte vector. The partial sums meet in shared memory and warp 0 adds them
+// in a fixed order, then selects. With T/16 CTAs of 8 warps the whole batch is in flight at once, which is
+// what an HBM-bound kernel with ~3 KB per token needs.
 // wrt: [NSPLIT][8][d] bf16; NSPLIT = 3 holds hi/mid/lo parts of fp32 router weights (their sum is exact to
 // 2^-24), NSPLIT = 1 is used when the weights are bf16 values already.
 // XF32: x is fp32 [T,d]; it is rounded to bf16 (RNE) for the product and the bf16 copy is written to `xs`
 // for the expert GEMMs (saves a separate conversion pass).
+constexpr int ROUTER_WARPS = 8;
+
 template <int NSPLIT, bool XF32>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ wrt,
                   const float* __restrict__ bias, const ConceptBias cb, int T, int d, int E, int top_k,
                   float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
                   int* __restrict__ tile_counts) {
+    __shared__ float4 partial[ROUTER_WARPS][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x * 2 + warp;
-    if (tile * TILE_TOKENS >= T) return;
+    const int tile = blockIdx.x;
     const int g = lane >> 2, q = lane & 3;
     const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
     const size_t r0c = (size_t)min(r0, T - 1), r1c = (size_t)min(r1, T - 1);
@@ -158,8 +163,8 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
     const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
     const size_t wsplit = (size_t)MAX_E * d;
 
-#pragma unroll 4
-    for (int kk = 0; kk < d; kk += 32) {
+#pragma unroll 6
+    for (int kk = warp * 32; kk < d; kk += ROUTER_WARPS * 32) {
         uint4 a0, a1;
         if (XF32) {
             const float* x0 = reinterpret_cast<const float*>(x) + r0c * d + kk + 8 * q;
@@ -194,6 +199,14 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
 #pragma unroll
         for (int s = NSPLIT - 1; s >= 0; --s) v += acc[s][0][i] + acc[s][1][i];
         c[i] = v;
+    }
+    partial[warp][lane] = make_float4(c[0], c[1], c[2], c[3]);
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 1; w < ROUTER_WARPS; ++w) {
+        const float4 p = partial[w][lane];
+        c[0] += p.x; c[1] += p.y; c[2] += p.z; c[3] += p.w;
     }
     // lanes q = 0 / q = 1 of each quad take row g / g + 8; gather the row's 8 logits from the quad
     float L[MAX_E];
