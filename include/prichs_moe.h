@@ -174,6 +174,34 @@ PRICHS_API int prichs_moe_get_stage_ms(prichs_moe_t* h, float* ms6);
  *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 128. */
 PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes);
 
+/* ---- routing without any allocation ---------------------------------------------------------------
+ * This entry point has no counterpart in the reference. It exists for callers that are not allowed to
+ * allocate device memory at the point where they need routing decisions -- a plugin running inside a host
+ * application that owns the whole memory pool, a real-time loop that must not enter the allocator, a hook
+ * invoked where cudaMalloc would synchronise the device. Such callers cannot create a handle (create
+ * allocates), so they get the router stage on its own: logits, top-k experts, gates and per-expert counts for
+ * one batch, computed with the same kernels as prichs_moe_forward.
+ *
+ * Every intermediate (transposed router weights, per-tile histograms, prefix sums, packed selections) lives in
+ * ONE fixed 1 MiB array that is part of the library image on each GPU that loads it and stays there until the
+ * process exits. The call performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ *   x_dev        [T,d] bf16, device          router_dev   [d,E] fp32, device (the reference's layout)
+ *   bias_dev     [E] fp32 device, or null for a zero bias
+ *   outputs (device, caller-owned): logits_dev [T,E] fp32, selected_dev [T,top_k] int32,
+ *   gating_dev [T,top_k] fp32, counts_dev [E] int32
+ * Limits: T <= PRICHS_ROUTE_STATIC_MAX_TOKENS, d <= PRICHS_ROUTE_STATIC_MAX_HIDDEN (d a multiple of 256),
+ * E <= 8, top_k <= 2; anything larger returns PRICHS_ERR_CAPACITY and does nothing.
+ * The first call on a device looks up the array's device address (once per device, with that device
+ * current); make that first call before starting any stream capture. All calls on a device share the array
+ * and it keeps the previous call's contents (what must start at zero is cleared on `stream` by the call
+ * itself): two calls whose work overlaps on the GPU -- different streams, no ordering between them -- race on
+ * it. Order them on one stream or with events. */
+#define PRICHS_ROUTE_STATIC_MAX_TOKENS 16384
+#define PRICHS_ROUTE_STATIC_MAX_HIDDEN 2048
+PRICHS_API int prichs_moe_route_static(const void* x_dev, const float* router_dev, const float* bias_dev, int T, int d,
+                                       int E, int top_k, float* logits_dev, int32_t* selected_dev, float* gating_dev,
+                                       int32_t* counts_dev, void* stream);
+
 /* ---- stand-alone kernels with the reference's signatures ----------------------------------------- */
 
 /* Same symbols, arguments and semantics as the reference's wrappers, so engine.rs links unchanged:

@@ -763,3 +763,114 @@ void launch_swiglu_forward(const float* dev_gate, const float* dev_up, float* de
 
 }  // extern "C"
 
+// =====================================================================================================
+// Routing without allocation (prichs_moe_route_static). Scratch lives in a file-scope device array; host
+// code never uses the symbol as a pointer -- it asks the runtime for the device address once per device.
+namespace {
+
+constexpr size_t RS_MAX_T = PRICHS_ROUTE_STATIC_MAX_TOKENS;
+constexpr size_t RS_MAX_D = PRICHS_ROUTE_STATIC_MAX_HIDDEN;
+constexpr size_t RS_MAX_TILES = RS_MAX_T / route::TILE_TOKENS;
+// byte offsets inside the scratch array (all multiples of 256)
+constexpr size_t RS_OFF_WRT = 0;                                                   // [3][8][d] bf16
+constexpr size_t RS_OFF_WR8 = RS_OFF_WRT + 3 * route::MAX_E * RS_MAX_D * 2;        // [d][8] fp32
+constexpr size_t RS_OFF_BIAS0 = RS_OFF_WR8 + RS_MAX_D * route::MAX_E * 4;          // 8 zeros
+constexpr size_t RS_OFF_LOGITS = RS_OFF_BIAS0 + 256;                               // [T][8] fp32
+constexpr size_t RS_OFF_SEL = RS_OFF_LOGITS + RS_MAX_T * route::MAX_E * 4;         // [T][2] packed int32
+constexpr size_t RS_OFF_GATES = RS_OFF_SEL + RS_MAX_T * 2 * 4;                     // [T][2] fp32
+constexpr size_t RS_OFF_TCOUNT = RS_OFF_GATES + RS_MAX_T * 2 * 4;                  // [tiles][8] int32
+constexpr size_t RS_OFF_TPREFIX = RS_OFF_TCOUNT + RS_MAX_TILES * route::MAX_E * 4; // [tiles][8] int32
+constexpr size_t RS_OFF_META = RS_OFF_TPREFIX + RS_MAX_TILES * route::MAX_E * 4;   // RouteMeta
+constexpr size_t RS_OFF_SLOTS = RS_OFF_META + 512;                                 // m-tile table
+constexpr size_t RS_OFF_STATUS = RS_OFF_SLOTS + 2048;                              // status word
+constexpr size_t RS_BYTES = 1u << 20;
+static_assert(RS_OFF_STATUS + 256 <= RS_BYTES, "scratch layout exceeds the static array");
+static_assert(sizeof(route::RouteMeta) <= 512, "RouteMeta outgrew its slot");
+static_assert((RS_MAX_T * 2 + route::MAX_E * 128) / 128 + 1 <= 2048 / 4, "m-tile table outgrew its slot");
+
+static __device__ __align__(256) unsigned char g_route_scratch[RS_BYTES];
+
+// Unpacks the router's internal layouts into the caller's arrays.
+__global__ void route_static_export_kernel(const float* __restrict__ logits8, const int* __restrict__ sel2,
+                                           const float* __restrict__ gates2, const route::RouteMeta* __restrict__ meta,
+                                           int T, int E, int top_k, float* __restrict__ logits, int32_t* __restrict__ selected,
+                                           float* __restrict__ gating, int32_t* __restrict__ counts) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < E) counts[t] = meta->counts[t];
+    if (t >= T) return;
+    for (int e = 0; e < E; ++e) logits[(size_t)t * E + e] = logits8[(size_t)t * route::MAX_E + e];
+    for (int j = 0; j < top_k; ++j) {
+        selected[(size_t)t * top_k + j] = sel2[(size_t)t * 2 + j] & 0xff;
+        gating[(size_t)t * top_k + j] = gates2[(size_t)t * 2 + j];
+    }
+}
+
+// Device address of the scratch array on the current device, resolved once per device.
+int route_scratch_base(unsigned char** out) {
+    constexpr int MAX_DEV = 64;
+    static unsigned char* base[MAX_DEV] = {nullptr};
+    static std::atomic<int> ready[MAX_DEV];
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEV) return fail(PRICHS_ERR_BAD_ARG, "device ordinal %d is out of range", dev);
+    if (!ready[dev].load(std::memory_order_acquire)) {
+        unsigned char* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch));
+        base[dev] = p;
+        ready[dev].store(1, std::memory_order_release);
+    }
+    *out = base[dev];
+    return PRICHS_OK;
+}
+
+}  // namespace
+
+extern "C" int prichs_moe_route_static(const void* x_dev, const float* router_dev, const float* bias_dev, int T, int d,
+                                       int E, int top_k, float* logits_dev, int32_t* selected_dev, float* gating_dev,
+                                       int32_t* counts_dev, void* stream_) {
+    if (!x_dev || !router_dev || !logits_dev || !selected_dev || !gating_dev || !counts_dev)
+        return fail(PRICHS_ERR_BAD_ARG, "null device pointer");
+    if (T < 1 || d < 256 || d % 256 != 0) return fail(PRICHS_ERR_BAD_SHAPE, "T must be positive and d a positive multiple of 256");
+    if (E < 1 || E > route::MAX_E || top_k < 1 || top_k > 2 || top_k > E)
+        return fail(PRICHS_ERR_BAD_SHAPE, "num_experts must be in 1..8 and top_k in 1..min(2, num_experts)");
+    if ((size_t)T > RS_MAX_T || (size_t)d > RS_MAX_D)
+        return fail(PRICHS_ERR_CAPACITY, "T=%d, d=%d exceed the static scratch limits (T <= %zu, d <= %zu)", T, d, RS_MAX_T, RS_MAX_D);
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(PRICHS_ERR_BAD_ARG, "x must be 16-byte aligned");
+    unsigned char* sc = nullptr;
+    int rc = route_scratch_base(&sc);
+    if (rc != PRICHS_OK) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+
+    bf16* wrt = reinterpret_cast<bf16*>(sc + RS_OFF_WRT);
+    float* wr8 = reinterpret_cast<float*>(sc + RS_OFF_WR8);
+    float* bias0 = reinterpret_cast<float*>(sc + RS_OFF_BIAS0);
+    float* logits8 = reinterpret_cast<float*>(sc + RS_OFF_LOGITS);
+    int* sel2 = reinterpret_cast<int*>(sc + RS_OFF_SEL);
+    float* gates2 = reinterpret_cast<float*>(sc + RS_OFF_GATES);
+    int* tcount = reinterpret_cast<int*>(sc + RS_OFF_TCOUNT);
+    int* tprefix = reinterpret_cast<int*>(sc + RS_OFF_TPREFIX);
+    route::RouteMeta* meta = reinterpret_cast<route::RouteMeta*>(sc + RS_OFF_META);
+    int* slots = reinterpret_cast<int*>(sc + RS_OFF_SLOTS);
+    int* status = reinterpret_cast<int*>(sc + RS_OFF_STATUS);
+
+    // the zero-bias block and the status word must start at zero; everything else is overwritten before use
+    CUDA_TRY(cudaMemsetAsync(bias0, 0, 256, st));
+    CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
+    if (bias_dev) CUDA_TRY(cudaMemcpyAsync(bias0, bias_dev, (size_t)E * sizeof(float), cudaMemcpyDeviceToDevice, st));
+
+    repack_router_kernel<<<64, 256, 0, st>>>(router_dev, wrt, wr8, d, E);
+    LAUNCH_CHECK("router repack");
+    route::ConceptBias cb;
+    for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = 0.0f;
+    const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    route::router_mma_kernel<3, false><<<ntiles, route::ROUTER_WARPS * 32, 0, st>>>(x_dev, nullptr, wrt, bias0, cb, T, d, E, top_k, logits8, sel2,
+                                                                        gates2, tcount);
+    LAUNCH_CHECK("router");
+    const int cap_rows = (int)((RS_MAX_T * 2 + route::MAX_E * 128) / 128 * 128);
+    route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, E, E, 1, 0, cap_rows, 1, status);
+    LAUNCH_CHECK("scan");
+    route_static_export_kernel<<<(T + 255) / 256, 256, 0, st>>>(logits8, sel2, gates2, meta, T, E, top_k, logits_dev, selected_dev,
+                                                               gating_dev, counts_dev);
+    LAUNCH_CHECK("export");
+    return PRICHS_OK;
+}
