@@ -196,11 +196,20 @@ def main():
         bias = synth.router_bias(seed, E, -0.1, 0.1)
         layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank)
     else:
-        raise SystemExit("expert-parallel benchmark is not available in this build")
+        from prichs_b200 import ep
+        seed, T = 3, (args.tokens or 32768)
+        ws = synth.layer_weights(seed, D, F, E, bf16=True)
+        bias = np.zeros(E, np.float32)
+        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank)
+        for e in range(E):  # only the experts this rank owns are uploaded
+            if e // (E // world) != rank:
+                layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
+        ep.connect(layer, dist, max_tokens=T)
     layer.router_bias = bias
 
-    nbatch = 4
-    xs_host = [synth.tokens(seed * 1000 + i if i else seed, T, D, bf16=True) for i in range(nbatch)]
+    nbatch = 4 if n_gpus == 1 else 2
+    xseed = seed if n_gpus == 1 else seed * 1000 + rank  # config 3: per-rank token seed 3000 + rank
+    xs_host = [synth.tokens(xseed + 7919 * i, T, D, bf16=True) for i in range(nbatch)]
     xs = [torch.from_numpy(synth.to_bf16_bits(x).view(np.int16)).view(torch.bfloat16).to(dev) for x in xs_host]
     y = torch.empty_like(xs[0])
     stream = torch.cuda.current_stream(dev)
@@ -264,8 +273,16 @@ def main():
 
     names = ["router", "scan", "dispatch", "gate_up_gemm", "down_gemm", "combine"]
     stage_ms = dict(zip(names, [float(v) for v in stage]))
-    gu_tf = T * GATE_UP_FLOPS_PER_TOKEN / (stage_ms["gate_up_gemm"] * 1e-3) / 1e12
-    dn_tf = T * DOWN_FLOPS_PER_TOKEN / (stage_ms["down_gemm"] * 1e-3) / 1e12
+    # rows the GEMMs of THIS rank processed: its T shared rows plus the routed rows its experts received
+    rows = T * (1 + K)
+    if world > 1:
+        import ctypes as C2
+        rr = C2.c_int64()
+        L.prichs_moe_ep_recv_rows(layer._h, C2.byref(rr))
+        rows = T + int(rr.value)
+    gu_flops = rows * 4 * D * F
+    gu_tf = gu_flops / (stage_ms["gate_up_gemm"] * 1e-3) / 1e12
+    dn_tf = rows * 2 * D * F / (stage_ms["down_gemm"] * 1e-3) / 1e12
     stages = {
         "router": {"ms": stage_ms["router"], "GB/s": T * ROUTER_BYTES / stage_ms["router"] / 1e6, "bound": "hbm"},
         "scan": {"ms": stage_ms["scan"]},
@@ -282,7 +299,7 @@ def main():
     roofline = {"kernel": "expert_gemm_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
                 "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
                 "traffic": None, "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
-                "algorithmic_flops_per_launch": T * GATE_UP_FLOPS_PER_TOKEN}
+                "algorithmic_flops_per_launch": gu_flops}
 
     line = {
         "metric": "MoE-layer tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
@@ -293,7 +310,7 @@ def main():
                 "d2h_bytes_per_step": T * D * 4, "steps": e2e_steps,
                 "api": "MoELayer.forward(numpy fp32 [T,d]) -> prichs_moe_forward_host, pinned host buffers"},
         "gpu_launches": launches, "roofline": roofline, "stages": stages,
-        "layer_tflops": T * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,
+        "layer_tflops": tokens * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,
         "clocks": clocks.summary(),
     }
     if rank == 0:

@@ -135,16 +135,31 @@ PRICHS_API int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* ex
                                     size_t total_tokens, float gamma);
 
 /* The same update taken from the counts of the last forward without leaving the device (enqueued on
- * `stream`). total_tokens == 0 means "the T of the last forward". In expert-parallel mode the counts and
- * total_tokens are the sums over all ranks, so every rank applies the identical update. */
+ * `stream`). total_tokens == 0 means "the T of the last forward". In expert-parallel mode the counts are the
+ * sums over all ranks and total_tokens must be the global token count too, so that every rank applies the
+ * identical update; 0 then stands for T of this rank times the number of ranks (right when all ranks pass
+ * the same T). */
 PRICHS_API int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_tokens, void* stream);
 
 /* ---- expert parallelism (no counterpart in the reference, which is single-GPU) --------------------- */
 
-/* Rank 0 fills a 128-byte id, the host passes it to every rank (any channel), then each rank calls init.
- * Experts are partitioned evenly; the shared expert, router and bias are replicated. */
+/* One process per GPU; rank r owns routed experts [r*E/G, (r+1)*E/G); the shared expert, router and bias are
+ * replicated; every rank routes its own tokens. The data path is inside the library's own kernels: the
+ * dispatch kernel writes each permuted row straight into the owner's receive buffer over NVLink (peer-mapped
+ * memory) and the combine kernel reads expert outputs straight from the owners' buffers, so no separate
+ * all-to-all copy exists. NCCL carries only the control plane: one 32-byte all-gather of the per-rank expert
+ * counts (placement plan + global counts for the bias update) and two token-sized all-gathers used as
+ * barriers (rows landed / outputs ready), all on the forward's stream.
+ * Set-up, with any host channel (MPI, torch.distributed, a file) moving the bytes:
+ *   1. rank 0: prichs_moe_ep_unique_id(id) and broadcast the 128 bytes;
+ *   2. every rank: prichs_moe_ep_export(h, blob) and all-gather the 128-byte blobs in rank order;
+ *   3. every rank: prichs_moe_ep_init(h, id, all_blobs)  (collective: creates the communicator, maps peers).
+ * All ranks must then call prichs_moe_forward in the same order. libnccl.so.2 is loaded at run time. */
+#define PRICHS_EP_ID_BYTES 128
+#define PRICHS_EP_BLOB_BYTES 128
 PRICHS_API int prichs_moe_ep_unique_id(void* id128);
-PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id128);
+PRICHS_API int prichs_moe_ep_export(prichs_moe_t* h, void* blob128);
+PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs);
 
 /* Rows this rank's experts received in the last forward (expert-parallel load), host value. */
 PRICHS_API int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows);

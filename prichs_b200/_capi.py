@@ -38,7 +38,8 @@ SYMBOLS = {
     "prichs_moe_update_aux_free_bias": (C.c_int, [C.c_void_p, C.POINTER(C.c_size_t), C.c_int, C.c_size_t, C.c_float]),
     "prichs_moe_update_bias_from_last": (C.c_int, [C.c_void_p, C.c_float, C.c_size_t, C.c_void_p]),
     "prichs_moe_ep_unique_id": (C.c_int, [C.c_void_p]),
-    "prichs_moe_ep_init": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "prichs_moe_ep_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "prichs_moe_ep_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "prichs_moe_ep_recv_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
     "prichs_last_error": (C.c_char_p, []),
     "prichs_kernel_launches": (C.c_int64, []),

@@ -17,6 +17,7 @@ SOURCES = ["prichs_moe.cu"]
 HEADERS = ["ptx_sm100.cuh", "expert_gemm_sm100.cuh", "route_sm100.cuh", "../../include/prichs_moe.h"]
 
 NVCC_FLAGS = [
+    "-ldl",
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]

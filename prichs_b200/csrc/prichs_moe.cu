@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <atomic>
 #include <cmath>
@@ -177,6 +178,48 @@ __global__ void compat_swiglu_kernel(const float* __restrict__ gate, const float
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// ---- NCCL, loaded at run time (control plane of the expert-parallel mode only) -------------------------
+// Only five entry points with a stable ABI are used; the library is opened by soname so that a process
+// that already carries an NCCL (for example through torch) shares it.
+struct NcclApi {
+    struct Id128 { char b[128]; };  // ncclUniqueId, passed by value
+    typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
+    typedef int (*CommDestroyFn)(void*);
+    typedef const char* (*GetErrorStringFn)(int);
+    int (*get_unique_id)(void*) = nullptr;
+    int (*comm_init_rank)(void**, int, Id128, int) = nullptr;
+    AllGatherFn all_gather = nullptr;
+    CommDestroyFn comm_destroy = nullptr;
+    GetErrorStringFn error_string = nullptr;
+    bool ok = false;
+};
+constexpr int NCCL_INT32 = 2;  // ncclInt32 in nccl.h
+
+NcclApi& nccl() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (lib) {
+            api.get_unique_id = reinterpret_cast<int (*)(void*)>(dlsym(lib, "ncclGetUniqueId"));
+            api.comm_init_rank = reinterpret_cast<int (*)(void**, int, NcclApi::Id128, int)>(dlsym(lib, "ncclCommInitRank"));
+            api.all_gather = reinterpret_cast<NcclApi::AllGatherFn>(dlsym(lib, "ncclAllGather"));
+            api.comm_destroy = reinterpret_cast<NcclApi::CommDestroyFn>(dlsym(lib, "ncclCommDestroy"));
+            api.error_string = reinterpret_cast<NcclApi::GetErrorStringFn>(dlsym(lib, "ncclGetErrorString"));
+            api.ok = api.get_unique_id && api.comm_init_rank && api.all_gather && api.comm_destroy && api.error_string;
+        }
+    }
+    return api;
+}
+
+#define NCCL_TRY(expr)                                                                                    \
+    do {                                                                                                  \
+        int r__ = (expr);                                                                                 \
+        if (r__ != 0) return fail(PRICHS_ERR_COMM, "%s failed: %s", #expr, nccl().error_string(r__));   \
+    } while (0)
+
 }  // namespace
 
 // =====================================================================================================
@@ -201,6 +244,13 @@ struct prichs_moe {
     route::RouteMeta* meta;
     CUtensorMap tm_xp, tm_wgu, tm_h, tm_wdn;
     CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
+
+    // expert-parallel group: communicator, peers' receive / output buffers mapped into this process
+    void* comm;
+    bool ep_ready;
+    void* xp_peer[route::MAX_RANKS];
+    void* y_peer[route::MAX_RANKS];
+    int* ep_token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers
 
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
@@ -318,6 +368,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
     A(dalloc(&h->status, 1));
     A(dalloc(&h->meta, 1));
+    A(dalloc(&h->ep_token, 2 * route::MAX_RANKS));
     if (rc != PRICHS_OK) {
         prichs_moe_destroy(h);
         return rc;
@@ -325,6 +376,11 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
     cudaMemset(h->status, 0, sizeof(int));
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
+    cudaMemset(h->ep_token, 0, 2 * route::MAX_RANKS * sizeof(int));
+    for (int i = 0; i < route::MAX_RANKS; ++i) {
+        h->xp_peer[i] = h->xp;
+        h->y_peer[i] = h->ybuf;
+    }
     cudaMemset(h->xp, 0, (size_t)h->Rcap * h->K1 * sizeof(bf16));
     cudaMemset(h->hbuf, 0, rows_all * h->K2 * sizeof(bf16));
 
@@ -354,7 +410,15 @@ int prichs_moe_destroy(prichs_moe_t* h) {
     if (!h) return PRICHS_OK;
     DeviceGuard guard(h->device);
     cudaDeviceSynchronize();
-    void* ptrs[] = {h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
+    if (h->ep_ready) {
+        for (int r = 0; r < h->world; ++r) {
+            if (r == h->rank) continue;
+            if (h->xp_peer[r]) cudaIpcCloseMemHandle(h->xp_peer[r]);
+            if (h->y_peer[r]) cudaIpcCloseMemHandle(h->y_peer[r]);
+        }
+        if (h->comm && nccl().ok) nccl().comm_destroy(h->comm);
+    }
+    void* ptrs[] = {h->ep_token, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
                     h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
                     h->stage_r, h->stage_y};
     for (void* p : ptrs)
@@ -446,11 +510,14 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     if (h->mode == PRICHS_MODE_F32 && x_dtype != PRICHS_DTYPE_F32)
         return fail(PRICHS_ERR_BAD_ARG, "the fp32-fidelity mode takes fp32 activations");
     if (n_concept < 0 || (n_concept > 0 && !concept_bias)) return fail(PRICHS_ERR_BAD_ARG, "concept bias length without data");
-    if (h->world > 1) return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not initialised");
+    if (h->world > 1 && !h->ep_ready) return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not initialised");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     h->last_stream = st;
     h->last_T = T;
-    if (T == 0) return PRICHS_OK;
+    if (T == 0) {
+        if (h->world > 1) return fail(PRICHS_ERR_BAD_SHAPE, "in expert-parallel mode every rank must pass at least one token");
+        return PRICHS_OK;
+    }
     if (!x_dev || !y_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation pointer");
     const size_t xalign = x_dtype == PRICHS_DTYPE_F32 ? 15 : 15;
     if ((reinterpret_cast<uintptr_t>(x_dev) & xalign) || (reinterpret_cast<uintptr_t>(y_dev) & 15) ||
@@ -497,17 +564,28 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     LAUNCH_CHECK("router");
     mark();
     // 2. prefix sums + placement plan
-    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0, h->Rcap, 1, h->status);
+    const bool ep = h->world > 1;
+    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, h->world, h->rank,
+                                           h->Rcap, ep ? 0 : 1, h->status);
     LAUNCH_CHECK("scan");
+    if (ep) {
+        // every rank contributes its 8 counts (row `rank` of the matrix, in place), then builds the same plan
+        int* cmat = h->meta->cmat;
+        NCCL_TRY(nccl().all_gather(cmat + h->rank * route::MAX_E, cmat, route::MAX_E, NCCL_INT32, h->comm, st));
+        route::plan_kernel<<<1, 256, 0, st>>>(h->meta, h->mtile_slot, E, h->El, h->world, h->rank, h->Rcap, h->status);
+        LAUNCH_CHECK("plan");
+    }
     mark();
     // 3. dispatch
     route::PeerPtrs xp_peers, y_peers;
     for (int i = 0; i < route::MAX_RANKS; ++i) {
-        xp_peers.p[i] = h->xp;
-        y_peers.p[i] = h->ybuf;
+        xp_peers.p[i] = h->xp_peer[i];
+        y_peers.p[i] = h->y_peer[i];
     }
     route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, h->sel, h->tile_prefix, h->meta, xp_peers, h->El, h->pos);
     LAUNCH_CHECK("dispatch");
+    // barrier: every rank's rows have landed in the owners' buffers before any expert GEMM reads them
+    if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + h->rank, h->ep_token, 1, NCCL_INT32, h->comm, st));
     mark();
     // 4. gate|up GEMM + SwiGLU for the shared and all routed experts
     egemm::Args a1;
@@ -539,6 +617,8 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
     LAUNCH_CHECK("down GEMM");
     mark();
+    // barrier: every owner's expert outputs are complete before the combine gathers them over NVLink
+    if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + route::MAX_RANKS + h->rank, h->ep_token + route::MAX_RANKS, 1, NCCL_INT32, h->comm, st));
     // 6. combine (+ residual)
     {
         const int grid = (T + 7) / 8;
@@ -680,13 +760,47 @@ int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_
 }
 
 int prichs_moe_ep_unique_id(void* id128) {
-    (void)id128;
-    return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not built into this library version");
+    if (!id128) return fail(PRICHS_ERR_BAD_ARG, "null id buffer");
+    if (!nccl().ok) return fail(PRICHS_ERR_COMM, "libnccl.so.2 could not be loaded");
+    NCCL_TRY(nccl().get_unique_id(id128));
+    return PRICHS_OK;
 }
-int prichs_moe_ep_init(prichs_moe_t* h, const void* id128) {
-    (void)h; (void)id128;
-    return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not built into this library version");
+
+int prichs_moe_ep_export(prichs_moe_t* h, void* blob128) {
+    if (!h || !blob128) return fail(PRICHS_ERR_BAD_ARG, "null handle or blob");
+    static_assert(2 * sizeof(cudaIpcMemHandle_t) <= PRICHS_EP_BLOB_BYTES, "two IPC handles must fit the blob");
+    DeviceGuard guard(h->device);
+    cudaIpcMemHandle_t hs[2];
+    CUDA_TRY(cudaIpcGetMemHandle(&hs[0], h->xp));
+    CUDA_TRY(cudaIpcGetMemHandle(&hs[1], h->ybuf));
+    memset(blob128, 0, PRICHS_EP_BLOB_BYTES);
+    memcpy(blob128, hs, sizeof(hs));
+    return PRICHS_OK;
 }
+
+int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs) {
+    if (!h || !id128 || !all_blobs) return fail(PRICHS_ERR_BAD_ARG, "null handle, id or blobs");
+    if (h->world < 2) return fail(PRICHS_ERR_BAD_ARG, "the handle was created with ep_world = 1");
+    if (h->ep_ready) return fail(PRICHS_ERR_BAD_ARG, "expert-parallel group is already initialised");
+    if (!nccl().ok) return fail(PRICHS_ERR_COMM, "libnccl.so.2 could not be loaded");
+    DeviceGuard guard(h->device);
+    for (int r = 0; r < h->world; ++r) {
+        if (r == h->rank) continue;
+        cudaIpcMemHandle_t hs[2];
+        memcpy(hs, static_cast<const char*>(all_blobs) + (size_t)r * PRICHS_EP_BLOB_BYTES, sizeof(hs));
+        void *pxp = nullptr, *py = nullptr;
+        CUDA_TRY(cudaIpcOpenMemHandle(&pxp, hs[0], cudaIpcMemLazyEnablePeerAccess));
+        CUDA_TRY(cudaIpcOpenMemHandle(&py, hs[1], cudaIpcMemLazyEnablePeerAccess));
+        h->xp_peer[r] = pxp;
+        h->y_peer[r] = py;
+    }
+    NcclApi::Id128 id;
+    memcpy(&id, id128, sizeof(id));
+    NCCL_TRY(nccl().comm_init_rank(&h->comm, h->world, id, h->rank));
+    h->ep_ready = true;
+    return PRICHS_OK;
+}
+
 int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows) {
     if (!h || !rows) return fail(PRICHS_ERR_BAD_ARG, "null handle or output");
     DeviceGuard guard(h->device);

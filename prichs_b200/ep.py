@@ -1,0 +1,69 @@
+"""Expert-parallel helpers on the host side.
+
+`plan` restates, in numpy, the placement plan the device computes from the all-gathered counts matrix
+(route::plan_from_cmat): where each expert's segment starts in its owner's receive buffer and where a given
+source rank's rows sit inside it. Tests use it to check the device plan; it is not on the data path.
+
+`connect` wires a group of MoELayer handles together using torch.distributed only as the byte channel that
+the C ABI asks for (broadcast of the 128-byte id, all-gather of the 128-byte buffer handles).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+
+
+def owner_of(expert: int, num_experts: int, world: int) -> int:
+    return expert // (num_experts // world)
+
+
+def plan(cmat: np.ndarray, rank: int):
+    """cmat[s, e] = assignments rank s produced for expert e. Returns total[e], src_off[e] (rows of lower ranks
+    ahead of `rank` inside expert e's segment), seg_base[e] (128-padded start of the segment in the owner's
+    buffer), recv_rows and n_mtiles of `rank`."""
+    cmat = np.asarray(cmat, np.int64)
+    world, E = cmat.shape
+    El = E // world
+    total = cmat.sum(axis=0)
+    src_off = cmat[:rank].sum(axis=0)
+    seg_base = np.zeros(E, np.int64)
+    padded = (total + 127) // 128 * 128
+    for o in range(world):
+        base = 0
+        for le in range(El):
+            e = o * El + le
+            seg_base[e] = base
+            base += padded[e]
+    mine = slice(rank * El, (rank + 1) * El)
+    return dict(total=total, src_off=src_off, seg_base=seg_base, recv_rows=int(total[mine].sum()),
+                n_mtiles=int(padded[mine].sum() // 128))
+
+
+def connect(layer, dist, max_tokens: int):
+    """Create the layer's device handle (for `max_tokens`) and join the expert-parallel group over `dist`
+    (an initialised torch.distributed module). Collective: every rank calls it."""
+    L = _capi.lib()
+    layer._want_max_tokens = max(layer._want_max_tokens, int(max_tokens))
+    layer._ensure(int(max_tokens))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ident = (C.c_char * 128)()
+    if rank == 0:
+        rc = L.prichs_moe_ep_unique_id(ident)
+        if rc != 0:
+            raise RuntimeError(_capi.last_error())
+    box = [bytes(ident)]
+    dist.broadcast_object_list(box, src=0)
+    blob = (C.c_char * 128)()
+    rc = L.prichs_moe_ep_export(layer._h, blob)
+    if rc != 0:
+        raise RuntimeError(_capi.last_error())
+    blobs = [None] * world
+    dist.all_gather_object(blobs, bytes(blob))
+    all_blobs = b"".join(blobs)
+    rc = L.prichs_moe_ep_init(layer._h, box[0], all_blobs)
+    if rc != 0:
+        raise RuntimeError(_capi.last_error())
+    layer._ep_connected = True

@@ -139,6 +139,8 @@ class MoELayer:
 
     def _ensure(self, T: int):
         L = _capi.lib()
+        if self._h and T > self._max_tokens and self._ep_world > 1:
+            raise PrichsError(_capi.ERR_CAPACITY, "an expert-parallel layer cannot grow past the max_tokens it was connected with")
         if not self._h or T > self._max_tokens:
             bias = self.router_bias if self._h else self._bias_host
             self.close()
@@ -150,15 +152,15 @@ class MoELayer:
             self._h, self._max_tokens, self._weights_dirty = h, cap, True
             _check(L.prichs_moe_set_bias(self._h, bias.ctypes.data_as(C.POINTER(C.c_float)), bias.size))
         if self._weights_dirty:
-            ws = [np.ascontiguousarray(w, np.float32) for w in self.parameter_list()]
+            ws = [None if w is None else np.ascontiguousarray(w, np.float32) for w in self.parameter_list()]
             shapes = [(self.hidden_dim, self._num_experts)] + [(self.hidden_dim, self.intermediate_dim)] * 2 + \
                      [(self.intermediate_dim, self.hidden_dim)]
             for i, w in enumerate(ws):
                 want = shapes[0] if i == 0 else shapes[1 + (i - 1) % 3]
-                if w.shape != want:
+                if w is not None and w.shape != want:
                     raise PrichsError(_capi.ERR_BAD_SHAPE, f"weight {i} has shape {w.shape}, expected {want}")
             fp = C.POINTER(C.c_float)
-            arr = (fp * len(ws))(*[w.ctypes.data_as(fp) for w in ws])
+            arr = (fp * len(ws))(*[fp() if w is None else w.ctypes.data_as(fp) for w in ws])
             _check(L.prichs_moe_upload_weights(self._h, arr, len(ws)))
             self._weights_dirty = False
 

@@ -1,0 +1,76 @@
+"""Expert-parallel parity worker, one process per GPU (launched by tests/test_gpu_ep.py through
+torch.distributed.run). Every rank routes its own seeded tokens, the experts are partitioned over the ranks,
+and each rank checks its outputs against the CPU oracle run on the full (unpartitioned) layer."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    from prichs_b200 import MoELayer, ep, synth
+    from oracle import oracle as O
+    from _util import assert_close
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cases = [(512, 384, 8, 2, 1000, (-0.1, 0.1)), (1536, 1280, 8, 2, 2048, None)]
+    for d, f, E, k, T, brange in cases:
+        Tr = T + 37 * rank  # ragged: every rank brings a different number of tokens
+        ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=True)
+        bias = synth.router_bias(3, E, *brange) if brange else np.zeros(E, np.float32)
+        x = synth.tokens(3000 + rank, Tr, d, bf16=True)
+        El = E // world
+        m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local)
+        for e in range(E):  # experts owned by other ranks are not uploaded here
+            if e // El != rank:
+                m.experts[e].gate_proj = m.experts[e].up_proj = m.experts[e].down_proj = None
+        m.router_bias = bias
+        ep.connect(m, dist, max_tokens=T + 37 * world)
+        xd = torch.from_numpy(synth.to_bf16_bits(x).view(np.int16)).view(torch.bfloat16).cuda()
+        for rep in range(2):  # twice: buffers are reused across calls
+            y = m.forward(xd).float().cpu().numpy()
+            m.sync_status()
+        st = m.last_stash()
+        given = O.route(None, ws[0], bias, k, logits=st.router_logits)
+        sel = st.selected_experts.reshape(Tr, k)
+        assert np.array_equal(sel, given["selected"]), "top-k differs from the oracle on the GPU's logits"
+        assert np.array_equal(st.expert_token_counts, given["counts"])
+        # device plan against the host restatement
+        cm = torch.tensor(st.expert_token_counts, device="cuda")
+        allc = [torch.zeros_like(cm) for _ in range(world)]
+        dist.all_gather(allc, cm)
+        cmat = np.stack([c.cpu().numpy() for c in allc])
+        hp = ep.plan(cmat, rank)
+        meta = m.debug_buffer(5, 4 * 100).view(np.int32)
+        assert np.array_equal(meta[8:16], hp["seg_base"]), (meta[8:16], hp["seg_base"])
+        assert np.array_equal(meta[16:24], hp["src_off"])
+        assert np.array_equal(meta[24:32], hp["total"])
+        assert meta[32] == hp["n_mtiles"] and meta[33] == hp["recv_rows"] and meta[34] == 0
+        assert np.array_equal(meta[36:36 + 8 * world].reshape(world, 8), cmat)
+        # outputs against the oracle of the whole layer on this rank's tokens
+        ref = O.moe_forward_train(ws, bias, k, x)
+        ok = np.all(ref["selected"] == sel, axis=1)
+        assert ok.mean() > 0.995
+        rep_ = assert_close(y[ok], ref["out"][ok], 2e-2, f"EP output rank {rank}")
+        # bias update from the global counts: identical on every rank, equal to the oracle's
+        total_tokens = sum(T + 37 * r for r in range(world))
+        m.update_bias_from_last(1e-3, total_tokens=total_tokens)  # ragged ranks: the global total is given
+        exp = O.update_aux_free_bias(bias, cmat.sum(axis=0), total_tokens, 1e-3, k)
+        assert np.array_equal(m.router_bias, exp)
+        print(f"EP_OK rank={rank} d={d} T={Tr} max_rel={rep_['max_rel']:.3e} recv_rows={hp['recv_rows']}", flush=True)
+        dist.barrier()
+        m.close()
+        dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
