@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -250,14 +251,19 @@ struct prichs_moe {
     bool ep_ready;
     void* xp_peer[route::MAX_RANKS];
     void* y_peer[route::MAX_RANKS];
-    int* ep_token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers
+    int* ep_token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers, then one int that stays zero
+    cudaStream_t side_stream;  // shared-expert GEMMs of the expert-parallel mode
+    cudaEvent_t ev_fork, ev_join;
 
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
-    cudaStream_t own_stream;
+    int* counts_acc;
+    cudaStream_t own_stream, in_stream, out_stream;
+    cudaEvent_t* chunk_ev;
 
     cudaStream_t last_stream;
     int last_T;
+    int tok_base;  // see prichs_moe_forward
     bool timing;
     cudaEvent_t ev[7];
     bool ev_valid;
@@ -368,7 +374,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
     A(dalloc(&h->status, 1));
     A(dalloc(&h->meta, 1));
-    A(dalloc(&h->ep_token, 2 * route::MAX_RANKS));
+    A(dalloc(&h->ep_token, 2 * route::MAX_RANKS + 8));
     if (rc != PRICHS_OK) {
         prichs_moe_destroy(h);
         return rc;
@@ -376,7 +382,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
     cudaMemset(h->status, 0, sizeof(int));
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
-    cudaMemset(h->ep_token, 0, 2 * route::MAX_RANKS * sizeof(int));
+    cudaMemset(h->ep_token, 0, (2 * route::MAX_RANKS + 8) * sizeof(int));
     for (int i = 0; i < route::MAX_RANKS; ++i) {
         h->xp_peer[i] = h->xp;
         h->y_peer[i] = h->ybuf;
@@ -417,6 +423,9 @@ int prichs_moe_destroy(prichs_moe_t* h) {
             if (h->y_peer[r]) cudaIpcCloseMemHandle(h->y_peer[r]);
         }
         if (h->comm && nccl().ok) nccl().comm_destroy(h->comm);
+        if (h->side_stream) cudaStreamDestroy(h->side_stream);
+        if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+        if (h->ev_join) cudaEventDestroy(h->ev_join);
     }
     void* ptrs[] = {h->ep_token, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
                     h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
@@ -426,6 +435,14 @@ int prichs_moe_destroy(prichs_moe_t* h) {
     for (int i = 0; i < 7; ++i)
         if (h->ev[i]) cudaEventDestroy(h->ev[i]);
     if (h->own_stream) cudaStreamDestroy(h->own_stream);
+    if (h->in_stream) cudaStreamDestroy(h->in_stream);
+    if (h->out_stream) cudaStreamDestroy(h->out_stream);
+    if (h->chunk_ev) {
+        for (int i = 0; i < 128; ++i)
+            if (h->chunk_ev[i]) cudaEventDestroy(h->chunk_ev[i]);
+        delete[] h->chunk_ev;
+    }
+    if (h->counts_acc) cudaFree(h->counts_acc);
     delete h;
     return PRICHS_OK;
 }
@@ -504,7 +521,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
     if (!h->weights_ready) return fail(PRICHS_ERR_BAD_ARG, "weights have not been uploaded");
     if (T < 0) return fail(PRICHS_ERR_BAD_SHAPE, "negative token count");
-    if (T > h->Tmax) return fail(PRICHS_ERR_CAPACITY, "T=%d exceeds max_tokens=%d of this handle", T, h->Tmax);
+    if (T > h->Tmax - h->tok_base) return fail(PRICHS_ERR_CAPACITY, "T=%d exceeds max_tokens=%d of this handle", T, h->Tmax);
     if ((x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) || (y_dtype != PRICHS_DTYPE_F32 && y_dtype != PRICHS_DTYPE_BF16))
         return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
     if (h->mode == PRICHS_MODE_F32 && x_dtype != PRICHS_DTYPE_F32)
@@ -526,6 +543,12 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     DeviceGuard guard(h->device);
 
     const int d = h->d, f = h->f, E = h->E;
+    // routing results of this call start at token `tok_base` of the stash arrays (non-zero only while the
+    // host-buffer entry point feeds a batch through in chunks)
+    float* logits = h->logits + (size_t)h->tok_base * route::MAX_E;
+    int* sel = h->sel + (size_t)h->tok_base * 2;
+    float* gates = h->gates + (size_t)h->tok_base * 2;
+    int* pos = h->pos + (size_t)h->tok_base * 2;
     route::ConceptBias cb;
     for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = (e < n_concept && e < E) ? concept_bias[e] : 0.0f;
 
@@ -545,26 +568,63 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     // 1. router
     if (f32mode) {
         route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
-                                                        h->logits, h->sel, h->gates, h->tile_counts);
+                                                        logits, sel, gates, h->tile_counts);
     } else {
         const int grid = ntiles;
         constexpr int RT = route::ROUTER_WARPS * 32;
         if (x_dtype == PRICHS_DTYPE_F32) {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<1, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
             else
-                route::router_mma_kernel<3, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<3, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
         } else {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<1, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
             else
-                route::router_mma_kernel<3, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, h->logits, h->sel, h->gates, h->tile_counts);
+                route::router_mma_kernel<3, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
         }
     }
     LAUNCH_CHECK("router");
     mark();
-    // 2. prefix sums + placement plan
+    // Arguments of the two grouped GEMMs (gate|up + SwiGLU, then down); they depend on host values only.
+    egemm::Args a1;
+    memset(&a1, 0, sizeof(a1));
+    a1.nk = d / egemm::BK;
+    a1.split3 = f32mode;
+    a1.n_ntiles = f / 128;
+    a1.shared_mtiles = (T + 127) / 128;
+    a1.routed_base_tiles = h->Tcap / 128;
+    a1.a_routed_tile_off = 0;
+    a1.n_routed_mtiles = &h->meta->n_routed_mtiles;
+    a1.mtile_slot = h->mtile_slot;
+    a1.w_rows = 2 * f;
+    a1.out_split = f32mode;
+    a1.out_lo_off = f;
+    a1.out_f32 = 0;
+    a1.status = h->status;
+    egemm::Args a2 = a1;
+    a2.nk = f / egemm::BK;
+    a2.n_ntiles = d / egemm::BN;
+    a2.a_routed_tile_off = h->Tcap / 128;
+    a2.w_rows = d;
+    a2.out_split = 0;
+    a2.out_f32 = f32mode;
     const bool ep = h->world > 1;
+    if (ep) {
+        // The shared expert needs no exchange: its two GEMMs run on a side stream while the main stream
+        // gathers counts, plans, dispatches rows over NVLink and waits for the peers.
+        egemm::Args s1 = a1, s2 = a2;
+        s1.n_routed_mtiles = s2.n_routed_mtiles = h->ep_token + 2 * route::MAX_RANKS;  // a device zero
+        CUDA_TRY(cudaEventRecord(h->ev_fork, st));
+        CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_fork, 0));
+        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, s1);
+        LAUNCH_CHECK("shared gate/up GEMM");
+        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, s2);
+        LAUNCH_CHECK("shared down GEMM");
+        CUDA_TRY(cudaEventRecord(h->ev_join, h->side_stream));
+        a1.shared_mtiles = a2.shared_mtiles = 0;  // the main-stream launches cover the routed rows only
+    }
+    // 2. prefix sums + placement plan
     route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, h->world, h->rank,
                                            h->Rcap, ep ? 0 : 1, h->status);
     LAUNCH_CHECK("scan");
@@ -582,41 +642,20 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         xp_peers.p[i] = h->xp_peer[i];
         y_peers.p[i] = h->y_peer[i];
     }
-    route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, h->sel, h->tile_prefix, h->meta, xp_peers, h->El, h->pos);
+    route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, sel, h->tile_prefix, h->meta, xp_peers, h->El, pos);
     LAUNCH_CHECK("dispatch");
     // barrier: every rank's rows have landed in the owners' buffers before any expert GEMM reads them
     if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + h->rank, h->ep_token, 1, NCCL_INT32, h->comm, st));
     mark();
-    // 4. gate|up GEMM + SwiGLU for the shared and all routed experts
-    egemm::Args a1;
-    memset(&a1, 0, sizeof(a1));
-    a1.nk = d / egemm::BK;
-    a1.split3 = f32mode;
-    a1.n_ntiles = f / 128;
-    a1.shared_mtiles = (T + 127) / 128;
-    a1.routed_base_tiles = h->Tcap / 128;
-    a1.a_routed_tile_off = 0;
-    a1.n_routed_mtiles = &h->meta->n_routed_mtiles;
-    a1.mtile_slot = h->mtile_slot;
-    a1.w_rows = 2 * f;
-    a1.out_split = f32mode;
-    a1.out_lo_off = f;
-    a1.out_f32 = 0;
-    a1.status = h->status;
+    // 4. gate|up GEMM + SwiGLU (shared + routed experts; routed only in expert-parallel mode)
     egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
     LAUNCH_CHECK("gate/up GEMM");
     mark();
     // 5. down GEMM
-    egemm::Args a2 = a1;
-    a2.nk = f / egemm::BK;
-    a2.n_ntiles = d / egemm::BN;
-    a2.a_routed_tile_off = h->Tcap / 128;
-    a2.w_rows = d;
-    a2.out_split = 0;
-    a2.out_f32 = f32mode;
     egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
     LAUNCH_CHECK("down GEMM");
     mark();
+    if (ep) CUDA_TRY(cudaStreamWaitEvent(st, h->ev_join, 0));  // shared-expert rows are complete
     // barrier: every owner's expert outputs are complete before the combine gathers them over NVLink
     if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + route::MAX_RANKS + h->rank, h->ep_token + route::MAX_RANKS, 1, NCCL_INT32, h->comm, st));
     // 6. combine (+ residual)
@@ -626,7 +665,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
         const bool of32 = y_dtype == PRICHS_DTYPE_F32;
 #define COMBINE(YF, OF, RS) \
-    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(h->ybuf, y_peers, rb, h->sel, h->gates, h->pos, resid_dev, y_dev, T, d, h->El)
+    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(h->ybuf, y_peers, rb, sel, gates, pos, resid_dev, y_dev, T, d, h->El)
         if (f32mode) {
             if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
             else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
@@ -642,6 +681,21 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     return PRICHS_OK;
 }
 
+// Adds the per-expert counts of the chunk that just ran to `acc` (first chunk: overwrite).
+__global__ void host_chunk_accumulate_kernel(const route::RouteMeta* __restrict__ meta, int* __restrict__ acc, int first) {
+    const int e = threadIdx.x;
+    if (e < route::MAX_E) acc[e] = (first ? 0 : acc[e]) + meta->counts[e];
+}
+// After the last chunk: the call's totals become the handle's "last forward" counts.
+__global__ void host_chunk_finish_kernel(route::RouteMeta* __restrict__ meta, const int* __restrict__ acc) {
+    const int e = threadIdx.x;
+    if (e < route::MAX_E) {
+        meta->counts[e] = acc[e];
+        meta->total[e] = acc[e];
+        meta->cmat[e] = acc[e];
+    }
+}
+
 int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host, const float* concept_bias,
                             int n_concept, float* y_host, int T) {
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
@@ -651,28 +705,68 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     if (!x_host || !y_host) return fail(PRICHS_ERR_BAD_ARG, "null host buffer");
     DeviceGuard guard(h->device);
     const size_t n = (size_t)h->Tmax * h->d;
+    constexpr int MAX_CHUNKS = 64;
     if (!h->stage_x) {
         int rc = dalloc(&h->stage_x, n);
         if (rc == PRICHS_OK) rc = dalloc(&h->stage_y, n);
+        if (rc == PRICHS_OK) rc = dalloc(&h->counts_acc, route::MAX_E);
         if (rc != PRICHS_OK) return rc;
         CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+        h->chunk_ev = new cudaEvent_t[2 * MAX_CHUNKS];
+        for (int i = 0; i < 2 * MAX_CHUNKS; ++i) CUDA_TRY(cudaEventCreateWithFlags(&h->chunk_ev[i], cudaEventDisableTiming));
     }
     if (resid_host && !h->stage_r) {
         int rc = dalloc(&h->stage_r, n);
         if (rc != PRICHS_OK) return rc;
     }
-    const size_t bytes = (size_t)T * h->d * sizeof(float);
+    // Tokens are independent, so a large batch is fed through in chunks: the upload of chunk i+1 and the
+    // download of chunk i-1 overlap the kernels of chunk i (three streams). Results are bit-identical to one
+    // pass; counts are summed over the chunks. Expert-parallel handles run one pass (all ranks in lock step).
+    int chunk = T;
+    if (h->world == 1 && T >= 4096) {
+        chunk = 2048;
+        while ((T + chunk - 1) / chunk > MAX_CHUNKS) chunk *= 2;
+    }
+    const int nchunks = (T + chunk - 1) / chunk;
     cudaStream_t st = h->own_stream;
-    CUDA_TRY(cudaMemcpyAsync(h->stage_x, x_host, bytes, cudaMemcpyHostToDevice, st));
-    if (resid_host) CUDA_TRY(cudaMemcpyAsync(h->stage_r, resid_host, bytes, cudaMemcpyHostToDevice, st));
-    int rc = prichs_moe_forward(h, h->stage_x, PRICHS_DTYPE_F32, resid_host ? h->stage_r : nullptr, concept_bias, n_concept,
-                                h->stage_y, PRICHS_DTYPE_F32, T, st);
+    const size_t row = (size_t)h->d;
+    int rc = PRICHS_OK;
+    for (int c = 0; c < nchunks && rc == PRICHS_OK; ++c) {
+        const int t0 = c * chunk, tc = std::min(chunk, T - t0);
+        const size_t off = (size_t)t0 * row, bytes = (size_t)tc * row * sizeof(float);
+        cudaEvent_t ev_in = h->chunk_ev[2 * c], ev_done = h->chunk_ev[2 * c + 1];
+        CUDA_TRY(cudaMemcpyAsync(h->stage_x + off, x_host + off, bytes, cudaMemcpyHostToDevice, h->in_stream));
+        if (resid_host) CUDA_TRY(cudaMemcpyAsync(h->stage_r + off, resid_host + off, bytes, cudaMemcpyHostToDevice, h->in_stream));
+        CUDA_TRY(cudaEventRecord(ev_in, h->in_stream));
+        CUDA_TRY(cudaStreamWaitEvent(st, ev_in, 0));
+        h->tok_base = t0;
+        rc = prichs_moe_forward(h, h->stage_x + off, PRICHS_DTYPE_F32, resid_host ? h->stage_r + off : nullptr, concept_bias,
+                                n_concept, h->stage_y + off, PRICHS_DTYPE_F32, tc, st);
+        h->tok_base = 0;
+        if (rc != PRICHS_OK) break;
+        if (nchunks > 1) {
+            host_chunk_accumulate_kernel<<<1, 32, 0, st>>>(h->meta, h->counts_acc, c == 0);
+            LAUNCH_CHECK("count accumulation");
+        }
+        CUDA_TRY(cudaEventRecord(ev_done, st));
+        CUDA_TRY(cudaStreamWaitEvent(h->out_stream, ev_done, 0));
+        CUDA_TRY(cudaMemcpyAsync(y_host + off, h->stage_y + off, bytes, cudaMemcpyDeviceToHost, h->out_stream));
+    }
+    if (rc == PRICHS_OK && nchunks > 1) {
+        host_chunk_finish_kernel<<<1, 32, 0, st>>>(h->meta, h->counts_acc);
+        LAUNCH_CHECK("count totals");
+    }
+    h->last_T = T;
+    h->last_stream = st;
+    cudaError_t e1 = cudaStreamSynchronize(h->in_stream), e2 = cudaStreamSynchronize(st), e3 = cudaStreamSynchronize(h->out_stream);
     if (rc != PRICHS_OK) return rc;
-    CUDA_TRY(cudaMemcpyAsync(y_host, h->stage_y, bytes, cudaMemcpyDeviceToHost, st));
-    CUDA_TRY(cudaStreamSynchronize(st));
-    int s = 0;
-    CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
-    return translate_status(s);
+    if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
+        return fail(PRICHS_ERR_CUDA, "host-buffer forward failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3)));
+    int sdev = 0;
+    CUDA_TRY(cudaMemcpy(&sdev, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return translate_status(sdev);
 }
 
 int prichs_moe_sync_status(prichs_moe_t* h) {
@@ -797,6 +891,9 @@ int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs
     NcclApi::Id128 id;
     memcpy(&id, id128, sizeof(id));
     NCCL_TRY(nccl().comm_init_rank(&h->comm, h->world, id, h->rank));
+    CUDA_TRY(cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
     h->ep_ready = true;
     return PRICHS_OK;
 }

@@ -1,0 +1,122 @@
+"""Expert-parallel protocol on CPU ranks (gloo, world_size 2): partition invariance.
+
+Each rank routes its own tokens (oracle), the ranks all-gather their counts, build the placement plan with
+prichs_b200.ep.plan (the host restatement of the device plan), place rows in the owners' receive buffers at
+seg_base + src_off + local index exactly as the dispatch kernel does, run the owned experts, and the source
+ranks gather the rows back and combine them in ascending expert order. The result must equal the single-rank
+oracle bit for bit in fp32 (the layer is token-wise independent once routing is fixed)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch.distributed as dist
+    from oracle import oracle as O
+    from prichs_b200 import ep
+    from _util import small_int_weights, grid_tensor
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        O.set_num_threads(2)
+        d, f, E, k = 64, 32, 8, 2
+        El = E // world
+        ws = small_int_weights(3, d, f, E)
+        bias = grid_tensor(3, 1000, (E,), 4, 32)
+        T = 50 + 13 * rank
+        x = grid_tensor(3000 + rank, 0, (T, d), 16, 8)
+        r = O.route(x, ws[0], bias, k)
+        sel, gat, counts = r["selected"], r["gating"], r["counts"]
+        allc = [None] * world
+        dist.all_gather_object(allc, counts)
+        cmat = np.stack(allc)
+        p = ep.plan(cmat, rank)
+        # dispatch: (owner, row, payload) for every assignment, rows in token order inside an expert
+        seen = np.zeros(E, np.int64)
+        pos = np.zeros((T, k), np.int64)
+        outbox = [[] for _ in range(world)]
+        for t in range(T):
+            for j in range(k):
+                e = int(sel[t, j])
+                row = int(p["seg_base"][e] + p["src_off"][e] + seen[e])
+                seen[e] += 1
+                pos[t, j] = row
+                outbox[e // El].append((row, x[t]))
+        inboxes = [None] * world
+        dist.all_gather_object(inboxes, outbox)
+        mine = ep.plan(cmat, rank)
+        cap = mine["n_mtiles"] * 128
+        xp = np.zeros((cap, d), np.float32)
+        filled = np.zeros(cap, bool)
+        for src in range(world):
+            for row, payload in inboxes[src][rank]:
+                assert not filled[row], "two assignments landed on one row"
+                xp[row], filled[row] = payload, True
+        assert int(filled.sum()) == mine["recv_rows"]
+        # owned experts over their 128-aligned segments
+        yp = np.zeros((cap, d), np.float32)
+        for le in range(El):
+            e = rank * El + le
+            lo, n = int(mine["seg_base"][e]), int(mine["total"][e])
+            assert lo % 128 == 0 and filled[lo:lo + n].all() and not filled[lo + n:lo + (n + 127) // 128 * 128].any()
+            if n:
+                h = O.swiglu(O.matmul_2d(xp[lo:lo + n], ws[4 + 3 * e]), O.matmul_2d(xp[lo:lo + n], ws[5 + 3 * e]))
+                yp[lo:lo + n] = O.matmul_2d(h, ws[6 + 3 * e])
+        ybufs = [None] * world
+        dist.all_gather_object(ybufs, yp)
+        # combine on the source rank: shared row, then experts ascending, multiply and add rounded separately
+        hs = O.swiglu(O.matmul_2d(x, ws[1]), O.matmul_2d(x, ws[2]))
+        out = O.matmul_2d(hs, ws[3])
+        for t in range(T):
+            for j in np.argsort(sel[t], kind="stable"):
+                e = int(sel[t, j])
+                out[t] = out[t] + np.float32(gat[t, j]) * ybufs[e // El][pos[t, j]]
+        ref = O.moe_forward_train(ws, bias, k, x)
+        ok = np.array_equal(out, ref["out"]) and np.array_equal(ref["counts"], counts)
+        # the bias update from global counts is the same on every rank
+        b = O.update_aux_free_bias(bias, cmat.sum(axis=0), int(sum(50 + 13 * q for q in range(world))), 1e-3, k)
+        allb = [None] * world
+        dist.all_gather_object(allb, b)
+        ok = ok and all(np.array_equal(b, o) for o in allb)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_partition_invariance_gloo():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29600 + os.getpid() % 200
+    ctx = mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=False)
+    import time
+    deadline = time.time() + 240
+    while not ctx.join(timeout=5):  # join() returns False while some rank is still running
+        assert time.time() < deadline, "gloo ranks did not finish"
+    assert dict(ret) == {0: True, 1: True}
+
+
+def test_plan_properties():
+    sys.path.insert(0, ROOT)
+    from prichs_b200 import ep
+    rng = np.random.default_rng(0)
+    for world in (1, 2, 4, 8):
+        cmat = rng.integers(0, 400, size=(world, 8))
+        cmat[:, 3] = 0  # an expert nobody selected
+        plans = [ep.plan(cmat, r) for r in range(world)]
+        El = 8 // world
+        for e in range(8):
+            o = e // El
+            # the ranks' slices tile the expert's segment without gaps or overlap, in rank order
+            offs = [int(plans[r]["src_off"][e]) for r in range(world)]
+            assert offs == np.concatenate([[0], np.cumsum(cmat[:-1, e])]).tolist()
+            assert all(int(pl["seg_base"][e]) == int(plans[o]["seg_base"][e]) for pl in plans)
+            assert plans[o]["seg_base"][e] % 128 == 0
+        assert sum(pl["recv_rows"] for pl in plans) == int(cmat.sum())

@@ -235,6 +235,29 @@ def test_f32_activations_in_bf16_mode(torch_cuda, oracle):
     assert np.array_equal(yh, y)
 
 
+def test_host_buffers_chunked_pipeline_equals_one_pass(torch_cuda, oracle):
+    """The host-buffer entry point feeds large batches through in chunks (upload / kernels / download overlap);
+    outputs, routing stash and counts must equal the one-pass device call bit for bit."""
+    from prichs_b200 import synth
+    d, f, E, k, T = 256, 128, 8, 2, 9000  # > 4096 tokens: five chunks, the last one ragged
+    ws, _, bias = _synth_case(91, T, d, f, E, bias_range=(-0.1, 0.1), std=0.05)
+    x32 = synth.normal(91, 0, (T, d))
+    resid = synth.normal(92, 0, (T, d))
+    m, y_dev, st_dev = _gpu_forward(torch_cuda, ws, bias, k, x32, x_kind="f32", resid=resid)
+    _, y_host, st_host = _gpu_forward(torch_cuda, ws, bias, k, x32, host=True, resid=resid, layer=m)
+    assert np.array_equal(y_host, y_dev)
+    assert np.array_equal(st_host.router_logits, st_dev.router_logits)
+    assert np.array_equal(st_host.selected_experts, st_dev.selected_experts)
+    assert np.array_equal(st_host.gating_weights, st_dev.gating_weights)
+    assert np.array_equal(st_host.expert_token_counts, st_dev.expert_token_counts)
+    # the device-side bias update sees the counts of the whole call, not of the last chunk
+    m.update_bias_from_last(1e-3)
+    assert np.array_equal(m.router_bias, oracle.update_aux_free_bias(bias, st_dev.expert_token_counts, T, 1e-3, k))
+    xr = synth.round_bf16(x32)
+    agree = _check_routing(oracle, ws, bias, k, xr, st_host)
+    _check_outputs(oracle, ws, bias, k, xr, y_host, agree, TOL_BF16, resid=resid, sample=np.arange(0, T, 7))
+
+
 def test_residual_and_concept_bias(torch_cuda, oracle):
     from prichs_b200 import synth
     d, f, E, k, T = 256, 128, 8, 2, 130
