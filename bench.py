@@ -298,7 +298,9 @@ def main():
             s["frac"] = s["TFLOP/s"] / peaks["tf"]
     roofline = {"kernel": "expert_gemm_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
                 "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
-                "traffic": None, "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
+                # dram__bytes_read + dram__bytes_write of one launch at this size, from the one-pass ncu capture
+                # summarised in profiles/traffic_config1_full_size.md (bytes); only valid for config 1
+                "traffic": 323.9e6 if (n_gpus == 1 and not args.tokens) else None, "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
                 "algorithmic_flops_per_launch": gu_flops}
 
     line = {
