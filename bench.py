@@ -239,17 +239,19 @@ def main():
         launches = int(L.prichs_kernel_launches() - launches0)
         ms_total = e0.elapsed_time(e1)
         # stage breakdown: the library records CUDA events on the launching stream between its kernels
-        L.prichs_moe_enable_timing(layer._h, 1)
-        stage = np.zeros(6, np.float64)
-        nstage = min(args.steps, 20)
-        import ctypes as C
-        buf = (C.c_float * 6)()
-        for i in range(nstage):
-            step(i)
-            L.prichs_moe_get_stage_ms(layer._h, buf)
-            stage += np.array(list(buf), np.float64)
-        stage /= nstage
-        L.prichs_moe_enable_timing(layer._h, 0)
+        stage = None
+        if world == 1:  # (the expert-parallel forward overlaps its kernels on several streams: no per-stage split)
+            L.prichs_moe_enable_timing(layer._h, 1)
+            stage = np.zeros(6, np.float64)
+            nstage = min(args.steps, 20)
+            import ctypes as C
+            buf = (C.c_float * 6)()
+            for i in range(nstage):
+                step(i)
+                L.prichs_moe_get_stage_ms(layer._h, buf)
+                stage += np.array(list(buf), np.float64)
+            stage /= nstage
+            L.prichs_moe_enable_timing(layer._h, 0)
 
         # ---- end to end through the host-buffer entry point ------------------------------------------
         xh = [torch.from_numpy(x).pin_memory() for x in xs_host[:2]]
@@ -271,8 +273,6 @@ def main():
     tokens = T * n_gpus
     value = tokens / (ms_step * 1e-3)
 
-    names = ["router", "scan", "dispatch", "gate_up_gemm", "down_gemm", "combine"]
-    stage_ms = dict(zip(names, [float(v) for v in stage]))
     # rows the GEMMs of THIS rank processed: its T shared rows plus the routed rows its experts received
     rows = T * (1 + K)
     if world > 1:
@@ -281,27 +281,40 @@ def main():
         L.prichs_moe_ep_recv_rows(layer._h, C2.byref(rr))
         rows = T + int(rr.value)
     gu_flops = rows * 4 * D * F
-    gu_tf = gu_flops / (stage_ms["gate_up_gemm"] * 1e-3) / 1e12
-    dn_tf = rows * 2 * D * F / (stage_ms["down_gemm"] * 1e-3) / 1e12
-    stages = {
-        "router": {"ms": stage_ms["router"], "GB/s": T * ROUTER_BYTES / stage_ms["router"] / 1e6, "bound": "hbm"},
-        "scan": {"ms": stage_ms["scan"]},
-        "dispatch": {"ms": stage_ms["dispatch"], "GB/s": T * DISPATCH_BYTES / stage_ms["dispatch"] / 1e6, "bound": "hbm"},
-        "gate_up_gemm": {"ms": stage_ms["gate_up_gemm"], "TFLOP/s": gu_tf, "bound": "tensor"},
-        "down_gemm": {"ms": stage_ms["down_gemm"], "TFLOP/s": dn_tf, "bound": "tensor"},
-        "combine": {"ms": stage_ms["combine"], "GB/s": T * COMBINE_BYTES_NORES / stage_ms["combine"] / 1e6, "bound": "hbm"},
-    }
-    for s in stages.values():
-        if "GB/s" in s:
-            s["frac"] = s["GB/s"] / peaks["hbm"]
-        if "TFLOP/s" in s:
-            s["frac"] = s["TFLOP/s"] / peaks["tf"]
-    roofline = {"kernel": "expert_gemm_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
-                "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
-                # dram__bytes_read + dram__bytes_write of one launch at this size, from the one-pass ncu capture
-                # summarised in profiles/traffic_config1_full_size.md (bytes); only valid for config 1
-                "traffic": 323.9e6 if (n_gpus == 1 and not args.tokens) else None, "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
-                "algorithmic_flops_per_launch": gu_flops}
+    if stage is not None:
+        names = ["router", "scan", "dispatch", "gate_up_gemm", "down_gemm", "combine"]
+        stage_ms = dict(zip(names, [float(v) for v in stage]))
+        gu_tf = gu_flops / (stage_ms["gate_up_gemm"] * 1e-3) / 1e12
+        dn_tf = rows * 2 * D * F / (stage_ms["down_gemm"] * 1e-3) / 1e12
+        stages = {
+            "router": {"ms": stage_ms["router"], "GB/s": T * ROUTER_BYTES / stage_ms["router"] / 1e6, "bound": "hbm"},
+            "scan": {"ms": stage_ms["scan"]},
+            "dispatch": {"ms": stage_ms["dispatch"], "GB/s": T * DISPATCH_BYTES / stage_ms["dispatch"] / 1e6, "bound": "hbm"},
+            "gate_up_gemm": {"ms": stage_ms["gate_up_gemm"], "TFLOP/s": gu_tf, "bound": "tensor"},
+            "down_gemm": {"ms": stage_ms["down_gemm"], "TFLOP/s": dn_tf, "bound": "tensor"},
+            "combine": {"ms": stage_ms["combine"], "GB/s": T * COMBINE_BYTES_NORES / stage_ms["combine"] / 1e6, "bound": "hbm"},
+        }
+        for s in stages.values():
+            if "GB/s" in s:
+                s["frac"] = s["GB/s"] / peaks["hbm"]
+            if "TFLOP/s" in s:
+                s["frac"] = s["TFLOP/s"] / peaks["tf"]
+        roofline = {"kernel": "expert_gemm_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
+                    "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
+                    # dram__bytes_read + dram__bytes_write of one launch at this size, from the one-pass ncu capture
+                    # summarised in profiles/traffic_config1_full_size.md (bytes); only valid for config 1
+                    "traffic": 323.9e6 if not args.tokens else None,
+                    "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
+                    "algorithmic_flops_per_launch": gu_flops}
+    else:
+        # Expert-parallel step: the GEMM launches of the waves overlap the exchange of other waves on several
+        # streams, so one kernel cannot be timed alone; the figure is this rank's GEMM flops over the WHOLE step.
+        stages = None
+        tf = rows * 6 * D * F / (ms_step * 1e-3) / 1e12
+        roofline = {"kernel": "expert_gemm_kernel (all GEMM launches of one rank) over the whole expert-parallel step",
+                    "bound": "tensor", "achieved": tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": tf / peaks["tf"],
+                    "traffic": None, "peak_source": f"{peaks['source']} bf16_tflops (burst)",
+                    "algorithmic_flops_per_launch": rows * 6 * D * F}
 
     line = {
         "metric": "MoE-layer tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,

@@ -62,6 +62,9 @@ typedef struct prichs_moe_config {
     int ep_world;         /* expert-parallel ranks (1 = all experts local); must divide num_experts    */
     int ep_rank;          /* this rank, 0..ep_world-1; owns experts [rank*E/world, (rank+1)*E/world)   */
     int ep_max_recv_rows; /* capacity of the receive side in rows (0 = worst case ep_world*max_tokens*top_k) */
+    int ep_waves;         /* expert-parallel only: the batch is cut into this many token waves (1..4) whose
+                             exchanges overlap the other waves' GEMMs; 0 = choose from max_tokens. Must be the
+                             same on every rank.                                                          */
 } prichs_moe_config_t;
 
 /* ---- lifetime ------------------------------------------------------------------------------------ */
@@ -151,15 +154,18 @@ PRICHS_API int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, si
  * counts (placement plan + global counts for the bias update) and two token-sized all-gathers used as
  * barriers (rows landed / outputs ready), all on the forward's stream.
  * Set-up, with any host channel (MPI, torch.distributed, a file) moving the bytes:
- *   1. rank 0: prichs_moe_ep_unique_id(id) and broadcast the 128 bytes;
+ *   1. rank 0: prichs_moe_ep_unique_id(id) and broadcast the PRICHS_EP_ID_BYTES bytes;
  *   2. every rank: prichs_moe_ep_export(h, blob) and all-gather the 128-byte blobs in rank order;
  *   3. every rank: prichs_moe_ep_init(h, id, all_blobs)  (collective: creates the communicator, maps peers).
- * All ranks must then call prichs_moe_forward in the same order. libnccl.so.2 is loaded at run time. */
-#define PRICHS_EP_ID_BYTES 128
+ * All ranks must then call prichs_moe_forward in the same order. libnccl.so.2 is loaded at run time.
+ * Waves: tokens are independent, so a forward cuts its batch into ep_waves token ranges, each with its own
+ * receive region, stream and communicator: while the experts of one wave compute, the rows of the next wave
+ * travel and the outputs of the previous wave are combined. The shared expert runs on a further stream. */
+#define PRICHS_EP_ID_BYTES 1024 /* one communicator id per wave */
 #define PRICHS_EP_BLOB_BYTES 128
-PRICHS_API int prichs_moe_ep_unique_id(void* id128);
+PRICHS_API int prichs_moe_ep_unique_id(void* id_bytes);
 PRICHS_API int prichs_moe_ep_export(prichs_moe_t* h, void* blob128);
-PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs);
+PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id_bytes, const void* all_blobs);
 
 /* Rows this rank's experts received in the last forward (expert-parallel load), host value. */
 PRICHS_API int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows);

@@ -18,7 +18,7 @@ MODE_BF16, MODE_F32 = 0, 1
 
 class Config(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("hidden_dim", "intermediate_dim", "num_experts", "top_k", "max_tokens",
-                                       "mode", "device", "ep_world", "ep_rank", "ep_max_recv_rows")]
+                                       "mode", "device", "ep_world", "ep_rank", "ep_max_recv_rows", "ep_waves")]
 
 
 # name -> (restype, argtypes); the full export list of include/prichs_moe.h

@@ -224,6 +224,17 @@ NcclApi& nccl() {
 }  // namespace
 
 // =====================================================================================================
+constexpr int MAX_WAVES = 4;
+// One token wave of an expert-parallel forward: its own stream, communicator, plan and barrier payload.
+struct EpWave {
+    cudaStream_t stream;
+    void* comm;
+    route::RouteMeta* meta;
+    int* mtile_slot;
+    int* token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers
+    cudaEvent_t done;
+};
+
 struct prichs_moe {
     prichs_moe_config_t cfg;
     int d, f, E, k, Tmax, mode, device;
@@ -246,14 +257,16 @@ struct prichs_moe {
     CUtensorMap tm_xp, tm_wgu, tm_h, tm_wdn;
     CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
 
-    // expert-parallel group: communicator, peers' receive / output buffers mapped into this process
-    void* comm;
+    // expert-parallel group: peers' receive / output buffers mapped into this process, and the token waves
     bool ep_ready;
     void* xp_peer[route::MAX_RANKS];
     void* y_peer[route::MAX_RANKS];
-    int* ep_token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers, then one int that stays zero
+    int n_waves;  // token waves of an expert-parallel forward (1 when all experts are local)
+    int Rw;       // rows of one wave's permuted region (multiple of 128); Rcap = n_waves * Rw
+    EpWave wave[MAX_WAVES];
+    int* ep_zero;              // a device int that stays zero (the "no permuted tiles" count of the shared launches)
     cudaStream_t side_stream;  // shared-expert GEMMs of the expert-parallel mode
-    cudaEvent_t ev_fork, ev_join;
+    cudaEvent_t ev_router, ev_shared;
 
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
@@ -300,6 +313,220 @@ int translate_status(int s) {
     }
 }
 
+// ---- launch helpers shared by the single-GPU and the expert-parallel forward ---------------------------
+// Router over T tokens starting at `x_dev`; routing arrays are the caller's (already offset) pointers.
+int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::ConceptBias& cb, int T, float* logits, int* sel,
+                  float* gates, int* tile_counts, cudaStream_t st) {
+    const int d = h->d, E = h->E;
+    const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    if (h->mode == PRICHS_MODE_F32) {
+        route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
+                                                        logits, sel, gates, tile_counts);
+    } else {
+        constexpr int RT = route::ROUTER_WARPS * 32;
+        if (x_dtype == PRICHS_DTYPE_F32) {
+            if (h->rt_nsplit == 1)
+                route::router_mma_kernel<1, true><<<ntiles, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+            else
+                route::router_mma_kernel<3, true><<<ntiles, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+        } else {
+            if (h->rt_nsplit == 1)
+                route::router_mma_kernel<1, false><<<ntiles, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+            else
+                route::router_mma_kernel<3, false><<<ntiles, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+        }
+    }
+    LAUNCH_CHECK("router");
+    return PRICHS_OK;
+}
+
+// Arguments of the two grouped GEMMs (gate|up + SwiGLU, then down) for T un-permuted tokens and the permuted
+// region that starts `region_tile` 128-row tiles into the permuted buffers.
+void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles, const int* mtile_slot, egemm::Args* a1,
+               egemm::Args* a2) {
+    const bool f32mode = h->mode == PRICHS_MODE_F32;
+    memset(a1, 0, sizeof(*a1));
+    a1->nk = h->d / egemm::BK;
+    a1->split3 = f32mode;
+    a1->n_ntiles = h->f / 128;
+    a1->shared_mtiles = (T + 127) / 128;
+    a1->routed_base_tiles = h->Tcap / 128 + region_tile;
+    a1->a_routed_tile_off = region_tile;
+    a1->n_routed_mtiles = n_routed_mtiles;
+    a1->mtile_slot = mtile_slot;
+    a1->w_rows = 2 * h->f;
+    a1->out_split = f32mode;
+    a1->out_lo_off = h->f;
+    a1->out_f32 = 0;
+    a1->status = h->status;
+    *a2 = *a1;
+    a2->nk = h->f / egemm::BK;
+    a2->n_ntiles = h->d / egemm::BN;
+    a2->a_routed_tile_off = h->Tcap / 128 + region_tile;
+    a2->w_rows = h->d;
+    a2->out_split = 0;
+    a2->out_f32 = f32mode;
+}
+
+// Combine of T tokens whose shared-expert rows start at `y_shared` and whose routing arrays / residual / output
+// are the caller's (already offset) pointers.
+int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y_peers, long long routed_base_rows, const int* sel,
+                   const float* gates, const int* pos, const void* resid_dev, void* y_dev, int x_dtype, int y_dtype, int T,
+                   cudaStream_t st) {
+    const int grid = (T + 7) / 8;
+    const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
+    const bool of32 = y_dtype == PRICHS_DTYPE_F32;
+#define COMBINE(YF, OF, RS) \
+    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
+    if (h->mode == PRICHS_MODE_F32) {
+        if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
+        else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
+    } else {
+        if (of32) { if (res == 0) COMBINE(false, true, 0); else if (res == 1) COMBINE(false, true, 1); else COMBINE(false, true, 2); }
+        else      { if (res == 0) COMBINE(false, false, 0); else if (res == 1) COMBINE(false, false, 1); else COMBINE(false, false, 2); }
+    }
+#undef COMBINE
+    LAUNCH_CHECK("combine");
+    return PRICHS_OK;
+}
+
+int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_dev, const route::ConceptBias& cb, void* y_dev,
+               int y_dtype, int T, cudaStream_t st);
+
+}  // namespace
+
+namespace {
+
+// Sums the waves' routing summaries into the handle's "last forward" summary (counts, totals, received rows,
+// counts matrix); segment bases and source offsets are those of wave 0.
+struct WaveMetas {
+    const route::RouteMeta* m[MAX_WAVES];
+};
+__global__ void ep_totals_kernel(const WaveMetas wm, int n_waves, route::RouteMeta* __restrict__ out) {
+    const int i = threadIdx.x;
+    if (i < route::MAX_E) {
+        int c = 0, t = 0;
+        for (int w = 0; w < n_waves; ++w) {
+            c += wm.m[w]->counts[i];
+            t += wm.m[w]->total[i];
+        }
+        out->counts[i] = c;
+        out->total[i] = t;
+        out->seg_base[i] = wm.m[0]->seg_base[i];
+        out->src_off[i] = wm.m[0]->src_off[i];
+    }
+    if (i < route::MAX_RANKS * route::MAX_E) {
+        int c = 0;
+        for (int w = 0; w < n_waves; ++w) c += wm.m[w]->cmat[i];
+        out->cmat[i] = c;
+    }
+    if (i == 0) {
+        int rows = 0, tiles = 0, over = 0;
+        for (int w = 0; w < n_waves; ++w) {
+            rows += wm.m[w]->recv_rows;
+            tiles += wm.m[w]->n_routed_mtiles;
+            over |= wm.m[w]->overflow;
+        }
+        out->recv_rows = rows;
+        out->n_routed_mtiles = tiles;
+        out->overflow = over;
+    }
+}
+
+// Expert-parallel forward. Buffer-reuse hazards between consecutive forwards are closed by stream order plus
+// the collectives: a peer writes this rank's receive region of wave w only after the counts all-gather of
+// its next forward's wave w, which this rank joins after every wave of the current forward has been joined
+// into `st`; a peer reads this rank's expert outputs of wave w in its combine, and this rank overwrites them
+// only after the "rows landed" barrier of the next forward's wave w, which that peer enters after its combine.
+int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_dev, const route::ConceptBias& cb, void* y_dev,
+               int y_dtype, int T, cudaStream_t st) {
+    const int E = h->E, W = h->n_waves;
+    const bool f32mode = h->mode == PRICHS_MODE_F32;
+    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    CUtensorMap tm_x;
+    int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
+    if (rc != PRICHS_OK) return rc;
+    h->ev_valid = false;
+    // A few SMs stay free of the persistent GEMM CTAs so that the small kernels of the other streams (scans,
+    // plans, NCCL) are never queued behind a whole GEMM.
+    const int gemm_grid = std::max(1, h->sm_count - 4);
+    const size_t xsz = x_dtype == PRICHS_DTYPE_F32 ? 4 : 2, osz = y_dtype == PRICHS_DTYPE_F32 ? 4 : 2, ysz = f32mode ? 4 : 2;
+
+    // 1. router over the whole batch
+    rc = launch_router(h, x_dev, x_dtype, cb, T, h->logits, h->sel, h->gates, h->tile_counts, st);
+    if (rc != PRICHS_OK) return rc;
+    CUDA_TRY(cudaEventRecord(h->ev_router, st));
+
+    // 2. the shared expert needs no exchange: both of its GEMMs run on the side stream
+    {
+        egemm::Args s1, s2;
+        gemm_args(h, T, 0, h->ep_zero, h->wave[0].mtile_slot, &s1, &s2);
+        CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_router, 0));
+        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, s1);
+        LAUNCH_CHECK("shared gate/up GEMM");
+        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, s2);
+        LAUNCH_CHECK("shared down GEMM");
+        CUDA_TRY(cudaEventRecord(h->ev_shared, h->side_stream));
+    }
+
+    // 3. token waves
+    const int Tw = round_up((T + W - 1) / W, route::TILE_TOKENS);
+    WaveMetas wm;
+    for (int w = 0; w < MAX_WAVES; ++w) wm.m[w] = h->wave[w < W ? w : 0].meta;
+    for (int w = 0; w < W; ++w) {
+        EpWave& wv = h->wave[w];
+        cudaStream_t ws = wv.stream;
+        const int t0 = std::min(T, w * Tw), tn = std::min(T, t0 + Tw) - t0;
+        const int tile0 = t0 / route::TILE_TOKENS, ntl = (tn + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+        const int region_tile = w * (h->Rw / 128);
+        int* sel = h->sel + (size_t)t0 * 2;
+        float* gates = h->gates + (size_t)t0 * 2;
+        int* pos = h->pos + (size_t)t0 * 2;
+        int* tprefix = h->tile_prefix + (size_t)tile0 * route::MAX_E;
+        CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_router, 0));
+        // counts of this rank's wave -> all-gather (row `rank` of the matrix, in place) -> the same plan everywhere
+        route::scan_kernel<<<1, 1024, 0, ws>>>(h->tile_counts + (size_t)tile0 * route::MAX_E, tprefix, ntl, wv.meta, wv.mtile_slot, E, h->El,
+                                               h->world, h->rank, h->Rw, 0, h->status);
+        LAUNCH_CHECK("scan");
+        NCCL_TRY(nccl().all_gather(wv.meta->cmat + h->rank * route::MAX_E, wv.meta->cmat, route::MAX_E, NCCL_INT32, wv.comm, ws));
+        route::plan_kernel<<<1, 256, 0, ws>>>(wv.meta, wv.mtile_slot, E, h->El, h->world, h->rank, h->Rw, h->status);
+        LAUNCH_CHECK("plan");
+        // dispatch: rows go straight into the owners' receive regions of this wave (peer memory over NVLink)
+        route::PeerPtrs xp_peers, y_peers;
+        for (int i = 0; i < route::MAX_RANKS; ++i) {
+            xp_peers.p[i] = static_cast<bf16*>(h->xp_peer[i]) + (size_t)w * h->Rw * h->K1;
+            y_peers.p[i] = h->y_peer[i];
+        }
+        if (tn > 0) {
+            route::dispatch_kernel<<<(tn + 7) / 8, 256, 0, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
+            LAUNCH_CHECK("dispatch");
+        }
+        // barrier: every rank's rows of this wave have landed before an expert GEMM reads them
+        NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
+        egemm::Args a1, a2;
+        gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, &a1, &a2);
+        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, ws>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
+        LAUNCH_CHECK("gate/up GEMM");
+        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, ws>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
+        LAUNCH_CHECK("down GEMM");
+        CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_shared, 0));  // the shared expert's rows are complete
+        // barrier: every owner's outputs of this wave are complete before the combine gathers them over NVLink
+        NCCL_TRY(nccl().all_gather(wv.token + route::MAX_RANKS + h->rank, wv.token + route::MAX_RANKS, 1, NCCL_INT32, wv.comm, ws));
+        if (tn > 0) {
+            const char* resid_w = resid_dev ? static_cast<const char*>(resid_dev) + (size_t)t0 * h->d * xsz : nullptr;
+            rc = launch_combine(h, static_cast<const char*>(h->ybuf) + (size_t)t0 * h->d * ysz, y_peers, (long long)h->Tcap + (long long)w * h->Rw,
+                                sel, gates, pos, resid_w, static_cast<char*>(y_dev) + (size_t)t0 * h->d * osz, x_dtype, y_dtype, tn, ws);
+            if (rc != PRICHS_OK) return rc;
+        }
+        CUDA_TRY(cudaEventRecord(wv.done, ws));
+    }
+    // 4. join the waves and publish the call's totals
+    for (int w = 0; w < W; ++w) CUDA_TRY(cudaStreamWaitEvent(st, h->wave[w].done, 0));
+    ep_totals_kernel<<<1, 64, 0, st>>>(wm, W, h->meta);
+    LAUNCH_CHECK("wave totals");
+    return PRICHS_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -339,12 +566,22 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     const int mul = h->mode == PRICHS_MODE_F32 ? 2 : 1;
     h->K1 = d * mul; h->K2 = f * mul;
     h->Tcap = round_up(h->Tmax, 128);
-    long long recv = cfg->ep_max_recv_rows > 0 ? cfg->ep_max_recv_rows : (long long)world * h->Tmax * k;
-    if (world == 1) recv = (long long)h->Tmax * k;
-    const long long rcap = (recv + (long long)h->El * 127 + 127) / 128 * 128;
+    h->n_waves = 1;
+    if (world > 1) {
+        const int want = cfg->ep_waves > 0 ? cfg->ep_waves : h->Tmax / 8192;
+        h->n_waves = std::max(1, std::min(MAX_WAVES, want));
+    }
+    // worst case per wave: every token of the wave, from every rank, picks experts of this rank
+    const long long tw_max = round_up((h->Tmax + h->n_waves - 1) / h->n_waves, route::TILE_TOKENS);
+    long long recv = world == 1 ? (long long)h->Tmax * k
+                                : (cfg->ep_max_recv_rows > 0 ? (cfg->ep_max_recv_rows + h->n_waves - 1) / h->n_waves
+                                                             : (long long)world * tw_max * k);
+    const long long rw = (recv + (long long)h->El * 127 + 127) / 128 * 128;
+    const long long rcap = rw * h->n_waves;
     if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30))
         return fail(PRICHS_ERR_CAPACITY, "workspace for max_tokens=%d is too large", h->Tmax);
     h->Rcap = (int)rcap;
+    h->Rw = (int)rw;
     h->sm_count = prop.multiProcessorCount;
 
     int rc = PRICHS_OK;
@@ -374,7 +611,12 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
     A(dalloc(&h->status, 1));
     A(dalloc(&h->meta, 1));
-    A(dalloc(&h->ep_token, 2 * route::MAX_RANKS + 8));
+    A(dalloc(&h->ep_zero, 8));
+    for (int w = 0; w < h->n_waves && world > 1; ++w) {
+        A(dalloc(&h->wave[w].meta, 1));
+        A(dalloc(&h->wave[w].mtile_slot, (size_t)h->Rw / 128 + 1));
+        A(dalloc(&h->wave[w].token, 2 * route::MAX_RANKS));
+    }
     if (rc != PRICHS_OK) {
         prichs_moe_destroy(h);
         return rc;
@@ -382,7 +624,11 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
     cudaMemset(h->status, 0, sizeof(int));
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
-    cudaMemset(h->ep_token, 0, (2 * route::MAX_RANKS + 8) * sizeof(int));
+    cudaMemset(h->ep_zero, 0, 8 * sizeof(int));
+    for (int w = 0; w < h->n_waves && world > 1; ++w) {
+        cudaMemset(h->wave[w].meta, 0, sizeof(route::RouteMeta));
+        cudaMemset(h->wave[w].token, 0, 2 * route::MAX_RANKS * sizeof(int));
+    }
     for (int i = 0; i < route::MAX_RANKS; ++i) {
         h->xp_peer[i] = h->xp;
         h->y_peer[i] = h->ybuf;
@@ -422,12 +668,20 @@ int prichs_moe_destroy(prichs_moe_t* h) {
             if (h->xp_peer[r]) cudaIpcCloseMemHandle(h->xp_peer[r]);
             if (h->y_peer[r]) cudaIpcCloseMemHandle(h->y_peer[r]);
         }
-        if (h->comm && nccl().ok) nccl().comm_destroy(h->comm);
         if (h->side_stream) cudaStreamDestroy(h->side_stream);
-        if (h->ev_fork) cudaEventDestroy(h->ev_fork);
-        if (h->ev_join) cudaEventDestroy(h->ev_join);
+        if (h->ev_router) cudaEventDestroy(h->ev_router);
+        if (h->ev_shared) cudaEventDestroy(h->ev_shared);
     }
-    void* ptrs[] = {h->ep_token, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
+    for (int w = 0; w < MAX_WAVES; ++w) {
+        EpWave& wv = h->wave[w];
+        if (wv.comm && nccl().ok) nccl().comm_destroy(wv.comm);
+        if (wv.stream) cudaStreamDestroy(wv.stream);
+        if (wv.done) cudaEventDestroy(wv.done);
+        if (wv.meta) cudaFree(wv.meta);
+        if (wv.mtile_slot) cudaFree(wv.mtile_slot);
+        if (wv.token) cudaFree(wv.token);
+    }
+    void* ptrs[] = {h->ep_zero, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
                     h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
                     h->stage_r, h->stage_y};
     for (void* p : ptrs)
@@ -542,7 +796,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         return fail(PRICHS_ERR_BAD_ARG, "activation pointers must be 16-byte aligned");
     DeviceGuard guard(h->device);
 
-    const int d = h->d, f = h->f, E = h->E;
+    const int E = h->E;
     // routing results of this call start at token `tok_base` of the stash arrays (non-zero only while the
     // host-buffer entry point feeds a batch through in chunks)
     float* logits = h->logits + (size_t)h->tok_base * route::MAX_E;
@@ -551,6 +805,8 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     int* pos = h->pos + (size_t)h->tok_base * 2;
     route::ConceptBias cb;
     for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = (e < n_concept && e < E) ? concept_bias[e] : 0.0f;
+
+    if (h->world > 1) return forward_ep(h, x_dev, x_dtype, resid_dev, cb, y_dev, y_dtype, T, st);
 
     const bool f32mode = h->mode == PRICHS_MODE_F32;
     const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
@@ -566,116 +822,35 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     mark();
     // 1. router
-    if (f32mode) {
-        route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
-                                                        logits, sel, gates, h->tile_counts);
-    } else {
-        const int grid = ntiles;
-        constexpr int RT = route::ROUTER_WARPS * 32;
-        if (x_dtype == PRICHS_DTYPE_F32) {
-            if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
-            else
-                route::router_mma_kernel<3, true><<<grid, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
-        } else {
-            if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
-            else
-                route::router_mma_kernel<3, false><<<grid, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, h->tile_counts);
-        }
-    }
-    LAUNCH_CHECK("router");
+    rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st);
+    if (rc != PRICHS_OK) return rc;
     mark();
-    // Arguments of the two grouped GEMMs (gate|up + SwiGLU, then down); they depend on host values only.
-    egemm::Args a1;
-    memset(&a1, 0, sizeof(a1));
-    a1.nk = d / egemm::BK;
-    a1.split3 = f32mode;
-    a1.n_ntiles = f / 128;
-    a1.shared_mtiles = (T + 127) / 128;
-    a1.routed_base_tiles = h->Tcap / 128;
-    a1.a_routed_tile_off = 0;
-    a1.n_routed_mtiles = &h->meta->n_routed_mtiles;
-    a1.mtile_slot = h->mtile_slot;
-    a1.w_rows = 2 * f;
-    a1.out_split = f32mode;
-    a1.out_lo_off = f;
-    a1.out_f32 = 0;
-    a1.status = h->status;
-    egemm::Args a2 = a1;
-    a2.nk = f / egemm::BK;
-    a2.n_ntiles = d / egemm::BN;
-    a2.a_routed_tile_off = h->Tcap / 128;
-    a2.w_rows = d;
-    a2.out_split = 0;
-    a2.out_f32 = f32mode;
-    const bool ep = h->world > 1;
-    if (ep) {
-        // The shared expert needs no exchange: its two GEMMs run on a side stream while the main stream
-        // gathers counts, plans, dispatches rows over NVLink and waits for the peers.
-        egemm::Args s1 = a1, s2 = a2;
-        s1.n_routed_mtiles = s2.n_routed_mtiles = h->ep_token + 2 * route::MAX_RANKS;  // a device zero
-        CUDA_TRY(cudaEventRecord(h->ev_fork, st));
-        CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_fork, 0));
-        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, s1);
-        LAUNCH_CHECK("shared gate/up GEMM");
-        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, s2);
-        LAUNCH_CHECK("shared down GEMM");
-        CUDA_TRY(cudaEventRecord(h->ev_join, h->side_stream));
-        a1.shared_mtiles = a2.shared_mtiles = 0;  // the main-stream launches cover the routed rows only
-    }
     // 2. prefix sums + placement plan
-    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, h->world, h->rank,
-                                           h->Rcap, ep ? 0 : 1, h->status);
+    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0, h->Rcap, 1,
+                                           h->status);
     LAUNCH_CHECK("scan");
-    if (ep) {
-        // every rank contributes its 8 counts (row `rank` of the matrix, in place), then builds the same plan
-        int* cmat = h->meta->cmat;
-        NCCL_TRY(nccl().all_gather(cmat + h->rank * route::MAX_E, cmat, route::MAX_E, NCCL_INT32, h->comm, st));
-        route::plan_kernel<<<1, 256, 0, st>>>(h->meta, h->mtile_slot, E, h->El, h->world, h->rank, h->Rcap, h->status);
-        LAUNCH_CHECK("plan");
-    }
     mark();
     // 3. dispatch
     route::PeerPtrs xp_peers, y_peers;
     for (int i = 0; i < route::MAX_RANKS; ++i) {
-        xp_peers.p[i] = h->xp_peer[i];
-        y_peers.p[i] = h->y_peer[i];
+        xp_peers.p[i] = h->xp;
+        y_peers.p[i] = h->ybuf;
     }
     route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, sel, h->tile_prefix, h->meta, xp_peers, h->El, pos);
     LAUNCH_CHECK("dispatch");
-    // barrier: every rank's rows have landed in the owners' buffers before any expert GEMM reads them
-    if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + h->rank, h->ep_token, 1, NCCL_INT32, h->comm, st));
     mark();
-    // 4. gate|up GEMM + SwiGLU (shared + routed experts; routed only in expert-parallel mode)
+    // 4. gate|up GEMM + SwiGLU for the shared and all routed experts, 5. down GEMM
+    egemm::Args a1, a2;
+    gemm_args(h, T, 0, &h->meta->n_routed_mtiles, h->mtile_slot, &a1, &a2);
     egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
     LAUNCH_CHECK("gate/up GEMM");
     mark();
-    // 5. down GEMM
     egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
     LAUNCH_CHECK("down GEMM");
     mark();
-    if (ep) CUDA_TRY(cudaStreamWaitEvent(st, h->ev_join, 0));  // shared-expert rows are complete
-    // barrier: every owner's expert outputs are complete before the combine gathers them over NVLink
-    if (ep) NCCL_TRY(nccl().all_gather(h->ep_token + route::MAX_RANKS + h->rank, h->ep_token + route::MAX_RANKS, 1, NCCL_INT32, h->comm, st));
     // 6. combine (+ residual)
-    {
-        const int grid = (T + 7) / 8;
-        const long long rb = h->Tcap;
-        const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
-        const bool of32 = y_dtype == PRICHS_DTYPE_F32;
-#define COMBINE(YF, OF, RS) \
-    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(h->ybuf, y_peers, rb, sel, gates, pos, resid_dev, y_dev, T, d, h->El)
-        if (f32mode) {
-            if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
-            else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
-        } else {
-            if (of32) { if (res == 0) COMBINE(false, true, 0); else if (res == 1) COMBINE(false, true, 1); else COMBINE(false, true, 2); }
-            else      { if (res == 0) COMBINE(false, false, 0); else if (res == 1) COMBINE(false, false, 1); else COMBINE(false, false, 2); }
-        }
-#undef COMBINE
-        LAUNCH_CHECK("combine");
-    }
+    rc = launch_combine(h, h->ybuf, y_peers, h->Tcap, sel, gates, pos, resid_dev, y_dev, x_dtype, y_dtype, T, st);
+    if (rc != PRICHS_OK) return rc;
     mark();
     h->ev_valid = timing;
     return PRICHS_OK;
@@ -856,7 +1031,8 @@ int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_
 int prichs_moe_ep_unique_id(void* id128) {
     if (!id128) return fail(PRICHS_ERR_BAD_ARG, "null id buffer");
     if (!nccl().ok) return fail(PRICHS_ERR_COMM, "libnccl.so.2 could not be loaded");
-    NCCL_TRY(nccl().get_unique_id(id128));
+    memset(id128, 0, PRICHS_EP_ID_BYTES);
+    for (int w = 0; w < MAX_WAVES; ++w) NCCL_TRY(nccl().get_unique_id(static_cast<char*>(id128) + 128 * w));
     return PRICHS_OK;
 }
 
@@ -888,12 +1064,17 @@ int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs
         h->xp_peer[r] = pxp;
         h->y_peer[r] = py;
     }
-    NcclApi::Id128 id;
-    memcpy(&id, id128, sizeof(id));
-    NCCL_TRY(nccl().comm_init_rank(&h->comm, h->world, id, h->rank));
+    static_assert(MAX_WAVES * 128 <= PRICHS_EP_ID_BYTES, "one 128-byte communicator id per wave");
+    for (int w = 0; w < h->n_waves; ++w) {
+        NcclApi::Id128 id;
+        memcpy(&id, static_cast<const char*>(id128) + 128 * w, sizeof(id));
+        NCCL_TRY(nccl().comm_init_rank(&h->wave[w].comm, h->world, id, h->rank));
+        CUDA_TRY(cudaStreamCreateWithFlags(&h->wave[w].stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaEventCreateWithFlags(&h->wave[w].done, cudaEventDisableTiming));
+    }
     CUDA_TRY(cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking));
-    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
-    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_router, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&h->ev_shared, cudaEventDisableTiming));
     h->ep_ready = true;
     return PRICHS_OK;
 }

@@ -49,7 +49,7 @@ def connect(layer, dist, max_tokens: int):
     layer._want_max_tokens = max(layer._want_max_tokens, int(max_tokens))
     layer._ensure(int(max_tokens))
     rank, world = dist.get_rank(), dist.get_world_size()
-    ident = (C.c_char * 128)()
+    ident = (C.c_char * 1024)()
     if rank == 0:
         rc = L.prichs_moe_ep_unique_id(ident)
         if rc != 0:

@@ -66,7 +66,7 @@ class MoEStash:
 class MoELayer:
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int, top_k: int, *, seed=None,
                  mode: str = "bf16", max_tokens: int = 0, device: int = -1, ep_world: int = 1, ep_rank: int = 0,
-                 ep_max_recv_rows: int = 0, init: bool = True):
+                 ep_max_recv_rows: int = 0, ep_waves: int = 0, init: bool = True):
         rng = np.random.default_rng(seed)
         self.hidden_dim, self.intermediate_dim = int(hidden_dim), int(intermediate_dim)
         self.top_k = int(top_k)
@@ -83,6 +83,7 @@ class MoELayer:
         self._bias_host = np.zeros(num_experts, np.float32)
         self.mode = {"bf16": _capi.MODE_BF16, "f32": _capi.MODE_F32}[mode]
         self._device, self._ep_world, self._ep_rank, self._ep_max_recv = device, ep_world, ep_rank, ep_max_recv_rows
+        self._ep_waves = int(ep_waves)
         self._h = C.c_void_p()
         self._max_tokens = 0
         self._want_max_tokens = int(max_tokens)
@@ -146,7 +147,7 @@ class MoELayer:
             self.close()
             cap = max(T, self._want_max_tokens, 1)
             cfg = _capi.Config(self.hidden_dim, self.intermediate_dim, self._num_experts, self.top_k, cap, self.mode,
-                               self._device, self._ep_world, self._ep_rank, self._ep_max_recv)
+                               self._device, self._ep_world, self._ep_rank, self._ep_max_recv, self._ep_waves)
             h = C.c_void_p()
             _check(L.prichs_moe_create(C.byref(cfg), C.byref(h)))
             self._h, self._max_tokens, self._weights_dirty = h, cap, True

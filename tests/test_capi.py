@@ -37,7 +37,7 @@ def test_bad_arguments_are_rejected_before_touching_a_device(capi):
     for bad in (dict(hidden_dim=100), dict(intermediate_dim=100), dict(num_experts=9), dict(top_k=3),
                 dict(num_experts=1, top_k=2), dict(max_tokens=0), dict(mode=7), dict(ep_world=3)):
         base = dict(hidden_dim=256, intermediate_dim=128, num_experts=8, top_k=2, max_tokens=64, mode=0, device=-1,
-                    ep_world=1, ep_rank=0, ep_max_recv_rows=0)
+                    ep_world=1, ep_rank=0, ep_max_recv_rows=0, ep_waves=0)
         base.update(bad)
         cfg = capi.Config(**base)
         rc = L.prichs_moe_create(C.byref(cfg), C.byref(h))
