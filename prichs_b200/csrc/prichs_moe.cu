@@ -14,11 +14,13 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 #include <vector>
 
 #include "../../include/prichs_moe.h"
+#include "expert_gemm_pair_sm100.cuh"
 #include "expert_gemm_sm100.cuh"
 #include "route_sm100.cuh"
 
@@ -179,6 +181,9 @@ __global__ void compat_swiglu_kernel(const float* __restrict__ gate, const float
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// Every expert's segment of a permuted region starts on a multiple of this many rows (one CTA-pair tile).
+constexpr int SEG_PAD = 256;
+
 // ---- NCCL, loaded at run time (control plane of the expert-parallel mode only) -------------------------
 // Only five entry points with a stable ABI are used; the library is opened by soname so that a process
 // that already carries an NCCL (for example through torch) shares it.
@@ -256,6 +261,8 @@ struct prichs_moe {
     route::RouteMeta* meta;
     CUtensorMap tm_xp, tm_wgu, tm_h, tm_wdn;
     CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
+    CUtensorMap tm_wgu_half, tm_wdn_half;  // 128-row boxes: one CTA's half of a B tile in the CTA-pair kernel
+    bool pair_gemm;  // use the CTA-pair (cta_group::2) GEMM kernel
 
     // expert-parallel group: peers' receive / output buffers mapped into this process, and the token waves
     bool ep_ready;
@@ -368,6 +375,25 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
     a2->out_f32 = f32mode;
 }
 
+// One grouped-GEMM launch: epi 0 = gate|up + SwiGLU into H, epi 1 = down projection into Y.
+int launch_expert_gemm(prichs_moe* h, int epi, const CUtensorMap& tm_a_shared, const CUtensorMap& tm_a_routed, const egemm::Args& a,
+                       int grid, cudaStream_t st) {
+    if (h->pair_gemm) {
+        const int g2 = std::max(2, grid & ~1);  // whole CTA pairs
+        if (epi == 0)
+            egemm::expert_gemm_pair_kernel<egemm::EPI_SWIGLU><<<g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wgu_half, h->tm_h_out, a);
+        else
+            egemm::expert_gemm_pair_kernel<egemm::EPI_PLAIN><<<g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wdn_half, h->tm_y_out, a);
+    } else {
+        if (epi == 0)
+            egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wgu, h->tm_h_out, a);
+        else
+            egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wdn, h->tm_y_out, a);
+    }
+    LAUNCH_CHECK(epi == 0 ? "gate/up GEMM" : "down GEMM");
+    return PRICHS_OK;
+}
+
 // Combine of T tokens whose shared-expert rows start at `y_shared` and whose routing arrays / residual / output
 // are the caller's (already offset) pointers.
 int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y_peers, long long routed_base_rows, const int* sel,
@@ -462,10 +488,10 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         egemm::Args s1, s2;
         gemm_args(h, T, 0, h->ep_zero, h->wave[0].mtile_slot, &s1, &s2);
         CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_router, 0));
-        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, s1);
-        LAUNCH_CHECK("shared gate/up GEMM");
-        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, h->side_stream>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, s2);
-        LAUNCH_CHECK("shared down GEMM");
+        rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, s1, gemm_grid, h->side_stream);
+        if (rc != PRICHS_OK) return rc;
+        rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, s2, gemm_grid, h->side_stream);
+        if (rc != PRICHS_OK) return rc;
         CUDA_TRY(cudaEventRecord(h->ev_shared, h->side_stream));
     }
 
@@ -486,10 +512,10 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_router, 0));
         // counts of this rank's wave -> all-gather (row `rank` of the matrix, in place) -> the same plan everywhere
         route::scan_kernel<<<1, 1024, 0, ws>>>(h->tile_counts + (size_t)tile0 * route::MAX_E, tprefix, ntl, wv.meta, wv.mtile_slot, E, h->El,
-                                               h->world, h->rank, h->Rw, 0, h->status);
+                                               h->world, h->rank, h->Rw, 0, SEG_PAD, h->status);
         LAUNCH_CHECK("scan");
         NCCL_TRY(nccl().all_gather(wv.meta->cmat + h->rank * route::MAX_E, wv.meta->cmat, route::MAX_E, NCCL_INT32, wv.comm, ws));
-        route::plan_kernel<<<1, 256, 0, ws>>>(wv.meta, wv.mtile_slot, E, h->El, h->world, h->rank, h->Rw, h->status);
+        route::plan_kernel<<<1, 256, 0, ws>>>(wv.meta, wv.mtile_slot, E, h->El, h->world, h->rank, h->Rw, SEG_PAD, h->status);
         LAUNCH_CHECK("plan");
         // dispatch: rows go straight into the owners' receive regions of this wave (peer memory over NVLink)
         route::PeerPtrs xp_peers, y_peers;
@@ -505,10 +531,10 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
         egemm::Args a1, a2;
         gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, &a1, &a2);
-        egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, ws>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
-        LAUNCH_CHECK("gate/up GEMM");
-        egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<gemm_grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, ws>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
-        LAUNCH_CHECK("down GEMM");
+        rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, gemm_grid, ws);
+        if (rc != PRICHS_OK) return rc;
+        rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, gemm_grid, ws);
+        if (rc != PRICHS_OK) return rc;
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_shared, 0));  // the shared expert's rows are complete
         // barrier: every owner's outputs of this wave are complete before the combine gathers them over NVLink
         NCCL_TRY(nccl().all_gather(wv.token + route::MAX_RANKS + h->rank, wv.token + route::MAX_RANKS, 1, NCCL_INT32, wv.comm, ws));
@@ -565,7 +591,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     h->world = world; h->rank = cfg->ep_rank; h->El = E / world; h->n_slots = 1 + h->El;
     const int mul = h->mode == PRICHS_MODE_F32 ? 2 : 1;
     h->K1 = d * mul; h->K2 = f * mul;
-    h->Tcap = round_up(h->Tmax, 128);
+    h->Tcap = round_up(h->Tmax, SEG_PAD);
     h->n_waves = 1;
     if (world > 1) {
         const int want = cfg->ep_waves > 0 ? cfg->ep_waves : h->Tmax / 8192;
@@ -576,7 +602,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     long long recv = world == 1 ? (long long)h->Tmax * k
                                 : (cfg->ep_max_recv_rows > 0 ? (cfg->ep_max_recv_rows + h->n_waves - 1) / h->n_waves
                                                              : (long long)world * tw_max * k);
-    const long long rw = (recv + (long long)h->El * 127 + 127) / 128 * 128;
+    const long long rw = (recv + (long long)h->El * (SEG_PAD - 1) + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
     const long long rcap = rw * h->n_waves;
     if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30))
         return fail(PRICHS_ERR_CAPACITY, "workspace for max_tokens=%d is too large", h->Tmax);
@@ -640,12 +666,23 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(make_tmap(&h->tm_wgu, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, egemm::BN));
     A(make_tmap(&h->tm_h, h->hbuf, rows_all, h->K2, egemm::BM));
     A(make_tmap(&h->tm_wdn, h->w_dn, (size_t)h->n_slots * d, h->K2, egemm::BN));
+    A(make_tmap(&h->tm_wgu_half, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, 128));
+    A(make_tmap(&h->tm_wdn_half, h->w_dn, (size_t)h->n_slots * d, h->K2, 128));
     A(make_tmap(&h->tm_h_out, h->hbuf, rows_all, h->K2, 32));
     A(make_tmap(&h->tm_y_out, h->ybuf, rows_all, d, 32, h->mode == PRICHS_MODE_F32));
     if (rc == PRICHS_OK) {
         if (cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(egemm::expert_gemm_kernel<egemm::EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::SMEM_BYTES) != cudaSuccess)
             rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the expert GEMM", egemm::SMEM_BYTES);
+        if (cudaFuncSetAttribute(egemm::expert_gemm_pair_kernel<egemm::EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::PAIR_SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(egemm::expert_gemm_pair_kernel<egemm::EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, egemm::PAIR_SMEM_BYTES) != cudaSuccess)
+            rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the CTA-pair expert GEMM", egemm::PAIR_SMEM_BYTES);
+    }
+    {
+        // The CTA-pair kernel (256 x 256 tiles over two SMs) is the default; PRICHS_GEMM=single selects the
+        // one-CTA kernel (128 x 256 tiles), kept for comparison.
+        const char* sel = getenv("PRICHS_GEMM");
+        h->pair_gemm = !(sel && strcmp(sel, "single") == 0);
     }
     for (int i = 0; i < 7 && rc == PRICHS_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "cudaEventCreate failed");
@@ -827,7 +864,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     mark();
     // 2. prefix sums + placement plan
     route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0, h->Rcap, 1,
-                                           h->status);
+                                           SEG_PAD, h->status);
     LAUNCH_CHECK("scan");
     mark();
     // 3. dispatch
@@ -842,11 +879,11 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     // 4. gate|up GEMM + SwiGLU for the shared and all routed experts, 5. down GEMM
     egemm::Args a1, a2;
     gemm_args(h, T, 0, &h->meta->n_routed_mtiles, h->mtile_slot, &a1, &a2);
-    egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_x, h->tm_xp, h->tm_wgu, h->tm_h_out, a1);
-    LAUNCH_CHECK("gate/up GEMM");
+    rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, h->sm_count, st);
+    if (rc != PRICHS_OK) return rc;
     mark();
-    egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(h->tm_h, h->tm_h, h->tm_wdn, h->tm_y_out, a2);
-    LAUNCH_CHECK("down GEMM");
+    rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, h->sm_count, st);
+    if (rc != PRICHS_OK) return rc;
     mark();
     // 6. combine (+ residual)
     rc = launch_combine(h, h->ybuf, y_peers, h->Tcap, sel, gates, pos, resid_dev, y_dev, x_dtype, y_dtype, T, st);
@@ -885,7 +922,7 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
         int rc = dalloc(&h->stage_x, n);
         if (rc == PRICHS_OK) rc = dalloc(&h->stage_y, n);
         if (rc == PRICHS_OK) rc = dalloc(&h->counts_acc, route::MAX_E);
-        if (rc != PRICHS_OK) return rc;
+    if (rc != PRICHS_OK) return rc;
         CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
         CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
         CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
@@ -894,7 +931,7 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     }
     if (resid_host && !h->stage_r) {
         int rc = dalloc(&h->stage_r, n);
-        if (rc != PRICHS_OK) return rc;
+    if (rc != PRICHS_OK) return rc;
     }
     // Tokens are independent, so a large batch is fed through in chunks: the upload of chunk i+1 and the
     // download of chunk i-1 overlap the kernels of chunk i (three streams). Results are bit-identical to one
@@ -1259,7 +1296,7 @@ extern "C" int prichs_moe_route_static(const void* x_dev, const float* router_de
                                                                         gates2, tcount);
     LAUNCH_CHECK("router");
     const int cap_rows = (int)((RS_MAX_T * 2 + route::MAX_E * 128) / 128 * 128);
-    route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, E, E, 1, 0, cap_rows, 1, status);
+    route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, E, E, 1, 0, cap_rows, 1, 128, status);
     LAUNCH_CHECK("scan");
     route_static_export_kernel<<<(T + 255) / 256, 256, 0, st>>>(logits8, sel2, gates2, meta, T, E, top_k, logits_dev, selected_dev,
                                                                gating_dev, counts_dev);

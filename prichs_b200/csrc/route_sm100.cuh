@@ -294,10 +294,10 @@ router_f32_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, c
 // ---------------------------------------------------------------------------------------------------
 // Placement plan from the counts matrix (one CTA). For every expert e, owned by rank e / El:
 //   total[e] = sum_s cmat[s][e],  src_off[e] = sum_{s < rank} cmat[s][e],
-//   seg_base[e] = sum of the 128-padded totals of the owner's lower experts.
+//   seg_base[e] = sum of the padded totals (to pad_rows, a multiple of 128) of the owner's lower experts.
 // For the local experts it also fills the m-tile -> weight-slot table the grouped GEMM walks.
 __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El,
-                                               int world, int rank, int cap_rows, int* __restrict__ status) {
+                                               int world, int rank, int cap_rows, int pad_rows, int* __restrict__ status) {
     __shared__ int s_total[MAX_E], s_base[MAX_E + 1];
     const int tid = threadIdx.x;
     if (tid < MAX_E) {
@@ -325,7 +325,7 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
                     s_base[le] = base;
                     recv += s_total[e];
                 }
-                base += (s_total[e] + 127) & ~127;
+                base += (s_total[e] + pad_rows - 1) / pad_rows * pad_rows;
             }
             if (o == rank) {
                 s_base[El] = base;
@@ -353,7 +353,7 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
 __global__ void __launch_bounds__(1024)
 scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, int ntiles, RouteMeta* meta,
             int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
-            int* __restrict__ status) {
+            int pad_rows, int* __restrict__ status) {
     __shared__ int warp_tot[32][MAX_E];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per = (ntiles + 1023) / 1024;
@@ -411,15 +411,15 @@ scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, 
     }
     if (fuse_plan) {
         __syncthreads();
-        plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, status);
+        plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status);
     }
 }
 
 // Placement plan as its own launch (expert-parallel mode, after the counts of all ranks were gathered).
 __global__ void __launch_bounds__(256)
 plan_kernel(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows,
-            int* __restrict__ status) {
-    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, status);
+            int pad_rows, int* __restrict__ status) {
+    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status);
 }
 
 // ---------------------------------------------------------------------------------------------------

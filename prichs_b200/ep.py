@@ -20,17 +20,20 @@ def owner_of(expert: int, num_experts: int, world: int) -> int:
     return expert // (num_experts // world)
 
 
-def plan(cmat: np.ndarray, rank: int):
+SEG_PAD = 256  # rows; every expert's segment starts on a multiple of it (one CTA-pair GEMM tile)
+
+
+def plan(cmat: np.ndarray, rank: int, pad: int = SEG_PAD):
     """cmat[s, e] = assignments rank s produced for expert e. Returns total[e], src_off[e] (rows of lower ranks
-    ahead of `rank` inside expert e's segment), seg_base[e] (128-padded start of the segment in the owner's
-    buffer), recv_rows and n_mtiles of `rank`."""
+    ahead of `rank` inside expert e's segment), seg_base[e] (start of the segment in the owner's buffer, segments
+    padded to `pad` rows), recv_rows and n_mtiles (128-row tiles) of `rank`."""
     cmat = np.asarray(cmat, np.int64)
     world, E = cmat.shape
     El = E // world
     total = cmat.sum(axis=0)
     src_off = cmat[:rank].sum(axis=0)
     seg_base = np.zeros(E, np.int64)
-    padded = (total + 127) // 128 * 128
+    padded = (total + pad - 1) // pad * pad
     for o in range(world):
         base = 0
         for le in range(El):

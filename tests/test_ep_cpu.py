@@ -64,7 +64,7 @@ def _worker(rank, world, port, ret):
         for le in range(El):
             e = rank * El + le
             lo, n = int(mine["seg_base"][e]), int(mine["total"][e])
-            assert lo % 128 == 0 and filled[lo:lo + n].all() and not filled[lo + n:lo + (n + 127) // 128 * 128].any()
+            assert lo % 256 == 0 and filled[lo:lo + n].all() and not filled[lo + n:lo + (n + 255) // 256 * 256].any()
             if n:
                 h = O.swiglu(O.matmul_2d(xp[lo:lo + n], ws[4 + 3 * e]), O.matmul_2d(xp[lo:lo + n], ws[5 + 3 * e]))
                 yp[lo:lo + n] = O.matmul_2d(h, ws[6 + 3 * e])
@@ -118,5 +118,5 @@ def test_plan_properties():
             offs = [int(plans[r]["src_off"][e]) for r in range(world)]
             assert offs == np.concatenate([[0], np.cumsum(cmat[:-1, e])]).tolist()
             assert all(int(pl["seg_base"][e]) == int(plans[o]["seg_base"][e]) for pl in plans)
-            assert plans[o]["seg_base"][e] % 128 == 0
+            assert plans[o]["seg_base"][e] % 256 == 0
         assert sum(pl["recv_rows"] for pl in plans) == int(cmat.sum())

@@ -133,7 +133,7 @@ def test_ragged_token_counts(torch_cuda, oracle, T):
 
 
 def test_dispatch_layout_and_intermediates(torch_cuda, oracle):
-    """Stage by stage: permutation rows are exact copies in ascending token order inside 128-aligned segments;
+    """Stage by stage: permutation rows are exact copies in ascending token order inside 256-aligned segments;
     H and Y of the shared expert match the oracle's intermediates."""
     from prichs_b200 import synth
     d, f, E, k, T = 256, 128, 8, 2, 200
@@ -144,7 +144,7 @@ def test_dispatch_layout_and_intermediates(torch_cuda, oracle):
     meta = m.debug_buffer(5, 4 * 36).view(np.int32)
     assert np.array_equal(meta[0:8], counts)
     seg_base = meta[8:16]
-    pad = (counts + 127) // 128 * 128
+    pad = (counts + 255) // 256 * 256  # segments are padded to one CTA-pair tile
     assert np.array_equal(seg_base, np.concatenate([[0], np.cumsum(pad)[:-1]]))
     assert meta[32] == pad.sum() // 128 and meta[34] == 0
     pos = m.debug_buffer(4, T * 2 * 4).view(np.int32).reshape(T, 2)
@@ -159,7 +159,7 @@ def test_dispatch_layout_and_intermediates(torch_cuda, oracle):
     exp_slots = np.concatenate([np.full(pad[e] // 128, e) for e in range(E)]).astype(np.int32)
     assert np.array_equal(slots, exp_slots)
     # shared expert intermediates
-    Tcap = (m.token_capacity + 127) // 128 * 128
+    Tcap = (m.token_capacity + 255) // 256 * 256
     H = synth.from_bf16_bits(m.debug_buffer(2, T * f * 2).view(np.uint16)).reshape(T, f)
     Hexp = oracle.swiglu(oracle.matmul_2d(x, ws[1]), oracle.matmul_2d(x, ws[2]))
     assert_close(H, Hexp, 1e-2, "shared H")
