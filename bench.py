@@ -239,7 +239,21 @@ def main():
         launches = int(L.prichs_kernel_launches() - launches0)
         ms_total = e0.elapsed_time(e1)
         # stage breakdown: the library records CUDA events on the launching stream between its kernels
-        stage = None
+        stage, timeline = None, None
+        if world > 1:
+            import ctypes as C
+            L.prichs_moe_enable_timing(layer._h, 1)
+            for i in range(3):
+                step(i)
+            tlb = (C.c_float * 34)()
+            if L.prichs_moe_get_ep_timeline(layer._h, tlb, 34) == 0:
+                v = [round(float(x), 4) for x in tlb]
+                nw = max(1, min(4, T // 8192))
+                timeline = {"ms_since_router": {"shared_gate_up": v[0], "shared_down": v[1]},
+                            "marks": ["scan", "plan", "dispatched", "rows_landed", "gate_up", "down", "outputs_ready", "combined"],
+                            "waves": [v[2 + 8 * w: 10 + 8 * w] for w in range(nw)]}
+            L.prichs_moe_enable_timing(layer._h, 0)
+            torch.cuda.synchronize(dev)
         if world == 1:  # (the expert-parallel forward overlaps its kernels on several streams: no per-stage split)
             L.prichs_moe_enable_timing(layer._h, 1)
             stage = np.zeros(6, np.float64)
@@ -324,7 +338,7 @@ def main():
         "e2e": {"value": tokens * e2e_steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 4,
                 "d2h_bytes_per_step": T * D * 4, "steps": e2e_steps,
                 "api": "MoELayer.forward(numpy fp32 [T,d]) -> prichs_moe_forward_host, pinned host buffers"},
-        "gpu_launches": launches, "roofline": roofline, "stages": stages,
+        "gpu_launches": launches, "roofline": roofline, "stages": stages, "ep_timeline": timeline,
         "layer_tflops": tokens * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,
         "clocks": clocks.summary(),
     }

@@ -184,6 +184,12 @@ PRICHS_API int64_t prichs_kernel_launches(void);
 PRICHS_API int prichs_moe_enable_timing(prichs_moe_t* h, int on);
 PRICHS_API int prichs_moe_get_stage_ms(prichs_moe_t* h, float* ms6);
 
+/* Expert-parallel timeline of the last forward (timing enabled): device times in milliseconds since the router
+ * finished, ms[0..1] = shared gate|up done, shared down done; then for every wave w eight marks at
+ * ms[2 + 8 w + i]: i = 0 counts scanned, 1 plan ready, 2 rows dispatched, 3 all ranks' rows landed, 4 gate|up
+ * done, 5 down done, 6 all ranks' outputs ready, 7 combined. n must be at least 2 + 8 * waves. */
+PRICHS_API int prichs_moe_get_ep_timeline(prichs_moe_t* h, float* ms, int n);
+
 /* Copies `bytes` bytes at `offset_bytes` of one internal device buffer of the last forward to the host (waits
  * for the handle's last stream). For tests and diagnostics of the intermediate stages; the reference exposes
  * the same intermediates as the stash vectors of forward_train (moe.rs:32-53).

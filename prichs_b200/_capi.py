@@ -45,6 +45,7 @@ SYMBOLS = {
     "prichs_kernel_launches": (C.c_int64, []),
     "prichs_moe_enable_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "prichs_moe_get_stage_ms": (C.c_int, [C.c_void_p, _fp]),
+    "prichs_moe_get_ep_timeline": (C.c_int, [C.c_void_p, _fp, C.c_int]),
     "prichs_moe_debug_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t]),
     "prichs_moe_route_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -238,6 +238,7 @@ struct EpWave {
     int* mtile_slot;
     int* token;  // [2][MAX_RANKS] ints: payload of the two barrier all-gathers
     cudaEvent_t done;
+    cudaEvent_t tl[8];  // timeline marks (timing enabled): scan, plan, dispatch, rows landed, gate|up, down, outputs ready, combine
 };
 
 struct prichs_moe {
@@ -274,6 +275,7 @@ struct prichs_moe {
     int* ep_zero;              // a device int that stays zero (the "no permuted tiles" count of the shared launches)
     cudaStream_t side_stream;  // shared-expert GEMMs of the expert-parallel mode
     cudaEvent_t ev_router, ev_shared;
+    cudaEvent_t tl_base, tl_side[2];  // timeline: router done; shared gate|up done, shared down done
 
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
@@ -287,6 +289,7 @@ struct prichs_moe {
     bool timing;
     cudaEvent_t ev[7];
     bool ev_valid;
+    bool tl_valid;  // the expert-parallel timeline events of the last forward are recorded
 };
 
 namespace {
@@ -482,6 +485,8 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     rc = launch_router(h, x_dev, x_dtype, cb, T, h->logits, h->sel, h->gates, h->tile_counts, st);
     if (rc != PRICHS_OK) return rc;
     CUDA_TRY(cudaEventRecord(h->ev_router, st));
+    const bool tl = h->timing;
+    if (tl) CUDA_TRY(cudaEventRecord(h->tl_base, st));
 
     // 2. the shared expert needs no exchange: both of its GEMMs run on the side stream
     {
@@ -490,8 +495,10 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_router, 0));
         rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, s1, gemm_grid, h->side_stream);
         if (rc != PRICHS_OK) return rc;
+        if (tl) cudaEventRecord(h->tl_side[0], h->side_stream);
         rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, s2, gemm_grid, h->side_stream);
         if (rc != PRICHS_OK) return rc;
+        if (tl) cudaEventRecord(h->tl_side[1], h->side_stream);
         CUDA_TRY(cudaEventRecord(h->ev_shared, h->side_stream));
     }
 
@@ -514,9 +521,11 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         route::scan_kernel<<<1, 1024, 0, ws>>>(h->tile_counts + (size_t)tile0 * route::MAX_E, tprefix, ntl, wv.meta, wv.mtile_slot, E, h->El,
                                                h->world, h->rank, h->Rw, 0, SEG_PAD, h->status);
         LAUNCH_CHECK("scan");
+        if (tl) cudaEventRecord(wv.tl[0], ws);
         NCCL_TRY(nccl().all_gather(wv.meta->cmat + h->rank * route::MAX_E, wv.meta->cmat, route::MAX_E, NCCL_INT32, wv.comm, ws));
         route::plan_kernel<<<1, 256, 0, ws>>>(wv.meta, wv.mtile_slot, E, h->El, h->world, h->rank, h->Rw, SEG_PAD, h->status);
         LAUNCH_CHECK("plan");
+        if (tl) cudaEventRecord(wv.tl[1], ws);
         // dispatch: rows go straight into the owners' receive regions of this wave (peer memory over NVLink)
         route::PeerPtrs xp_peers, y_peers;
         for (int i = 0; i < route::MAX_RANKS; ++i) {
@@ -527,25 +536,32 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
             route::dispatch_kernel<<<(tn + 7) / 8, 256, 0, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
             LAUNCH_CHECK("dispatch");
         }
+        if (tl) cudaEventRecord(wv.tl[2], ws);
         // barrier: every rank's rows of this wave have landed before an expert GEMM reads them
         NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
+        if (tl) cudaEventRecord(wv.tl[3], ws);
         egemm::Args a1, a2;
         gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, &a1, &a2);
         rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, gemm_grid, ws);
         if (rc != PRICHS_OK) return rc;
+        if (tl) cudaEventRecord(wv.tl[4], ws);
         rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, gemm_grid, ws);
         if (rc != PRICHS_OK) return rc;
+        if (tl) cudaEventRecord(wv.tl[5], ws);
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_shared, 0));  // the shared expert's rows are complete
         // barrier: every owner's outputs of this wave are complete before the combine gathers them over NVLink
         NCCL_TRY(nccl().all_gather(wv.token + route::MAX_RANKS + h->rank, wv.token + route::MAX_RANKS, 1, NCCL_INT32, wv.comm, ws));
+        if (tl) cudaEventRecord(wv.tl[6], ws);
         if (tn > 0) {
             const char* resid_w = resid_dev ? static_cast<const char*>(resid_dev) + (size_t)t0 * h->d * xsz : nullptr;
             rc = launch_combine(h, static_cast<const char*>(h->ybuf) + (size_t)t0 * h->d * ysz, y_peers, (long long)h->Tcap + (long long)w * h->Rw,
                                 sel, gates, pos, resid_w, static_cast<char*>(y_dev) + (size_t)t0 * h->d * osz, x_dtype, y_dtype, tn, ws);
             if (rc != PRICHS_OK) return rc;
         }
+        if (tl) cudaEventRecord(wv.tl[7], ws);
         CUDA_TRY(cudaEventRecord(wv.done, ws));
     }
+    h->tl_valid = tl;
     // 4. join the waves and publish the call's totals
     for (int w = 0; w < W; ++w) CUDA_TRY(cudaStreamWaitEvent(st, h->wave[w].done, 0));
     ep_totals_kernel<<<1, 64, 0, st>>>(wm, W, h->meta);
@@ -708,12 +724,17 @@ int prichs_moe_destroy(prichs_moe_t* h) {
         if (h->side_stream) cudaStreamDestroy(h->side_stream);
         if (h->ev_router) cudaEventDestroy(h->ev_router);
         if (h->ev_shared) cudaEventDestroy(h->ev_shared);
+        if (h->tl_base) cudaEventDestroy(h->tl_base);
+        if (h->tl_side[0]) cudaEventDestroy(h->tl_side[0]);
+        if (h->tl_side[1]) cudaEventDestroy(h->tl_side[1]);
     }
     for (int w = 0; w < MAX_WAVES; ++w) {
         EpWave& wv = h->wave[w];
         if (wv.comm && nccl().ok) nccl().comm_destroy(wv.comm);
         if (wv.stream) cudaStreamDestroy(wv.stream);
         if (wv.done) cudaEventDestroy(wv.done);
+        for (int i = 0; i < 8; ++i)
+            if (wv.tl[i]) cudaEventDestroy(wv.tl[i]);
         if (wv.meta) cudaFree(wv.meta);
         if (wv.mtile_slot) cudaFree(wv.mtile_slot);
         if (wv.token) cudaFree(wv.token);
@@ -1108,7 +1129,11 @@ int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs
         NCCL_TRY(nccl().comm_init_rank(&h->wave[w].comm, h->world, id, h->rank));
         CUDA_TRY(cudaStreamCreateWithFlags(&h->wave[w].stream, cudaStreamNonBlocking));
         CUDA_TRY(cudaEventCreateWithFlags(&h->wave[w].done, cudaEventDisableTiming));
+        for (int i = 0; i < 8; ++i) CUDA_TRY(cudaEventCreate(&h->wave[w].tl[i]));
     }
+    CUDA_TRY(cudaEventCreate(&h->tl_base));
+    CUDA_TRY(cudaEventCreate(&h->tl_side[0]));
+    CUDA_TRY(cudaEventCreate(&h->tl_side[1]));
     CUDA_TRY(cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaEventCreateWithFlags(&h->ev_router, cudaEventDisableTiming));
     CUDA_TRY(cudaEventCreateWithFlags(&h->ev_shared, cudaEventDisableTiming));
@@ -1154,6 +1179,19 @@ int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void*
 int prichs_moe_enable_timing(prichs_moe_t* h, int on) {
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
     h->timing = on != 0;
+    return PRICHS_OK;
+}
+
+int prichs_moe_get_ep_timeline(prichs_moe_t* h, float* ms, int n) {
+    if (!h || !ms) return fail(PRICHS_ERR_BAD_ARG, "null handle or output");
+    if (!h->tl_valid) return fail(PRICHS_ERR_BAD_ARG, "no expert-parallel timeline: enable timing before the forward");
+    if (n < 2 + 8 * h->n_waves) return fail(PRICHS_ERR_BAD_SHAPE, "the timeline needs %d floats", 2 + 8 * h->n_waves);
+    DeviceGuard guard(h->device);
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    CUDA_TRY(cudaEventElapsedTime(&ms[0], h->tl_base, h->tl_side[0]));
+    CUDA_TRY(cudaEventElapsedTime(&ms[1], h->tl_base, h->tl_side[1]));
+    for (int w = 0; w < h->n_waves; ++w)
+        for (int i = 0; i < 8; ++i) CUDA_TRY(cudaEventElapsedTime(&ms[2 + 8 * w + i], h->tl_base, h->wave[w].tl[i]));
     return PRICHS_OK;
 }
 
