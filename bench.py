@@ -164,6 +164,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-waves", type=int, default=0, help="expert-parallel token waves (0 = library default)")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override T (profiling of a small case only; the line is then not the baseline's config)")
     args = ap.parse_args()
@@ -200,7 +201,7 @@ def main():
         seed, T = 3, (args.tokens or 32768)
         ws = synth.layer_weights(seed, D, F, E, bf16=True)
         bias = np.zeros(E, np.float32)
-        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank)
+        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves)
         for e in range(E):  # only the experts this rank owns are uploaded
             if e // (E // world) != rank:
                 layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
@@ -248,7 +249,7 @@ def main():
             tlb = (C.c_float * 34)()
             if L.prichs_moe_get_ep_timeline(layer._h, tlb, 34) == 0:
                 v = [round(float(x), 4) for x in tlb]
-                nw = max(1, min(4, T // 8192))
+                nw = args.ep_waves or max(1, min(4, T // 8192))
                 timeline = {"ms_since_router": {"shared_gate_up": v[0], "shared_down": v[1]},
                             "marks": ["scan", "plan", "dispatched", "rows_landed", "gate_up", "down", "outputs_ready", "combined"],
                             "waves": [v[2 + 8 * w: 10 + 8 * w] for w in range(nw)]}

@@ -181,6 +181,15 @@ __global__ void compat_swiglu_kernel(const float* __restrict__ gate, const float
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// Token waves of the expert-parallel forward shrink towards the end: the last wave's combine is the only
+// exchange nothing can hide, so it is kept small. Cumulative fractions of the batch (per mille) per wave count.
+inline int wave_begin(int T, int n_waves, int w) {
+    static const int cum[5][5] = {{0, 0, 0, 0, 0}, {0, 1000, 0, 0, 0}, {0, 640, 1000, 0, 0}, {0, 440, 790, 1000, 0}, {0, 350, 650, 870, 1000}};
+    if (w >= n_waves) return T;
+    const long long b = (long long)T * cum[n_waves][w] / 1000;
+    return (int)std::min<long long>(T, (b + 15) / 16 * 16);
+}
+
 // Every expert's segment of a permuted region starts on a multiple of this many rows (one CTA-pair tile).
 constexpr int SEG_PAD = 256;
 
@@ -272,6 +281,10 @@ struct prichs_moe {
     int n_waves;  // token waves of an expert-parallel forward (1 when all experts are local)
     int Rw;       // rows of one wave's permuted region (multiple of 128); Rcap = n_waves * Rw
     EpWave wave[MAX_WAVES];
+    int ep_reserve_sms;  // SMs the expert-parallel GEMM launches leave to the exchange kernels
+    int ep_combine_mode; // which combine launches keep off the GEMM SMs: 0 all, 1 all but the last wave's, 2 none
+    int ep_copy_smem;    // dynamic shared memory requested by dispatch/combine in expert-parallel mode: more than a
+                         // GEMM CTA leaves free, so these kernels only run on the reserved SMs (0 = share SMs)
     int* ep_zero;              // a device int that stays zero (the "no permuted tiles" count of the shared launches)
     cudaStream_t side_stream;  // shared-expert GEMMs of the expert-parallel mode
     cudaEvent_t ev_router, ev_shared;
@@ -401,12 +414,14 @@ int launch_expert_gemm(prichs_moe* h, int epi, const CUtensorMap& tm_a_shared, c
 // are the caller's (already offset) pointers.
 int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y_peers, long long routed_base_rows, const int* sel,
                    const float* gates, const int* pos, const void* resid_dev, void* y_dev, int x_dtype, int y_dtype, int T,
-                   cudaStream_t st) {
-    const int grid = (T + 7) / 8;
+                   cudaStream_t st, bool exclusive = false) {
+    // expert-parallel: a capped, grid-striding launch; `exclusive` keeps it off the SMs that hold GEMM CTAs
+    const int grid = h->world > 1 ? std::min((T + 7) / 8, 4 * h->sm_count) : (T + 7) / 8;
+    const int dyn_smem = exclusive ? h->ep_copy_smem : 0;
     const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
     const bool of32 = y_dtype == PRICHS_DTYPE_F32;
 #define COMBINE(YF, OF, RS) \
-    route::combine_kernel<YF, OF, RS><<<grid, 256, 0, st>>>(y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
+    route::combine_kernel<YF, OF, RS><<<grid, 256, dyn_smem, st>>>(y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
     if (h->mode == PRICHS_MODE_F32) {
         if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
         else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
@@ -478,7 +493,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     h->ev_valid = false;
     // A few SMs stay free of the persistent GEMM CTAs so that the small kernels of the other streams (scans,
     // plans, NCCL) are never queued behind a whole GEMM.
-    const int gemm_grid = std::max(1, h->sm_count - 4);
+    const int gemm_grid = std::max(2, h->sm_count - h->ep_reserve_sms);
     const size_t xsz = x_dtype == PRICHS_DTYPE_F32 ? 4 : 2, osz = y_dtype == PRICHS_DTYPE_F32 ? 4 : 2, ysz = f32mode ? 4 : 2;
 
     // 1. router over the whole batch
@@ -503,13 +518,12 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     }
 
     // 3. token waves
-    const int Tw = round_up((T + W - 1) / W, route::TILE_TOKENS);
     WaveMetas wm;
     for (int w = 0; w < MAX_WAVES; ++w) wm.m[w] = h->wave[w < W ? w : 0].meta;
     for (int w = 0; w < W; ++w) {
         EpWave& wv = h->wave[w];
         cudaStream_t ws = wv.stream;
-        const int t0 = std::min(T, w * Tw), tn = std::min(T, t0 + Tw) - t0;
+        const int t0 = wave_begin(T, W, w), tn = wave_begin(T, W, w + 1) - t0;
         const int tile0 = t0 / route::TILE_TOKENS, ntl = (tn + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
         const int region_tile = w * (h->Rw / 128);
         int* sel = h->sel + (size_t)t0 * 2;
@@ -533,7 +547,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
             y_peers.p[i] = h->y_peer[i];
         }
         if (tn > 0) {
-            route::dispatch_kernel<<<(tn + 7) / 8, 256, 0, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
+            route::dispatch_kernel<<<std::min((tn + 7) / 8, 2 * h->sm_count), 256, h->ep_copy_smem, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
             LAUNCH_CHECK("dispatch");
         }
         if (tl) cudaEventRecord(wv.tl[2], ws);
@@ -555,7 +569,8 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         if (tn > 0) {
             const char* resid_w = resid_dev ? static_cast<const char*>(resid_dev) + (size_t)t0 * h->d * xsz : nullptr;
             rc = launch_combine(h, static_cast<const char*>(h->ybuf) + (size_t)t0 * h->d * ysz, y_peers, (long long)h->Tcap + (long long)w * h->Rw,
-                                sel, gates, pos, resid_w, static_cast<char*>(y_dev) + (size_t)t0 * h->d * osz, x_dtype, y_dtype, tn, ws);
+                                sel, gates, pos, resid_w, static_cast<char*>(y_dev) + (size_t)t0 * h->d * osz, x_dtype, y_dtype, tn, ws,
+                                h->ep_combine_mode == 0 || (h->ep_combine_mode == 1 && w + 1 < W));
             if (rc != PRICHS_OK) return rc;
         }
         if (tl) cudaEventRecord(wv.tl[7], ws);
@@ -614,9 +629,10 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->n_waves = std::max(1, std::min(MAX_WAVES, want));
     }
     // worst case per wave: every token of the wave, from every rank, picks experts of this rank
-    const long long tw_max = round_up((h->Tmax + h->n_waves - 1) / h->n_waves, route::TILE_TOKENS);
+    // the first wave is the largest
+    const long long tw_max = wave_begin(h->Tmax, h->n_waves, 1) + route::TILE_TOKENS;
     long long recv = world == 1 ? (long long)h->Tmax * k
-                                : (cfg->ep_max_recv_rows > 0 ? (cfg->ep_max_recv_rows + h->n_waves - 1) / h->n_waves
+                                : (cfg->ep_max_recv_rows > 0 ? (long long)cfg->ep_max_recv_rows * tw_max / h->Tmax + 1
                                                              : (long long)world * tw_max * k);
     const long long rw = (recv + (long long)h->El * (SEG_PAD - 1) + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
     const long long rcap = rw * h->n_waves;
@@ -699,6 +715,12 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         // one-CTA kernel (128 x 256 tiles), kept for comparison.
         const char* sel = getenv("PRICHS_GEMM");
         h->pair_gemm = !(sel && strcmp(sel, "single") == 0);
+        const char* rs = getenv("PRICHS_EP_RESERVE_SMS");
+        h->ep_reserve_sms = rs ? std::max(0, std::min(64, atoi(rs))) & ~1 : 20;
+        const char* ex = getenv("PRICHS_EP_EXCLUSIVE");
+        h->ep_copy_smem = (ex && atoi(ex) == 0) ? 0 : 8192;
+        const char* cm = getenv("PRICHS_EP_COMBINE_MODE");
+        h->ep_combine_mode = cm ? atoi(cm) : 1;
     }
     for (int i = 0; i < 7 && rc == PRICHS_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "cudaEventCreate failed");
@@ -1123,18 +1145,24 @@ int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs
         h->y_peer[r] = py;
     }
     static_assert(MAX_WAVES * 128 <= PRICHS_EP_ID_BYTES, "one 128-byte communicator id per wave");
+    // Stream priorities order the work of a forward when several kernels compete for SMs: the shared expert
+    // first (every wave's combine needs it), then wave 0, wave 1, ... so that an earlier wave's exchange and
+    // combine are never queued behind a later wave's GEMM.
+    int prio_lo = 0, prio_hi = 0;
+    CUDA_TRY(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));  // hi is the numerically smallest
+    auto prio = [&](int rank_from_top) { return std::min(prio_lo, prio_hi + rank_from_top); };
     for (int w = 0; w < h->n_waves; ++w) {
         NcclApi::Id128 id;
         memcpy(&id, static_cast<const char*>(id128) + 128 * w, sizeof(id));
         NCCL_TRY(nccl().comm_init_rank(&h->wave[w].comm, h->world, id, h->rank));
-        CUDA_TRY(cudaStreamCreateWithFlags(&h->wave[w].stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamCreateWithPriority(&h->wave[w].stream, cudaStreamNonBlocking, prio(1 + w)));
         CUDA_TRY(cudaEventCreateWithFlags(&h->wave[w].done, cudaEventDisableTiming));
         for (int i = 0; i < 8; ++i) CUDA_TRY(cudaEventCreate(&h->wave[w].tl[i]));
     }
     CUDA_TRY(cudaEventCreate(&h->tl_base));
     CUDA_TRY(cudaEventCreate(&h->tl_side[0]));
     CUDA_TRY(cudaEventCreate(&h->tl_side[1]));
-    CUDA_TRY(cudaStreamCreateWithFlags(&h->side_stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaStreamCreateWithPriority(&h->side_stream, cudaStreamNonBlocking, prio(0)));
     CUDA_TRY(cudaEventCreateWithFlags(&h->ev_router, cudaEventDisableTiming));
     CUDA_TRY(cudaEventCreateWithFlags(&h->ev_shared, cudaEventDisableTiming));
     h->ep_ready = true;

@@ -432,8 +432,10 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, cons
                 const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
                 int* __restrict__ pos) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 8 + warp;
-    if (t >= T || meta->overflow) return;
+    if (meta->overflow) return;
+    // grid-stride over tokens: the expert-parallel forward caps the grid so that this NVLink-bound kernel
+    // does not flood the SMs it shares with a concurrently running GEMM
+    for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {
     int my_row = -1, my_owner = 0;
     if (lane < 2) {
         const int s = sel[(size_t)t * 2 + lane];
@@ -458,6 +460,7 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, cons
         if (row0 >= 0) d0[c] = v;
         if (row1 >= 0) d1[c] = v;
     }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -473,8 +476,7 @@ combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtr
                const int* __restrict__ sel, const float* __restrict__ gates, const int* __restrict__ pos,
                const void* __restrict__ resid, void* __restrict__ out, int T, int d, int El) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 8 + warp;
-    if (t >= T) return;
+    for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {  // grid-stride (see dispatch_kernel)
     const int2 s = *reinterpret_cast<const int2*>(sel + (size_t)t * 2);
     const float2 gw = *reinterpret_cast<const float2*>(gates + (size_t)t * 2);
     const int2 p = *reinterpret_cast<const int2*>(pos + (size_t)t * 2);
@@ -548,6 +550,7 @@ combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtr
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * d + c) =
                 make_uint4(w[0], w[1], w[2], w[3]);
         }
+    }
     }
 }
 
