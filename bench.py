@@ -157,6 +157,83 @@ def workload_config(n_gpus):
             "l2": "per-GPU working set (~1.2 GB) exceeds the 126 MB L2; inputs rotate over 2 batches"}
 
 
+ZIPF_ALPHA = 1.2
+
+
+def zipf_router(ws_router, seed, n_sample=65536, iters=60):
+    """Config 4: per-expert column factors sigma_i for W_r, found by a host-side fixed-point iteration on a
+    token sample, such that expert i's share of top-1 selections follows Zipf(alpha = 1.2)."""
+    from prichs_b200 import synth
+    target = 1.0 / np.arange(1, E + 1) ** ZIPF_ALPHA
+    target /= target.sum()
+    xs = synth.tokens(seed * 100 + 77, n_sample, D, bf16=True)
+    base = xs @ ws_router  # [n, E] logits at sigma = 1
+    sigma = np.ones(E, np.float64)
+    share = None
+    for _ in range(iters):
+        share = np.bincount(np.argmax(base * sigma[None, :].astype(np.float32), axis=1), minlength=E) / n_sample
+        if np.all(np.abs(share - target) <= 0.01 * target + 1e-4):
+            break
+        sigma *= (target / np.maximum(share, 1e-6)) ** 0.5
+        sigma /= sigma[-1]
+    return synth.round_bf16((ws_router * sigma[None, :].astype(np.float32))), sigma, share, target
+
+
+def run_decode(args):
+    """Config 2 (decode shape, bandwidth bound): 24 independent MoE layers of the production dimensions, each
+    with its own seeded weights (seed 2 + layer), applied to the same T = 64 tokens; one step = the 24 layer
+    forwards back to back on one stream. Reported as per-step latency and weight-streaming GB/s."""
+    import torch
+    from prichs_b200 import MoELayer, _capi, synth
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    T, n_layers = 64, args.layers
+    x_host = synth.tokens(2, T, D, bf16=True)
+    x = torch.from_numpy(synth.to_bf16_bits(x_host).view(np.int16)).view(torch.bfloat16).to(dev)
+    layers = []
+    for l in range(n_layers):
+        m = MoELayer.from_weights(synth.layer_weights(2 + l, D, F, E, bf16=True), K, max_tokens=T, device=0)
+        m.forward(x)  # creates the handle and uploads the weights
+        m.router = m.shared_expert = None  # the host copies are not needed any more
+        m.experts = []
+        layers.append(m)
+    y = torch.empty_like(x)
+    L = _capi.lib()
+    st = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        for m in layers:
+            L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, y.data_ptr(), _capi.DTYPE_BF16, T, st)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(dev)
+    peaks = measured_peaks()
+    with ClockSampler(0) as clocks:
+        launches0 = L.prichs_kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        launches = int(L.prichs_kernel_launches() - launches0)
+    ms = e0.elapsed_time(e1) / args.steps
+    wbytes = n_layers * 9 * 3 * D * F * 2  # every expert of every layer is hit with probability ~1 at 128 assignments
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    line = {"metric": "MoE-layer tokens/sec", "value": T * n_layers / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"config 2: decode, {n_layers} independent MoE layers (seed 2+layer), T=64 tokens each, bf16; "
+                                   "a step is the layer forwards back to back", "layers": n_layers,
+                       "l2": f"the step streams {wbytes / 1e6:.0f} MB of weights, far more than the 126 MB L2"},
+            "decode": {"ms_per_step": ms, "us_per_layer": ms * 1e3 / n_layers, "weight_GBps": gbs, "frac_hbm": gbs / peaks["hbm"]},
+            "roofline": {"kernel": "whole decode step (weight streaming through the grouped GEMMs)", "bound": "hbm",
+                         "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None},
+            "gpu_launches": launches, "clocks": clocks.summary()}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,9 +244,14 @@ def main():
     ap.add_argument("--ep-waves", type=int, default=0, help="expert-parallel token waves (0 = library default)")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override T (profiling of a small case only; the line is then not the baseline's config)")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="baseline config to run (0 = 1 for one GPU, 3 for several); 2 = decode, 4 = Zipf-skewed routing")
+    ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.config == 2:
+        return run_decode(args)
 
     import torch
     from prichs_b200 import MoELayer, _capi, synth
@@ -198,8 +280,11 @@ def main():
         layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank)
     else:
         from prichs_b200 import ep
-        seed, T = 3, (args.tokens or 32768)
+        skew = args.config == 4
+        seed, T = (4 if skew else 3), (args.tokens or 32768)
         ws = synth.layer_weights(seed, D, F, E, bf16=True)
+        if skew:
+            ws[0], zipf_sigma, zipf_share, zipf_target = zipf_router(ws[0], seed)
         bias = np.zeros(E, np.float32)
         layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves)
         for e in range(E):  # only the experts this rank owns are uploaded
@@ -343,6 +428,22 @@ def main():
         "layer_tflops": tokens * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,
         "clocks": clocks.summary(),
     }
+    if world > 1 and args.config == 4:
+        # one aux-loss-free bias step from the global counts of the last forward: b_i += gamma (k/E - count_i/total);
+        # gamma = 1e-3 on load fractions equals a count-form step of gamma / (T * world) per token of deviation
+        gcounts = torch.tensor(layer.last_counts(), device=dev)
+        dist.all_reduce(gcounts)
+        rr2 = torch.tensor([rows - T], device=dev, dtype=torch.int64)
+        allrows = [torch.zeros_like(rr2) for _ in range(world)]
+        dist.all_gather(allrows, rr2)
+        layer.update_bias_from_last(1e-3, total_tokens=T * world)
+        gc = gcounts.cpu().numpy().astype(np.float64)
+        line["skew"] = {"zipf_alpha": ZIPF_ALPHA, "sigma": [float(v) for v in zipf_sigma],
+                        "top1_share_sample": [float(v) for v in zipf_share], "top1_share_target": [float(v) for v in zipf_target],
+                        "global_counts": [int(v) for v in gc], "imbalance_max_over_mean": float(gc.max() / gc.mean()),
+                        "recv_rows_per_gpu": [int(t.item()) for t in allrows],
+                        "bias_after_step": [float(v) for v in layer.router_bias], "gamma": 1e-3}
+        line["config"]["workload"] = line["config"]["workload"].replace("config 3", "config 4 (Zipf(1.2)-skewed router, seed 4)")
     if rank == 0:
         if not args.no_cpu_baseline and n_gpus == 1:
             line["cpu_baseline"] = cpu_baseline(ws, bias, xs_host[0])

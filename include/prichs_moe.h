@@ -115,7 +115,9 @@ PRICHS_API int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, con
 
 /* Waits for the handle's last stream and returns the device status word of the work enqueued so far:
  * PRICHS_OK, PRICHS_ERR_CAPACITY (an expert's segment did not fit) or PRICHS_ERR_TIMEOUT (a bounded wait
- * inside a kernel gave up). The reference has no counterpart: its launches report nothing. */
+ * inside a kernel gave up); a reported error is cleared. After PRICHS_ERR_CAPACITY the outputs of that forward
+ * are undefined (the exchange was skipped on every rank) but the handle stays usable. The reference has no
+ * counterpart: its launches report nothing. */
 PRICHS_API int prichs_moe_sync_status(prichs_moe_t* h);
 
 /* ---- routing results of the last forward (the MoEStash fields, moe.rs:44-53) ---------------------- */

@@ -681,6 +681,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     }
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
     cudaMemset(h->status, 0, sizeof(int));
+    cudaMemset(h->pos, 0, (size_t)h->Tmax * 2 * sizeof(int));  // stale row maps always stay inside the buffers
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
     cudaMemset(h->ep_zero, 0, 8 * sizeof(int));
     for (int w = 0; w < h->n_waves && world > 1; ++w) {
@@ -1030,6 +1031,7 @@ int prichs_moe_sync_status(prichs_moe_t* h) {
     CUDA_TRY(cudaStreamSynchronize(h->last_stream));
     int s = 0;
     CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (s != 0) CUDA_TRY(cudaMemset(h->status, 0, sizeof(int)));  // reported once, then the handle goes on
     return translate_status(s);
 }
 

@@ -315,7 +315,7 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
     }
     __syncthreads();
     if (tid == 0) {
-        int recv = 0, local_rows = 0;
+        int recv = 0, local_rows = 0, over = 0;
         for (int o = 0; o < world; ++o) {
             int base = 0;
             for (int le = 0; le < El; ++le) {
@@ -327,12 +327,13 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
                 }
                 base += (s_total[e] + pad_rows - 1) / pad_rows * pad_rows;
             }
+            // every rank evaluates every owner's region, so that all of them skip the exchange together
+            if (base > cap_rows) over = 1;
             if (o == rank) {
                 s_base[El] = base;
                 local_rows = base;
             }
         }
-        const int over = local_rows > cap_rows;
         meta->overflow = over;
         meta->recv_rows = recv;
         meta->n_routed_mtiles = over ? 0 : local_rows / 128;

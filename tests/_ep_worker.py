@@ -22,12 +22,19 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     # (d, f, E, k, T, bias range, waves): the last two cases cut the batch into token waves
-    cases = [(512, 384, 8, 2, 1000, (-0.1, 0.1), 1), (1536, 1280, 8, 2, 2048, None, 1), (512, 384, 8, 2, 3000, (-0.1, 0.1), 3),
-             (1536, 1280, 8, 2, 4096, None, 4)]
-    for d, f, E, k, T, brange, waves in cases:
+    # (d, f, E, k, T, bias range, waves, skew): the later cases cut the batch into token waves; `skew` scales the
+    # router columns so that the first experts attract most tokens (the shape of the Zipf-skewed config)
+    cases = [(512, 384, 8, 2, 1000, (-0.1, 0.1), 1, False), (1536, 1280, 8, 2, 2048, None, 1, False),
+             (512, 384, 8, 2, 3000, (-0.1, 0.1), 3, False), (1536, 1280, 8, 2, 4096, None, 4, False),
+             (512, 384, 8, 2, 2500, None, 2, True)]
+    for d, f, E, k, T, brange, waves, skew in cases:
         Tr = T + 37 * rank  # ragged: every rank brings a different number of tokens
         ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=True)
         bias = synth.router_bias(3, E, *brange) if brange else np.zeros(E, np.float32)
+        if skew:
+            ws[0] = synth.round_bf16(np.abs(ws[0]) * np.array([6, 4, 3, 2, 1.5, 1, 1, 1], np.float32)[None, :] *
+                                     np.sign(synth.normal(5, 1, ws[0].shape)))
+            bias = np.array([0.6, 0.3, 0.15, 0, 0, 0, 0, 0], np.float32)
         x = synth.tokens(3000 + rank, Tr, d, bf16=True)
         El = E // world
         m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local, ep_waves=waves)
@@ -69,10 +76,37 @@ def main():
         m.update_bias_from_last(1e-3, total_tokens=total_tokens)  # ragged ranks: the global total is given
         exp = O.update_aux_free_bias(bias, cmat.sum(axis=0), total_tokens, 1e-3, k)
         assert np.array_equal(m.router_bias, exp)
+        if skew:
+            share = cmat.sum(axis=0) / cmat.sum()
+            assert share.max() > 1.5 / E, f"routing is not skewed: {share}"
         print(f"EP_OK rank={rank} d={d} T={Tr} waves={waves} max_rel={rep_['max_rel']:.3e} recv_rows={hp['recv_rows']}", flush=True)
         dist.barrier()
         m.close()
         dist.barrier()
+    # capacity: a receive region that is too small is detected on every rank, reported once, and nothing is
+    # written out of bounds; the handle stays usable
+    from prichs_b200 import PrichsError
+    d, f, E, k, T = 512, 384, 8, 2, 1500
+    ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=True)
+    m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local, ep_waves=1, ep_max_recv_rows=64)
+    El = E // world
+    for e in range(E):
+        if e // El != rank:
+            m.experts[e].gate_proj = m.experts[e].up_proj = m.experts[e].down_proj = None
+    ep.connect(m, dist, max_tokens=T)
+    xd = torch.from_numpy(synth.to_bf16_bits(synth.tokens(3100 + rank, T, d, bf16=True)).view(np.int16)).view(torch.bfloat16).cuda()
+    m.forward(xd)
+    try:
+        m.sync_status()
+        raise AssertionError("the overflow was not reported")
+    except PrichsError as e:
+        assert e.code == -2, e
+    m.sync_status()  # cleared after the report
+    assert int(m.last_counts().sum()) == T * k
+    print(f"EP_OK rank={rank} capacity overflow reported", flush=True)
+    dist.barrier()
+    m.close()
+    dist.barrier()
     dist.destroy_process_group()
 
 
