@@ -203,21 +203,42 @@ def run_decode(args):
 
     def step():
         for m in layers:
-            L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, y.data_ptr(), _capi.DTYPE_BF16, T, st)
+            rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, y.data_ptr(), _capi.DTYPE_BF16, T, st)
+            assert rc == 0, _capi.last_error()
 
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize(dev)
+    # the 24 x 6 small launches of a step are replayed as one CUDA graph (the forward neither allocates nor
+    # synchronises, so it can be captured); --no-graph times the plain launches
+    graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):
+            st = side.cuda_stream
+            graph = torch.cuda.CUDAGraph()
+            launches_per_step0 = L.prichs_kernel_launches()
+            with torch.cuda.graph(graph, stream=side):
+                st = torch.cuda.current_stream(dev).cuda_stream
+                step()
+            launches_per_step = int(L.prichs_kernel_launches() - launches_per_step0)
+        torch.cuda.synchronize(dev)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(dev)
     peaks = measured_peaks()
     with ClockSampler(0) as clocks:
         launches0 = L.prichs_kernel_launches()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            step()
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
         e1.record()
         torch.cuda.synchronize(dev)
-        launches = int(L.prichs_kernel_launches() - launches0)
+        launches = int(L.prichs_kernel_launches() - launches0) if graph is None else launches_per_step * args.steps
     ms = e0.elapsed_time(e1) / args.steps
     wbytes = n_layers * 9 * 3 * D * F * 2  # every expert of every layer is hit with probability ~1 at 128 assignments
     gbs = wbytes / (ms * 1e-3) / 1e9
@@ -230,7 +251,7 @@ def run_decode(args):
             "decode": {"ms_per_step": ms, "us_per_layer": ms * 1e3 / n_layers, "weight_GBps": gbs, "frac_hbm": gbs / peaks["hbm"]},
             "roofline": {"kernel": "whole decode step (weight streaming through the grouped GEMMs)", "bound": "hbm",
                          "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None},
-            "gpu_launches": launches, "clocks": clocks.summary()}
+            "gpu_launches": launches, "cuda_graph": graph is not None, "clocks": clocks.summary()}
     print(json.dumps(line))
 
 
@@ -247,6 +268,7 @@ def main():
     ap.add_argument("--config", type=int, default=0, choices=[0, 1, 2, 3, 4],
                     help="baseline config to run (0 = 1 for one GPU, 3 for several); 2 = decode, 4 = Zipf-skewed routing")
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
+    ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

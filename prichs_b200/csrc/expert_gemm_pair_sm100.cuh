@@ -97,6 +97,7 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
                 const bool is_shared = mp < shared_pairs;
                 const CUtensorMap* tm_a = is_shared ? &tm_a_shared : &tm_a_routed;
                 const int rp = mp - shared_pairs;  // pair index inside the permuted region
+                if (!is_shared && args.mtile_slot[2 * rp] < 0) continue;  // a pair of padding rows only
                 const int a_row = (is_shared ? 2 * mp : args.a_routed_tile_off + 2 * rp) * BM + (int)cta_rank * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[2 * rp];
                 const int b_row = slot * args.w_rows + nt * BN + (int)cta_rank * 128;
@@ -139,6 +140,8 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
             bool ok = true;
             const int iters = npass * args.nk;
             for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+                const int mp_ = tile / args.n_ntiles;
+                if (mp_ >= shared_pairs && args.mtile_slot[2 * (mp_ - shared_pairs)] < 0) continue;
                 if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, WAIT_CYCLES)) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -189,6 +192,7 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
         for (int tile = cluster_id; tile < total_tiles; tile += n_clusters) {
             const int mp = tile / args.n_ntiles;
             const int nt = tile - mp * args.n_ntiles;
+            if (mp >= shared_pairs && args.mtile_slot[2 * (mp - shared_pairs)] < 0) continue;
             // The vote keeps the warp converged for the .sync.aligned TMEM loads below.
             const bool ready = ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, WAIT_CYCLES);
             if (!__all_sync(0xffffffffu, ready)) break;

@@ -16,7 +16,7 @@
 // Row space: m-tile i < shared_mtiles covers rows [128 i, 128 i + 128) of the un-permuted tokens (shared
 // expert, weight slot 0); m-tile i >= shared_mtiles covers rows of the permuted buffer, where every
 // expert's segment starts on a multiple of 128 rows, so a tile never straddles two experts; its weight slot
-// is 1 + mtile_slot[i - shared_mtiles]. Output rows: shared tiles at [128 i, ...), permuted tiles at
+// is 1 + mtile_slot[i - shared_mtiles] (negative entries mark tiles made of padding rows only: skipped). Output rows: shared tiles at [128 i, ...), permuted tiles at
 // 128 * (routed_base_tiles + j), a base that does not depend on T (peers of an expert-parallel group
 // address each other's buffers with it).
 //
@@ -147,6 +147,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                 const int mt = tile / args.n_ntiles;
                 const int nt = tile - mt * args.n_ntiles;
                 const bool is_shared = mt < args.shared_mtiles;
+                if (!is_shared && args.mtile_slot[mt - args.shared_mtiles] < 0) continue;  // padding-only tile
                 const CUtensorMap* tm_a = is_shared ? &tm_a_shared : &tm_a_routed;
                 const int a_row = (is_shared ? mt : args.a_routed_tile_off + mt - args.shared_mtiles) * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[mt - args.shared_mtiles];
@@ -196,6 +197,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
             bool ok = true;
             const int iters = npass * args.nk;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int mt_ = tile / args.n_ntiles;
+                if (mt_ >= args.shared_mtiles && args.mtile_slot[mt_ - args.shared_mtiles] < 0) continue;
                 if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, WAIT_CYCLES)) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -240,6 +243,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int mt = tile / args.n_ntiles;
             const int nt = tile - mt * args.n_ntiles;
+            if (mt >= args.shared_mtiles && args.mtile_slot[mt - args.shared_mtiles] < 0) continue;
             // The vote keeps the warp converged for the .sync.aligned TMEM loads below.
             const bool ready = ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, WAIT_CYCLES);
             if (!__all_sync(0xffffffffu, ready)) break;

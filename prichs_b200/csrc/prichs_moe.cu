@@ -273,6 +273,7 @@ struct prichs_moe {
     CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
     CUtensorMap tm_wgu_half, tm_wdn_half;  // 128-row boxes: one CTA's half of a B tile in the CTA-pair kernel
     bool pair_gemm;  // use the CTA-pair (cta_group::2) GEMM kernel
+    bool small_batch;  // this forward has so few rows that 128-row tiles on single CTAs spread better over the SMs
 
     // expert-parallel group: peers' receive / output buffers mapped into this process, and the token waves
     bool ep_ready;
@@ -394,7 +395,7 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
 // One grouped-GEMM launch: epi 0 = gate|up + SwiGLU into H, epi 1 = down projection into Y.
 int launch_expert_gemm(prichs_moe* h, int epi, const CUtensorMap& tm_a_shared, const CUtensorMap& tm_a_routed, const egemm::Args& a,
                        int grid, cudaStream_t st) {
-    if (h->pair_gemm) {
+    if (h->pair_gemm && !h->small_batch) {
         const int g2 = std::max(2, grid & ~1);  // whole CTA pairs
         if (epi == 0)
             egemm::expert_gemm_pair_kernel<egemm::EPI_SWIGLU><<<g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wgu_half, h->tm_h_out, a);
@@ -887,6 +888,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     route::ConceptBias cb;
     for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = (e < n_concept && e < E) ? concept_bias[e] : 0.0f;
 
+    h->small_batch = T < 1024;
     if (h->world > 1) return forward_ep(h, x_dev, x_dtype, resid_dev, cb, y_dev, y_dtype, T, st);
 
     const bool f32mode = h->mode == PRICHS_MODE_F32;

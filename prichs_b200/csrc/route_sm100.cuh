@@ -344,7 +344,9 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
     for (int i = tid; i < ntiles; i += blockDim.x) {
         int le = 0;
         while (le + 1 < El && i * 128 >= s_base[le + 1]) ++le;
-        mtile_slot[i] = le;
+        // tiles that hold only padding rows are marked (-1 - slot): the GEMM kernels skip them
+        const bool padding_only = i * 128 >= s_base[le] + s_total[rank * El + le];
+        mtile_slot[i] = padding_only ? -1 - le : le;
     }
 }
 

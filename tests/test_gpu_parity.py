@@ -156,7 +156,8 @@ def test_dispatch_layout_and_intermediates(torch_cuda, oracle):
         assert np.array_equal(rows, seg_base[e] + np.arange(len(tok))), f"expert {e}: rows not in token order"
         assert np.array_equal(xp[rows], x[tok]), f"expert {e}: permuted rows are not exact copies"
     slots = m.debug_buffer(8, 4 * (rcap_rows // 128)).view(np.int32)
-    exp_slots = np.concatenate([np.full(pad[e] // 128, e) for e in range(E)]).astype(np.int32)
+    # tiles that hold only padding rows are marked -1 - expert
+    exp_slots = np.concatenate([np.where(np.arange(pad[e] // 128) * 128 < counts[e], e, -1 - e) for e in range(E)]).astype(np.int32)
     assert np.array_equal(slots, exp_slots)
     # shared expert intermediates
     Tcap = (m.token_capacity + 255) // 256 * 256
