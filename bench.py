@@ -197,14 +197,31 @@ def run_decode(args):
         m.router = m.shared_expert = None  # the host copies are not needed any more
         m.experts = []
         layers.append(m)
-    y = torch.empty_like(x)
     L = _capi.lib()
     st = torch.cuda.current_stream(dev).cuda_stream
 
+    # The layers are independent by the config's definition, so they may be spread over several streams
+    # (--streams, default 4): the small routing kernels of one layer then overlap the weight streaming of others.
+    nstreams = max(1, args.streams)
+    lanes = [torch.cuda.Stream(dev) for _ in range(nstreams)] if nstreams > 1 else []
+    ys = [torch.empty_like(x) for _ in range(max(1, nstreams))]
+
     def step():
-        for m in layers:
-            rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, y.data_ptr(), _capi.DTYPE_BF16, T, st)
+        if not lanes:
+            for m in layers:
+                rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[0].data_ptr(), _capi.DTYPE_BF16, T, st)
+                assert rc == 0, _capi.last_error()
+            return
+        cur = torch.cuda.current_stream(dev)
+        for ln in lanes:
+            ln.wait_stream(cur)
+        for i, m in enumerate(layers):
+            ln = lanes[i % nstreams]
+            rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[i % nstreams].data_ptr(),
+                                      _capi.DTYPE_BF16, T, ln.cuda_stream)
             assert rc == 0, _capi.last_error()
+        for ln in lanes:
+            cur.wait_stream(ln)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -246,12 +263,12 @@ def run_decode(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"config 2: decode, {n_layers} independent MoE layers (seed 2+layer), T=64 tokens each, bf16; "
-                                   "a step is the layer forwards back to back", "layers": n_layers,
+                                   f"a step is all layer forwards, spread over {nstreams} stream(s)", "layers": n_layers,
                        "l2": f"the step streams {wbytes / 1e6:.0f} MB of weights, far more than the 126 MB L2"},
             "decode": {"ms_per_step": ms, "us_per_layer": ms * 1e3 / n_layers, "weight_GBps": gbs, "frac_hbm": gbs / peaks["hbm"]},
             "roofline": {"kernel": "whole decode step (weight streaming through the grouped GEMMs)", "bound": "hbm",
                          "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None},
-            "gpu_launches": launches, "cuda_graph": graph is not None, "clocks": clocks.summary()}
+            "gpu_launches": launches, "cuda_graph": graph is not None, "streams": nstreams, "clocks": clocks.summary()}
     print(json.dumps(line))
 
 
@@ -269,6 +286,7 @@ def main():
                     help="baseline config to run (0 = 1 for one GPU, 3 for several); 2 = decode, 4 = Zipf-skewed routing")
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
+    ap.add_argument("--streams", type=int, default=4, help="decode config: streams the independent layers are spread over")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
