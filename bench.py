@@ -286,7 +286,7 @@ def main():
                     help="baseline config to run (0 = 1 for one GPU, 3 for several); 2 = decode, 4 = Zipf-skewed routing")
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
-    ap.add_argument("--streams", type=int, default=4, help="decode config: streams the independent layers are spread over")
+    ap.add_argument("--streams", type=int, default=8, help="decode config: streams the independent layers are spread over")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
