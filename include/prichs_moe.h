@@ -109,7 +109,9 @@ PRICHS_API int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtyp
 
 /* The same call with HOST buffers, the shape in which the reference's MoELayer::forward(&Tensor) -> Tensor
  * is used (f32 row-major slices, tensor.rs:14-29): copies x (and resid) to the device, runs the forward,
- * copies y back and waits for it. Pinned host memory makes the copies asynchronous; pageable memory works. */
+ * copies y back and waits for it. Pinned host memory makes the copies asynchronous; pageable memory works.
+ * Batches of 4096 tokens or more are fed through in chunks on three streams (upload, kernels, download
+ * overlap); the results, the routing stash and the counts are identical to one pass. */
 PRICHS_API int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host,
                             const float* concept_bias, int n_concept, float* y_host, int T);
 
@@ -182,7 +184,8 @@ PRICHS_API int64_t prichs_kernel_launches(void);
 
 /* Device-time breakdown of the last forward on this handle, in milliseconds, measured with CUDA events
  * recorded on the forward's stream when timing was enabled: router, scan, dispatch, gate_up, down,
- * combine (6 floats). Enabling timing adds event records only. */
+ * combine (6 floats). Enabling timing adds event records only. Handles with all experts local only; the
+ * expert-parallel forward overlaps its kernels on several streams and reports prichs_moe_get_ep_timeline. */
 PRICHS_API int prichs_moe_enable_timing(prichs_moe_t* h, int on);
 PRICHS_API int prichs_moe_get_stage_ms(prichs_moe_t* h, float* ms6);
 

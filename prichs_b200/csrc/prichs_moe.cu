@@ -1,8 +1,11 @@
 // libprichs_moe.so -- C ABI (include/prichs_moe.h) over the sm_100a kernels of the PRICHS MoE-layer forward.
 //
 // One handle = the device state of one MoELayer (crates/prichs-model/src/moe.rs:58-64): repacked weights,
-// router bias, workspace for max_tokens, TMA descriptors. A forward is six launches on the caller's stream:
+// router bias, workspace for max_tokens, TMA descriptors. With all experts local a forward is six launches on
+// the caller's stream:
 //   router -> scan/plan -> dispatch -> grouped gate|up GEMM (+SwiGLU) -> grouped down GEMM -> combine.
+// The expert-parallel forward (forward_ep) runs the same kernels in token waves on several streams and
+// exchanges rows through peer-mapped buffers.
 // There is no CPU fallback: every entry point that needs the device fails with PRICHS_ERR_CUDA without one.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -442,6 +445,21 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
 
 namespace {
 
+// Adds the per-expert counts of the chunk that just ran to `acc` (first chunk: overwrite).
+__global__ void host_chunk_accumulate_kernel(const route::RouteMeta* __restrict__ meta, int* __restrict__ acc, int first) {
+    const int e = threadIdx.x;
+    if (e < route::MAX_E) acc[e] = (first ? 0 : acc[e]) + meta->counts[e];
+}
+// After the last chunk: the call's totals become the handle's "last forward" counts.
+__global__ void host_chunk_finish_kernel(route::RouteMeta* __restrict__ meta, const int* __restrict__ acc) {
+    const int e = threadIdx.x;
+    if (e < route::MAX_E) {
+        meta->counts[e] = acc[e];
+        meta->total[e] = acc[e];
+        meta->cmat[e] = acc[e];
+    }
+}
+
 // Sums the waves' routing summaries into the handle's "last forward" summary (counts, totals, received rows,
 // counts matrix); segment bases and source offsets are those of wave 0.
 struct WaveMetas {
@@ -872,8 +890,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         return PRICHS_OK;
     }
     if (!x_dev || !y_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation pointer");
-    const size_t xalign = x_dtype == PRICHS_DTYPE_F32 ? 15 : 15;
-    if ((reinterpret_cast<uintptr_t>(x_dev) & xalign) || (reinterpret_cast<uintptr_t>(y_dev) & 15) ||
+    if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (reinterpret_cast<uintptr_t>(y_dev) & 15) ||
         (resid_dev && (reinterpret_cast<uintptr_t>(resid_dev) & 15)))
         return fail(PRICHS_ERR_BAD_ARG, "activation pointers must be 16-byte aligned");
     DeviceGuard guard(h->device);
@@ -939,21 +956,6 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     return PRICHS_OK;
 }
 
-// Adds the per-expert counts of the chunk that just ran to `acc` (first chunk: overwrite).
-__global__ void host_chunk_accumulate_kernel(const route::RouteMeta* __restrict__ meta, int* __restrict__ acc, int first) {
-    const int e = threadIdx.x;
-    if (e < route::MAX_E) acc[e] = (first ? 0 : acc[e]) + meta->counts[e];
-}
-// After the last chunk: the call's totals become the handle's "last forward" counts.
-__global__ void host_chunk_finish_kernel(route::RouteMeta* __restrict__ meta, const int* __restrict__ acc) {
-    const int e = threadIdx.x;
-    if (e < route::MAX_E) {
-        meta->counts[e] = acc[e];
-        meta->total[e] = acc[e];
-        meta->cmat[e] = acc[e];
-    }
-}
-
 int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host, const float* concept_bias,
                             int n_concept, float* y_host, int T) {
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
@@ -984,7 +986,9 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     // pass; counts are summed over the chunks. Expert-parallel handles run one pass (all ranks in lock step).
     int chunk = T;
     if (h->world == 1 && T >= 4096) {
-        chunk = 2048;
+        // small chunks keep the un-overlapped first upload and last download short; PRICHS_HOST_CHUNK overrides
+        const char* hc = getenv("PRICHS_HOST_CHUNK");
+        chunk = hc ? std::max(256, atoi(hc) / 16 * 16) : (T >= 8192 ? 1024 : 2048);
         while ((T + chunk - 1) / chunk > MAX_CHUNKS) chunk *= 2;
     }
     const int nchunks = (T + chunk - 1) / chunk;
