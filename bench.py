@@ -387,7 +387,10 @@ def main():
             import ctypes as C
             buf = (C.c_float * 6)()
             for i in range(nstage):
-                step(i)
+                # the measured forward is the last of a back-to-back group, so that the GPU is as busy (and as
+                # power-limited) around it as in the timed region above
+                for r in range(5):
+                    step(5 * i + r)
                 L.prichs_moe_get_stage_ms(layer._h, buf)
                 stage += np.array(list(buf), np.float64)
             stage /= nstage
@@ -439,19 +442,20 @@ def main():
                 s["frac"] = s["GB/s"] / peaks["hbm"]
             if "TFLOP/s" in s:
                 s["frac"] = s["TFLOP/s"] / peaks["tf"]
-        roofline = {"kernel": "expert_gemm_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
+        roofline = {"kernel": "expert_gemm_pair_kernel<EPI_SWIGLU> (gate|up GEMM + SwiGLU, shared + 8 routed experts in one launch)",
                     "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
                     # dram__bytes_read + dram__bytes_write of one launch at this size, from the one-pass ncu capture
                     # summarised in profiles/traffic_config1_full_size.md (bytes); only valid for config 1
-                    "traffic": 323.9e6 if not args.tokens else None,
+                    "traffic": 330.4e6 if not args.tokens else None,
                     "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
+                    "frac_of_sustained_peak": gu_tf / peaks["tf_sustained"] if peaks["tf_sustained"] else None,
                     "algorithmic_flops_per_launch": gu_flops}
     else:
         # Expert-parallel step: the GEMM launches of the waves overlap the exchange of other waves on several
         # streams, so one kernel cannot be timed alone; the figure is this rank's GEMM flops over the WHOLE step.
         stages = None
         tf = rows * 6 * D * F / (ms_step * 1e-3) / 1e12
-        roofline = {"kernel": "expert_gemm_kernel (all GEMM launches of one rank) over the whole expert-parallel step",
+        roofline = {"kernel": "expert_gemm_pair_kernel (all GEMM launches of one rank) over the whole expert-parallel step",
                     "bound": "tensor", "achieved": tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": tf / peaks["tf"],
                     "traffic": None, "peak_source": f"{peaks['source']} bf16_tflops (burst)",
                     "algorithmic_flops_per_launch": rows * 6 * D * F}
