@@ -26,24 +26,31 @@ def main():
     # router columns so that the first experts attract most tokens (the shape of the Zipf-skewed config)
     cases = [(512, 384, 8, 2, 1000, (-0.1, 0.1), 1, False), (1536, 1280, 8, 2, 2048, None, 1, False),
              (512, 384, 8, 2, 3000, (-0.1, 0.1), 3, False), (1536, 1280, 8, 2, 4096, None, 4, False),
-             (512, 384, 8, 2, 2500, None, 2, True)]
+             (512, 384, 8, 2, 2500, None, 2, True),
+             (512, 384, 8, 2, 40, (-0.1, 0.1), 4, False),       # fewer tokens than waves x 16: some waves are empty
+             (512, 384, 8, 2, 700, (-0.1, 0.1), 2, "f32")]      # fp32-fidelity mode across ranks
     for d, f, E, k, T, brange, waves, skew in cases:
+        f32 = skew == "f32"
+        skew = skew is True
         Tr = T + 37 * rank  # ragged: every rank brings a different number of tokens
-        ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=True)
+        ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=not f32)
         bias = synth.router_bias(3, E, *brange) if brange else np.zeros(E, np.float32)
         if skew:
             ws[0] = synth.round_bf16(np.abs(ws[0]) * np.array([6, 4, 3, 2, 1.5, 1, 1, 1], np.float32)[None, :] *
                                      np.sign(synth.normal(5, 1, ws[0].shape)))
             bias = np.array([0.6, 0.3, 0.15, 0, 0, 0, 0, 0], np.float32)
-        x = synth.tokens(3000 + rank, Tr, d, bf16=True)
+        x = synth.tokens(3000 + rank, Tr, d, bf16=not f32)
         El = E // world
-        m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local, ep_waves=waves)
+        m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local, ep_waves=waves, mode="f32" if f32 else "bf16")
         for e in range(E):  # experts owned by other ranks are not uploaded here
             if e // El != rank:
                 m.experts[e].gate_proj = m.experts[e].up_proj = m.experts[e].down_proj = None
         m.router_bias = bias
         ep.connect(m, dist, max_tokens=T + 37 * world)
-        xd = torch.from_numpy(synth.to_bf16_bits(x).view(np.int16)).view(torch.bfloat16).cuda()
+        if f32:
+            xd = torch.from_numpy(x).cuda()
+        else:
+            xd = torch.from_numpy(synth.to_bf16_bits(x).view(np.int16)).view(torch.bfloat16).cuda()
         for rep in range(2):  # twice: buffers are reused across calls
             y = m.forward(xd).float().cpu().numpy()
             m.sync_status()
@@ -69,8 +76,8 @@ def main():
         # outputs against the oracle of the whole layer on this rank's tokens
         ref = O.moe_forward_train(ws, bias, k, x)
         ok = np.all(ref["selected"] == sel, axis=1)
-        assert ok.mean() > 0.995
-        rep_ = assert_close(y[ok], ref["out"][ok], 2e-2, f"EP output rank {rank}")
+        assert (~ok).sum() <= max(2, Tr // 200)
+        rep_ = assert_close(y[ok], ref["out"][ok], 1e-3 if f32 else 2e-2, f"EP output rank {rank}")
         # bias update from the global counts: identical on every rank, equal to the oracle's
         total_tokens = sum(T + 37 * r for r in range(world))
         m.update_bias_from_last(1e-3, total_tokens=total_tokens)  # ragged ranks: the global total is given
