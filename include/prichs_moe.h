@@ -107,6 +107,15 @@ PRICHS_API int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtyp
                        const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T,
                        void* stream);
 
+/* The MoE sub-layer of the reference's block in one call (crates/prichs-model/src/block.rs:64-67):
+ *   y = x_res + MoELayer::forward_with_memory(rms_norm(x_res, norm_weight, eps), concept_bias)
+ * with rms_norm as in crates/prichs-core/src/ops.rs:109-135 (the engine's counterpart is gpu_rmsnorm_forward,
+ * crates/prichs-cuda/src/kernels.cu:329-362). x_res_dev [T,d] of element type x_dtype is both the input of the
+ * norm and the residual; norm_weight_dev is [d] fp32 on the device. hidden_dim <= 2048. */
+PRICHS_API int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype, const float* norm_weight_dev,
+                                        float eps, const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T,
+                                        void* stream);
+
 /* The same call with HOST buffers, the shape in which the reference's MoELayer::forward(&Tensor) -> Tensor
  * is used (f32 row-major slices, tensor.rs:14-29): copies x (and resid) to the device, runs the forward,
  * copies y back and waits for it. Pinned host memory makes the copies asynchronous; pageable memory works.

@@ -21,6 +21,7 @@
 //   crates/prichs-core/src/ops.rs:250-267  add_tensors (the residual add of block.rs:67)
 //   crates/prichs-model/src/moe.rs:93-211  MoELayer::forward_train
 //   crates/prichs-model/src/moe.rs:228-245 MoELayer::update_aux_free_bias
+//   crates/prichs-core/src/ops.rs:109-135  rms_norm (the caller's pre-norm of the MoE sub-layer, block.rs:64)
 //
 // Build: see oracle/Makefile (g++ -O3 -march=native -ffp-contract=off -pthread; the image has no OpenMP runtime).
 
@@ -263,6 +264,20 @@ int oracle_moe_forward_train(const float* const* weights, const float* router_bi
         }
     }
     return 0;
+}
+
+// rms_norm (ops.rs:109-135): per row sum of squares in index order, rms = sqrt(sum/d + eps), inv = 1/rms,
+// out = (x * inv) * weight. Used for the MoE sub-layer of the block (block.rs:64): the caller-side step that the
+// library can fuse in front of the layer.
+void oracle_rms_norm(const float* x, const float* weight, float eps, float* out, size_t rows, size_t d) {
+    parallel_for(rows, [=](size_t r) {
+        const float* row = x + r * d;
+        float sum_sq = 0.0f;
+        for (size_t c = 0; c < d; ++c) sum_sq += row[c] * row[c];
+        const float rms = std::sqrt(sum_sq / (float)d + eps);
+        const float inv_rms = 1.0f / rms;
+        for (size_t c = 0; c < d; ++c) out[r * d + c] = row[c] * inv_rms * weight[c];
+    });
 }
 
 // MoELayer::update_aux_free_bias (moe.rs:228-245).

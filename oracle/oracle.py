@@ -7,6 +7,7 @@ moe_oracle.cpp for what pins it instead.
 
 The functions mirror the reference one to one:
   matmul_2d, swiglu, top_k_gating_unbiased, add_tensors      crates/prichs-core/src/ops.rs:8-61,142-159,219-248,250-267
+  rms_norm                                                    crates/prichs-core/src/ops.rs:109-135
   moe_forward_train, update_aux_free_bias                     crates/prichs-model/src/moe.rs:93-211,228-245
 """
 from __future__ import annotations
@@ -47,6 +48,7 @@ def lib():
                                                C.POINTER(C.c_ubyte), fp, fp, zp, fp, zp, fp]
         L.oracle_moe_forward_train.restype = C.c_int
         L.oracle_update_aux_free_bias.argtypes = [fp, sz, sz, zp, sz, C.c_float]
+        L.oracle_rms_norm.argtypes = [fp, fp, C.c_float, fp, sz, sz]
         _lib = L
     return _lib
 
@@ -109,6 +111,17 @@ def add_tensors(a, b):
         raise ValueError("Tensor length mismatch in addition")
     out = np.empty_like(a)
     lib().oracle_add_tensors(pa, pb, out.ctypes.data_as(C.POINTER(C.c_float)), a.size)
+    return out
+
+
+def rms_norm(x, weight, eps):
+    """rms_norm of ops.rs:109-135 over the last dimension of a 2-D array."""
+    x, px = _f(x)
+    w, pw = _f(weight)
+    if w.size != x.shape[-1]:
+        raise ValueError(f"Weight length {w.size} != hidden_dim {x.shape[-1]}")
+    out = np.empty_like(x)
+    lib().oracle_rms_norm(px, pw, C.c_float(eps), out.ctypes.data_as(C.POINTER(C.c_float)), x.shape[0], x.shape[1])
     return out
 
 

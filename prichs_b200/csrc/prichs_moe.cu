@@ -268,6 +268,7 @@ struct prichs_moe {
     bf16 *w_gu, *w_dn, *w_rt;
     float *w_r8, *bias;
     bf16 *xs, *xp, *hbuf;
+    void* xnorm;  // normalised activations of the block entry point: bf16 [Tmax,d] (fp32 in the fp32-fidelity mode)
     void* ybuf;
     float *logits, *gates;
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
@@ -303,6 +304,7 @@ struct prichs_moe {
     cudaStream_t last_stream;
     int last_T;
     int tok_base;  // see prichs_moe_forward
+    int resid_dtype;  // element type of the residual when it differs from x (block entry point), else -1
     bool timing;
     cudaEvent_t ev[7];
     bool ev_valid;
@@ -422,7 +424,8 @@ int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y
     // expert-parallel: a capped, grid-striding launch; `exclusive` keeps it off the SMs that hold GEMM CTAs
     const int grid = h->world > 1 ? std::min((T + 7) / 8, 4 * h->sm_count) : (T + 7) / 8;
     const int dyn_smem = exclusive ? h->ep_copy_smem : 0;
-    const int res = !resid_dev ? 0 : (x_dtype == PRICHS_DTYPE_BF16 ? 1 : 2);
+    const int rdt = h->resid_dtype >= 0 ? h->resid_dtype : x_dtype;
+    const int res = !resid_dev ? 0 : (rdt == PRICHS_DTYPE_BF16 ? 1 : 2);
     const bool of32 = y_dtype == PRICHS_DTYPE_F32;
 #define COMBINE(YF, OF, RS) \
     route::combine_kernel<YF, OF, RS><<<grid, 256, dyn_smem, st>>>(y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
@@ -513,7 +516,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     // A few SMs stay free of the persistent GEMM CTAs so that the small kernels of the other streams (scans,
     // plans, NCCL) are never queued behind a whole GEMM.
     const int gemm_grid = std::max(2, h->sm_count - h->ep_reserve_sms);
-    const size_t xsz = x_dtype == PRICHS_DTYPE_F32 ? 4 : 2, osz = y_dtype == PRICHS_DTYPE_F32 ? 4 : 2, ysz = f32mode ? 4 : 2;
+    const size_t xsz = (h->resid_dtype >= 0 ? h->resid_dtype : x_dtype) == PRICHS_DTYPE_F32 ? 4 : 2, osz = y_dtype == PRICHS_DTYPE_F32 ? 4 : 2, ysz = f32mode ? 4 : 2;
 
     // 1. router over the whole batch
     rc = launch_router(h, x_dev, x_dtype, cb, T, h->logits, h->sel, h->gates, h->tile_counts, st);
@@ -642,6 +645,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     const int mul = h->mode == PRICHS_MODE_F32 ? 2 : 1;
     h->K1 = d * mul; h->K2 = f * mul;
     h->Tcap = round_up(h->Tmax, SEG_PAD);
+    h->resid_dtype = -1;
     h->n_waves = 1;
     if (world > 1) {
         const int want = cfg->ep_waves > 0 ? cfg->ep_waves : h->Tmax / 8192;
@@ -672,6 +676,12 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->bias, route::MAX_E));
     A(dalloc(&h->xs, (size_t)h->Tmax * h->K1));
     A(dalloc(&h->xp, (size_t)h->Rcap * h->K1));
+    {
+        void* p = nullptr;
+        if (rc == PRICHS_OK && cudaMalloc(&p, (size_t)h->Tmax * d * (h->mode == PRICHS_MODE_F32 ? 4 : 2)) != cudaSuccess)
+            rc = fail(PRICHS_ERR_CUDA, "cudaMalloc of the normalised-activation buffer failed");
+        h->xnorm = p;
+    }
     A(dalloc(&h->hbuf, rows_all * h->K2));
     {
         void* p = nullptr;
@@ -781,7 +791,7 @@ int prichs_moe_destroy(prichs_moe_t* h) {
         if (wv.mtile_slot) cudaFree(wv.mtile_slot);
         if (wv.token) cudaFree(wv.token);
     }
-    void* ptrs[] = {h->ep_zero, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
+    void* ptrs[] = {h->xnorm, h->ep_zero, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
                     h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
                     h->stage_r, h->stage_y};
     for (void* p : ptrs)
@@ -954,6 +964,37 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     mark();
     h->ev_valid = timing;
     return PRICHS_OK;
+}
+
+int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype, const float* norm_weight_dev, float eps,
+                             const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (!x_res_dev || !norm_weight_dev || !y_dev) return fail(PRICHS_ERR_BAD_ARG, "null device pointer");
+    if (x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    if (T < 0 || T > h->Tmax) return fail(PRICHS_ERR_CAPACITY, "T=%d exceeds max_tokens=%d of this handle", T, h->Tmax);
+    if (h->d > 2048) return fail(PRICHS_ERR_BAD_SHAPE, "the fused pre-norm supports hidden_dim up to 2048");
+    if (h->mode == PRICHS_MODE_F32 && x_dtype != PRICHS_DTYPE_F32) return fail(PRICHS_ERR_BAD_ARG, "the fp32-fidelity mode takes fp32 activations");
+    if ((reinterpret_cast<uintptr_t>(x_res_dev) & 15) || (reinterpret_cast<uintptr_t>(norm_weight_dev) & 15))
+        return fail(PRICHS_ERR_BAD_ARG, "activation and weight pointers must be 16-byte aligned");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+    const bool of32 = h->mode == PRICHS_MODE_F32;
+    if (T > 0) {
+        DeviceGuard guard(h->device);
+        const int grid = (T + 7) / 8;
+        if (x_dtype == PRICHS_DTYPE_F32) {
+            if (of32) route::rmsnorm_rows_kernel<true, true, 8><<<grid, 256, 0, st>>>(x_res_dev, norm_weight_dev, eps, h->xnorm, T, h->d);
+            else route::rmsnorm_rows_kernel<true, false, 8><<<grid, 256, 0, st>>>(x_res_dev, norm_weight_dev, eps, h->xnorm, T, h->d);
+        } else {
+            route::rmsnorm_rows_kernel<false, false, 8><<<grid, 256, 0, st>>>(x_res_dev, norm_weight_dev, eps, h->xnorm, T, h->d);
+        }
+        LAUNCH_CHECK("pre-norm");
+    }
+    // the normalised rows are the layer's input, the un-normalised ones its fused residual (block.rs:64-67)
+    h->resid_dtype = x_dtype;  // the residual keeps the caller's element type even when the normalised input is bf16
+    const int rc = prichs_moe_forward(h, h->xnorm, of32 ? PRICHS_DTYPE_F32 : PRICHS_DTYPE_BF16, x_res_dev, concept_bias, n_concept,
+                                      y_dev, y_dtype, T, stream_);
+    h->resid_dtype = -1;
+    return rc;
 }
 
 int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host, const float* concept_bias,

@@ -558,6 +558,71 @@ combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtr
 }
 
 // ---------------------------------------------------------------------------------------------------
+// Pre-norm of the block's MoE sub-layer (crates/prichs-model/src/block.rs:64, rms_norm of
+// crates/prichs-core/src/ops.rs:109-135): out = (x * inv_rms) * weight with inv_rms = 1 / sqrt(mean(x^2) + eps).
+// One warp per row, the row stays in registers between the two passes. XF32: x is fp32 (else bf16);
+// OF32: the normalised row is written as fp32 (fp32-fidelity mode) else bf16. d is a multiple of 256.
+template <bool XF32, bool OF32, int MAXC>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const void* __restrict__ x, const float* __restrict__ weight, float eps, void* __restrict__ out, int T, int d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    float v[MAXC][8];
+    float ss = 0.f;
+    const int nchunk = d / 256;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        if (i < nchunk) {
+            const int c = i * 256 + lane * 8;
+            if (XF32) {
+                const float* p = reinterpret_cast<const float*>(x) + (size_t)t * d + c;
+                const uint4 a = ptx::ld_stream_16(p), b = ptx::ld_stream_16(p + 4);
+                v[i][0] = __uint_as_float(a.x); v[i][1] = __uint_as_float(a.y); v[i][2] = __uint_as_float(a.z); v[i][3] = __uint_as_float(a.w);
+                v[i][4] = __uint_as_float(b.x); v[i][5] = __uint_as_float(b.y); v[i][6] = __uint_as_float(b.z); v[i][7] = __uint_as_float(b.w);
+            } else {
+                const uint4 a = ptx::ld_stream_16(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)t * d + c);
+                const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[i][2 * j] = __uint_as_float(w[j] << 16);
+                    v[i][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv_rms = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        if (i < nchunk) {
+            const int c = i * 256 + lane * 8;
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + c)), w1 = __ldg(reinterpret_cast<const float4*>(weight + c + 4));
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            float o8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o8[j] = __fmul_rn(__fmul_rn(v[i][j], inv_rms), wv[j]);
+            if (OF32) {
+                float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * d + c);
+                op[0] = make_float4(o8[0], o8[1], o8[2], o8[3]);
+                op[1] = make_float4(o8[4], o8[5], o8[6], o8[7]);
+            } else {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(o8[2 * j], o8[2 * j + 1]);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * d + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
 // b_i += gamma * (top_k / E - count_i / total_tokens), each operation rounded on its own like the
 // reference's f32 arithmetic (moe.rs:237-244). count_i is the total over all ranks.
 __global__ void bias_update_kernel(float* __restrict__ bias, const RouteMeta* __restrict__ meta, int E, int top_k,

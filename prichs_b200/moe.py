@@ -236,6 +236,31 @@ class MoELayer:
     def forward(self, x, **kw):
         return self.forward_with_memory(x, None, **kw)
 
+    def block_forward(self, x_residual, post_attn_norm, eps: float, starkdb_concept_bias=None, out=None, stream=None):
+        """The MoE sub-layer of PrichsBlock::forward_with_rope (crates/prichs-model/src/block.rs:64-67) in one call:
+        x_residual + MoE(rms_norm(x_residual, post_attn_norm, eps)). CUDA torch tensors; `post_attn_norm` is [d] fp32."""
+        import torch
+        x = x_residual
+        if not (isinstance(x, torch.Tensor) and x.is_cuda) or x.dim() != 2 or x.shape[1] != self.hidden_dim:
+            raise PrichsError(_capi.ERR_BAD_SHAPE, "x_residual must be a CUDA tensor of shape [T, hidden_dim]")
+        if post_attn_norm.numel() != self.hidden_dim:
+            raise PrichsError(_capi.ERR_BAD_SHAPE, f"Weight length {post_attn_norm.numel()} != hidden_dim {self.hidden_dim}")
+        dt = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}[x.dtype]
+        x = x.contiguous()
+        w = post_attn_norm.to(device=x.device, dtype=torch.float32).contiguous()
+        T = x.shape[0]
+        if self._device < 0:
+            self._device = x.device.index
+        self._ensure(T)
+        y = out if out is not None else torch.empty_like(x)
+        ydt = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}[y.dtype]
+        cb_ptr, cb_n, _keep = self._cb(starkdb_concept_bias)
+        st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
+        _check(_capi.lib().prichs_moe_block_forward(self._h, x.data_ptr(), dt, w.data_ptr(), C.c_float(eps), cb_ptr, cb_n,
+                                                    y.data_ptr(), ydt, T, st))
+        self._T_last = T
+        return y
+
     def forward_train(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, **kw):
         out = self.forward_with_memory(x, starkdb_concept_bias, **kw)
         return out, self.last_stash()

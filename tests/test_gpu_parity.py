@@ -273,6 +273,61 @@ def test_residual_and_concept_bias(torch_cuda, oracle):
     np.testing.assert_allclose(y - y0, resid, atol=2e-6 * (1 + np.abs(y).max()))
 
 
+@pytest.mark.parametrize("mode,x_kind", [("bf16", "bf16"), ("bf16", "f32"), ("f32", "f32")])
+def test_block_sublayer_prenorm_moe_residual(torch_cuda, oracle, mode, x_kind):
+    """x_res + MoE(rms_norm(x_res, w, eps)) in one call (crates/prichs-model/src/block.rs:64-67, ops.rs:109-135)."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    d, f, E, k, T, eps = 512, 384, 8, 2, 300, 1e-5
+    bf = mode == "bf16"
+    ws = synth.layer_weights(61, d, f, E, std=0.03, bf16=bf)
+    bias = synth.router_bias(61, E, -0.1, 0.1)
+    x_res = synth.normal(62, 0, (T, d), 0.0, 3.0)
+    if x_kind == "bf16":
+        x_res = synth.round_bf16(x_res)
+    w = (1.0 + 0.1 * synth.normal(63, 0, (d,))).astype(np.float32)
+    m = MoELayer.from_weights(ws, k, mode=mode)
+    m.router_bias = bias
+    xd = _to_dev(torch, x_res, x_kind)
+    y = _to_host(m.block_forward(xd, torch.from_numpy(w), eps))
+    m.sync_status()
+    st = m.last_stash()
+    # oracle: the layer's input is the normalised row (rounded to bf16 in bf16 mode, like any input of that mode)
+    xn = oracle.rms_norm(x_res, w, eps)
+    if bf:
+        xn = synth.round_bf16(xn)
+    given = oracle.route(None, ws[0], bias, k, logits=st.router_logits)
+    sel = st.selected_experts.reshape(T, k)
+    assert np.array_equal(sel, given["selected"]) and np.array_equal(st.expert_token_counts, given["counts"])
+    ref = oracle.moe_forward_train(ws, bias, k, xn)
+    agree = np.all(ref["selected"] == sel, axis=1)
+    assert (~agree).sum() <= max(2, T // 100)
+    assert_close(st.router_logits, ref["logits"], 2e-3 if bf else 1e-4, "logits of the normalised rows")
+    exp = oracle.add_tensors(x_res, ref["out"]).reshape(T, d)
+    tol = TOL_BF16 if bf else TOL_F32
+    assert_close(y[agree], exp[agree], tol, "block output")
+
+
+def test_rmsnorm_reference_fixture_values(torch_cuda, oracle):
+    """The reference's RMSNorm fixture (crates/prichs-cuda/src/engine.rs:3032-3064): rows [1,2,3,4] and [2,2,2,2],
+    weight 1 -- here tiled to the supported width; checked through the block entry point with zero expert weights,
+    where y = x_res exactly, and against the oracle's rms_norm through the router logits."""
+    import torch
+    from prichs_b200 import MoELayer
+    d, f, E, k = 256, 128, 8, 2
+    ws = small_int_weights(3, d, f, E)
+    for i in range(1, len(ws)):
+        ws[i] = np.zeros_like(ws[i])  # experts output zero: the layer returns the residual
+    x = np.stack([np.tile([1.0, 2.0, 3.0, 4.0], d // 4), np.full(d, 2.0)]).astype(np.float32)
+    m = MoELayer.from_weights(ws, k, mode="f32")
+    y = m.block_forward(torch.from_numpy(x).cuda(), torch.ones(d), 1e-5).cpu().numpy()
+    assert np.array_equal(y, x)
+    xn = oracle.rms_norm(x, np.ones(d, np.float32), 1e-5)
+    np.testing.assert_allclose(xn[0, :4], np.array([1, 2, 3, 4]) / np.sqrt(7.5 + 1e-5), rtol=1e-6)
+    np.testing.assert_allclose(xn[1], 2.0 / np.sqrt(4.0 + 1e-5), rtol=1e-6)
+    assert_close(m.last_stash().router_logits, oracle.matmul_2d(xn, ws[0]), 1e-5, "logits = rms_norm(x) . W_r")
+
+
 def test_collisions_all_tokens_to_two_experts_and_empty_experts(torch_cuda, oracle):
     d, f, E, k, T = 256, 128, 8, 2, 260
     ws, x, _ = _synth_case(44, T, d, f, E, std=0.05)

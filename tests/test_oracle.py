@@ -180,3 +180,15 @@ def test_route_with_given_logits(oracle):
         i, w = np_top_k_unbiased(lg[t], lg[t] + bias, 2)
         assert r["selected"][t].tolist() == i.tolist()
     assert int(r["counts"].sum()) == 100
+
+
+def test_rms_norm_known_answer(oracle):
+    # the reference's own RMSNorm check uses x = [1, 2, 3, 4], weight 1, eps 1e-5 (crates/prichs-cli/src/main.rs:1210-1213,
+    # crates/prichs-cuda/src/engine.rs:3032-3064): rms = sqrt(30/4 + 1e-5)
+    x = np.array([[1.0, 2.0, 3.0, 4.0]], np.float32)
+    out = oracle.rms_norm(x, np.ones(4, np.float32), 1e-5)
+    np.testing.assert_allclose(out, x / np.sqrt(7.5 + 1e-5), rtol=1e-6)
+    w = np.array([0.5, 2.0, -1.0, 0.0], np.float32)
+    np.testing.assert_allclose(oracle.rms_norm(x, w, 1e-5), x / np.sqrt(7.5 + 1e-5) * w, rtol=1e-6)
+    with pytest.raises(ValueError):
+        oracle.rms_norm(x, np.ones(3, np.float32), 1e-5)
