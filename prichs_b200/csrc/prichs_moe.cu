@@ -347,7 +347,10 @@ int translate_status(int s) {
 int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::ConceptBias& cb, int T, float* logits, int* sel,
                   float* gates, int* tile_counts, cudaStream_t st) {
     const int d = h->d, E = h->E;
-    const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    const int ntiles_all = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+    // PRICHS_ROUTER_CTAS_PER_SM caps the router grid (the kernel strides over tiles); 0 = one CTA per tile
+    static const int cap_per_sm = [] { const char* e = getenv("PRICHS_ROUTER_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+    const int ntiles = cap_per_sm > 0 && h->mode != PRICHS_MODE_F32 ? std::min(ntiles_all, cap_per_sm * h->sm_count) : ntiles_all;
     if (h->mode == PRICHS_MODE_F32) {
         route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
                                                         logits, sel, gates, tile_counts);

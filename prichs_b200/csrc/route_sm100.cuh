@@ -147,8 +147,11 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
                   int* __restrict__ tile_counts) {
     __shared__ float4 partial[ROUTER_WARPS][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x;
     const int g = lane >> 2, q = lane & 3;
+    const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
+    // grid-stride over tiles: with fewer CTAs than tiles the CTAs of an SM drift out of phase, so the loads of
+    // one overlap the reduction and selection of another
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
     const size_t r0c = (size_t)min(r0, T - 1), r1c = (size_t)min(r1, T - 1);
 
@@ -202,7 +205,7 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
     }
     partial[warp][lane] = make_float4(c[0], c[1], c[2], c[3]);
     __syncthreads();
-    if (warp != 0) return;
+    if (warp == 0) {
 #pragma unroll
     for (int w = 1; w < ROUTER_WARPS; ++w) {
         const float4 p = partial[w][lane];
@@ -226,6 +229,9 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
     const uint32_t below = (1u << (4 * g)) - 1u;
     const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
     route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
+    }
+    __syncthreads();  // `partial` is reused by the next tile
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------
