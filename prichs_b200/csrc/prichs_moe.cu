@@ -662,8 +662,11 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
                                                              : (long long)world * tw_max * k);
     const long long rw = (recv + (long long)h->El * (SEG_PAD - 1) + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
     const long long rcap = rw * h->n_waves;
-    if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30))
-        return fail(PRICHS_ERR_CAPACITY, "workspace for max_tokens=%d is too large", h->Tmax);
+    if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30)) {
+        const int tmax = h->Tmax;
+        delete h;
+        return fail(PRICHS_ERR_CAPACITY, "workspace for max_tokens=%d is too large", tmax);
+    }
     h->Rcap = (int)rcap;
     h->Rw = (int)rw;
     h->sm_count = prop.multiProcessorCount;
@@ -1132,6 +1135,8 @@ int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* expert_token_
     if (!h || !expert_token_counts) return fail(PRICHS_ERR_BAD_ARG, "null handle or counts");
     if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "counts has %d entries, the layer has %d experts", n, h->E);
     if (total_tokens == 0) return PRICHS_OK;  // the reference returns early (moe.rs:233-235)
+    for (int i = 0; i < n; ++i)
+        if (expert_token_counts[i] > 0x7fffffffull) return fail(PRICHS_ERR_BAD_ARG, "expert_token_counts[%d] does not fit 31 bits", i);
     DeviceGuard guard(h->device);
     // Host-supplied counts: same arithmetic as the device kernel, applied through a scratch RouteMeta.
     route::RouteMeta* tmp = nullptr;

@@ -192,3 +192,35 @@ def test_rms_norm_known_answer(oracle):
     np.testing.assert_allclose(oracle.rms_norm(x, w, 1e-5), x / np.sqrt(7.5 + 1e-5) * w, rtol=1e-6)
     with pytest.raises(ValueError):
         oracle.rms_norm(x, np.ones(3, np.float32), 1e-5)
+
+
+def test_route_properties_hypothesis(oracle):
+    """Randomised properties of the routing restatement: gates of a token sum to 1, the selected experts are distinct,
+    adding a constant to all selection logits changes nothing, and a bias only changes WHICH experts are picked, never
+    the gate formula (gates depend on the raw logits of the picked experts, ops.rs:233-245)."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.integers(1, 40), st.integers(2, 8), st.integers(1, 2), st.integers(0, 2**31 - 1))
+    def prop(T, E, k, seed):
+        rng = np.random.default_rng(seed)
+        lg = rng.standard_normal((T, E)).astype(np.float32) * 3
+        bias = rng.standard_normal(E).astype(np.float32)
+        w = np.zeros((4, E), np.float32)
+        r = oracle.route(None, w, bias, k, logits=lg)
+        assert np.allclose(r["gating"].sum(axis=1), 1.0, atol=1e-6)
+        assert all(len(set(row)) == k for row in r["selected"].tolist())
+        assert int(r["counts"].sum()) == T * k
+        r2 = oracle.route(None, w, bias + np.float32(8.0), k, logits=lg)  # exact shift: 8 is a power of two
+        shifted_same = np.array_equal((lg + bias).astype(np.float32) + np.float32(8.0), lg + (bias + np.float32(8.0)))
+        if shifted_same:
+            assert np.array_equal(r["selected"], r2["selected"])
+        for t in range(T):
+            raw = lg[t, r["selected"][t]]
+            e = np.exp(raw - raw.max(), dtype=np.float32)
+            s = np.float32(0)
+            for v in e:
+                s = np.float32(s + v)
+            assert np.allclose(r["gating"][t], e * (np.float32(1) / np.float32(s + np.float32(1e-9))), rtol=2e-6)
+
+    prop()
