@@ -49,6 +49,7 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    ptx::grid_dep_launch();
     const uint32_t cta_rank = ptx::cluster_ctarank();  // 0 = leader
     const bool leader = cta_rank == 0;
 
@@ -73,6 +74,8 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
     ptx::cluster_sync();  // the peer's barriers are initialised before anything signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    // set-up above touched no global memory; everything below may depend on the previous kernel of the stream
+    ptx::grid_dep_wait();
 
     // tiles are enumerated in 256-row pairs: pair p covers 128-row tiles 2p and 2p+1 of the same kind
     const int shared_pairs = (args.shared_mtiles + 1) / 2;

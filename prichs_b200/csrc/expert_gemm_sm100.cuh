@@ -106,6 +106,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    ptx::grid_dep_launch();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -127,6 +128,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    // set-up above touched no global memory; everything below may depend on the previous kernel of the stream
+    ptx::grid_dep_wait();
 
     const int total_mtiles = args.shared_mtiles + *args.n_routed_mtiles;
     const int total_tiles = total_mtiles * args.n_ntiles;

@@ -58,6 +58,24 @@ int fail(int code, const char* fmt, ...) {
 
 using bf16 = __nv_bfloat16;
 
+// Kernel launch with the programmatic-dependent-launch attribute when `pdl` is set: the kernel may then be
+// scheduled while its predecessor in the stream still runs and blocks at its griddepcontrol.wait until that one
+// has completed. Kernel names that contain commas go in parentheses.
+#define LAUNCH_K(pdl, kern, grid, block, smem, st, ...)                                        \
+    do {                                                                                       \
+        cudaLaunchConfig_t c__ = {};                                                           \
+        c__.gridDim = dim3((unsigned)(grid));                                                  \
+        c__.blockDim = dim3((unsigned)(block));                                                \
+        c__.dynamicSmemBytes = (size_t)(smem);                                                 \
+        c__.stream = (st);                                                                     \
+        cudaLaunchAttribute a__[1];                                                            \
+        a__[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                        \
+        a__[0].val.programmaticStreamSerializationAllowed = 1;                                 \
+        c__.attrs = a__;                                                                       \
+        c__.numAttrs = (pdl) ? 1 : 0;                                                          \
+        cudaLaunchKernelEx(&c__, kern, __VA_ARGS__);                                           \
+    } while (0)
+
 // cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link libcuda.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -277,6 +295,7 @@ struct prichs_moe {
     CUtensorMap tm_h_out, tm_y_out;  // 32-row store boxes of the GEMM epilogues
     CUtensorMap tm_wgu_half, tm_wdn_half;  // 128-row boxes: one CTA's half of a B tile in the CTA-pair kernel
     bool pair_gemm;  // use the CTA-pair (cta_group::2) GEMM kernel
+    bool pdl;  // launch the kernels of the single-GPU forward with programmatic dependent launch
     bool small_batch;  // this forward has so few rows that 128-row tiles on single CTAs spread better over the SMs
 
     // expert-parallel group: peers' receive / output buffers mapped into this process, and the token waves
@@ -345,7 +364,7 @@ int translate_status(int s) {
 // ---- launch helpers shared by the single-GPU and the expert-parallel forward ---------------------------
 // Router over T tokens starting at `x_dev`; routing arrays are the caller's (already offset) pointers.
 int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::ConceptBias& cb, int T, float* logits, int* sel,
-                  float* gates, int* tile_counts, cudaStream_t st) {
+                  float* gates, int* tile_counts, cudaStream_t st, bool pdl = false) {
     const int d = h->d, E = h->E;
     const int ntiles_all = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     // PRICHS_ROUTER_CTAS_PER_SM caps the router grid (the kernel strides over tiles); 0 = one CTA per tile
@@ -358,14 +377,14 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
         constexpr int RT = route::ROUTER_WARPS * 32;
         if (x_dtype == PRICHS_DTYPE_F32) {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, true><<<ntiles, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+                LAUNCH_K(pdl, (route::router_mma_kernel<1, true>), ntiles, RT, 0, st, (const void*)x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
             else
-                route::router_mma_kernel<3, true><<<ntiles, RT, 0, st>>>(x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+                LAUNCH_K(pdl, (route::router_mma_kernel<3, true>), ntiles, RT, 0, st, (const void*)x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
         } else {
             if (h->rt_nsplit == 1)
-                route::router_mma_kernel<1, false><<<ntiles, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+                LAUNCH_K(pdl, (route::router_mma_kernel<1, false>), ntiles, RT, 0, st, (const void*)x_dev, (bf16*)nullptr, (const bf16*)h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
             else
-                route::router_mma_kernel<3, false><<<ntiles, RT, 0, st>>>(x_dev, nullptr, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+                LAUNCH_K(pdl, (route::router_mma_kernel<3, false>), ntiles, RT, 0, st, (const void*)x_dev, (bf16*)nullptr, (const bf16*)h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
         }
     }
     LAUNCH_CHECK("router");
@@ -402,18 +421,18 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
 
 // One grouped-GEMM launch: epi 0 = gate|up + SwiGLU into H, epi 1 = down projection into Y.
 int launch_expert_gemm(prichs_moe* h, int epi, const CUtensorMap& tm_a_shared, const CUtensorMap& tm_a_routed, const egemm::Args& a,
-                       int grid, cudaStream_t st) {
+                       int grid, cudaStream_t st, bool pdl = false) {
     if (h->pair_gemm && !h->small_batch) {
         const int g2 = std::max(2, grid & ~1);  // whole CTA pairs
         if (epi == 0)
-            egemm::expert_gemm_pair_kernel<egemm::EPI_SWIGLU><<<g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wgu_half, h->tm_h_out, a);
+            LAUNCH_K(pdl, egemm::expert_gemm_pair_kernel<egemm::EPI_SWIGLU>, g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st, tm_a_shared, tm_a_routed, h->tm_wgu_half, h->tm_h_out, a);
         else
-            egemm::expert_gemm_pair_kernel<egemm::EPI_PLAIN><<<g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wdn_half, h->tm_y_out, a);
+            LAUNCH_K(pdl, egemm::expert_gemm_pair_kernel<egemm::EPI_PLAIN>, g2, egemm::NUM_THREADS, egemm::PAIR_SMEM_BYTES, st, tm_a_shared, tm_a_routed, h->tm_wdn_half, h->tm_y_out, a);
     } else {
         if (epi == 0)
-            egemm::expert_gemm_kernel<egemm::EPI_SWIGLU><<<grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wgu, h->tm_h_out, a);
+            LAUNCH_K(pdl, egemm::expert_gemm_kernel<egemm::EPI_SWIGLU>, grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st, tm_a_shared, tm_a_routed, h->tm_wgu, h->tm_h_out, a);
         else
-            egemm::expert_gemm_kernel<egemm::EPI_PLAIN><<<grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st>>>(tm_a_shared, tm_a_routed, h->tm_wdn, h->tm_y_out, a);
+            LAUNCH_K(pdl, egemm::expert_gemm_kernel<egemm::EPI_PLAIN>, grid, egemm::NUM_THREADS, egemm::SMEM_BYTES, st, tm_a_shared, tm_a_routed, h->tm_wdn, h->tm_y_out, a);
     }
     LAUNCH_CHECK(epi == 0 ? "gate/up GEMM" : "down GEMM");
     return PRICHS_OK;
@@ -423,7 +442,7 @@ int launch_expert_gemm(prichs_moe* h, int epi, const CUtensorMap& tm_a_shared, c
 // are the caller's (already offset) pointers.
 int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y_peers, long long routed_base_rows, const int* sel,
                    const float* gates, const int* pos, const void* resid_dev, void* y_dev, int x_dtype, int y_dtype, int T,
-                   cudaStream_t st, bool exclusive = false) {
+                   cudaStream_t st, bool exclusive = false, bool pdl = false) {
     // expert-parallel: a capped, grid-striding launch; `exclusive` keeps it off the SMs that hold GEMM CTAs
     const int grid = h->world > 1 ? std::min((T + 7) / 8, 4 * h->sm_count) : (T + 7) / 8;
     const int dyn_smem = exclusive ? h->ep_copy_smem : 0;
@@ -431,7 +450,7 @@ int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y
     const int res = !resid_dev ? 0 : (rdt == PRICHS_DTYPE_BF16 ? 1 : 2);
     const bool of32 = y_dtype == PRICHS_DTYPE_F32;
 #define COMBINE(YF, OF, RS) \
-    route::combine_kernel<YF, OF, RS><<<grid, 256, dyn_smem, st>>>(y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
+    LAUNCH_K(pdl, (route::combine_kernel<YF, OF, RS>), grid, 256, dyn_smem, st, y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
     if (h->mode == PRICHS_MODE_F32) {
         if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
         else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
@@ -755,6 +774,8 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->ep_reserve_sms = rs ? std::max(0, std::min(64, atoi(rs))) & ~1 : 20;
         const char* ex = getenv("PRICHS_EP_EXCLUSIVE");
         h->ep_copy_smem = (ex && atoi(ex) == 0) ? 0 : 8192;
+        const char* pd = getenv("PRICHS_PDL");
+        h->pdl = pd && atoi(pd) != 0;
         const char* cm = getenv("PRICHS_EP_COMBINE_MODE");
         h->ep_combine_mode = cm ? atoi(cm) : 1;
     }
@@ -938,12 +959,13 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     mark();
     // 1. router
-    rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st);
+    const bool pdl = h->pdl;
+    rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st, pdl);
     if (rc != PRICHS_OK) return rc;
     mark();
     // 2. prefix sums + placement plan
-    route::scan_kernel<<<1, 1024, 0, st>>>(h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0, h->Rcap, 1,
-                                           SEG_PAD, h->status);
+    LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0,
+             h->Rcap, 1, SEG_PAD, h->status);
     LAUNCH_CHECK("scan");
     mark();
     // 3. dispatch
@@ -952,20 +974,21 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         xp_peers.p[i] = h->xp;
         y_peers.p[i] = h->ybuf;
     }
-    route::dispatch_kernel<<<(T + 7) / 8, 256, 0, st>>>(a_shared, h->K1, T, sel, h->tile_prefix, h->meta, xp_peers, h->El, pos);
+    LAUNCH_K(pdl, route::dispatch_kernel, (T + 7) / 8, 256, 0, st, a_shared, h->K1, T, (const int*)sel, (const int*)h->tile_prefix,
+             (const route::RouteMeta*)h->meta, xp_peers, h->El, pos);
     LAUNCH_CHECK("dispatch");
     mark();
     // 4. gate|up GEMM + SwiGLU for the shared and all routed experts, 5. down GEMM
     egemm::Args a1, a2;
     gemm_args(h, T, 0, &h->meta->n_routed_mtiles, h->mtile_slot, &a1, &a2);
-    rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, h->sm_count, st);
+    rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, h->sm_count, st, pdl);
     if (rc != PRICHS_OK) return rc;
     mark();
-    rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, h->sm_count, st);
+    rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, h->sm_count, st, pdl);
     if (rc != PRICHS_OK) return rc;
     mark();
     // 6. combine (+ residual)
-    rc = launch_combine(h, h->ybuf, y_peers, h->Tcap, sel, gates, pos, resid_dev, y_dev, x_dtype, y_dtype, T, st);
+    rc = launch_combine(h, h->ybuf, y_peers, h->Tcap, sel, gates, pos, resid_dev, y_dev, x_dtype, y_dtype, T, st, false, pdl);
     if (rc != PRICHS_OK) return rc;
     mark();
     h->ev_valid = timing;

@@ -226,6 +226,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
                  : "memory");
 }
 
+// ---- programmatic dependent launch: both are no-ops in a grid that was launched without the attribute ------
+// Lets the next kernel of the stream be scheduled while this grid is still running (its CTAs then sit at
+// grid_dep_wait until this grid has completed and its memory operations are visible).
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- legacy warp-level MMA used by the router (N = 8 experts fits m16n8k16 exactly) -----------------
 __device__ __forceinline__ void mma_m16n8k16_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                   uint32_t b0, uint32_t b1) {

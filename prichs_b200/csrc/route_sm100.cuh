@@ -146,6 +146,8 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
                   float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
                   int* __restrict__ tile_counts) {
     __shared__ float4 partial[ROUTER_WARPS][32];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
@@ -244,6 +246,8 @@ router_f32_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, c
                   float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
                   int* __restrict__ tile_counts) {
     __shared__ float sl[TILE_TOKENS][MAX_E];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x;
     const int row = tile * TILE_TOKENS + warp;
@@ -364,6 +368,8 @@ scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, 
             int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
             int pad_rows, int* __restrict__ status) {
     __shared__ int warp_tot[32][MAX_E];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per = (ntiles + 1023) / 1024;
     const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
@@ -441,6 +447,8 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, cons
                 const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
                 int* __restrict__ pos) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     if (meta->overflow) return;
     // grid-stride over tokens: the expert-parallel forward caps the grid so that this NVLink-bound kernel
     // does not flood the SMs it shares with a concurrently running GEMM
@@ -485,6 +493,8 @@ combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtr
                const int* __restrict__ sel, const float* __restrict__ gates, const int* __restrict__ pos,
                const void* __restrict__ resid, void* __restrict__ out, int T, int d, int El) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     for (int t = blockIdx.x * 8 + warp; t < T; t += gridDim.x * 8) {  // grid-stride (see dispatch_kernel)
     const int2 s = *reinterpret_cast<const int2*>(sel + (size_t)t * 2);
     const float2 gw = *reinterpret_cast<const float2*>(gates + (size_t)t * 2);
