@@ -22,6 +22,7 @@
 //   crates/prichs-model/src/moe.rs:93-211  MoELayer::forward_train
 //   crates/prichs-model/src/moe.rs:228-245 MoELayer::update_aux_free_bias
 //   crates/prichs-core/src/ops.rs:109-135  rms_norm (the caller's pre-norm of the MoE sub-layer, block.rs:64)
+//   crates/prichs-model/src/model.rs:566-766  MoE part of the backward pass (second half of this file)
 //
 // Build: see oracle/Makefile (g++ -O3 -march=native -ffp-contract=off -pthread; the image has no OpenMP runtime).
 
@@ -290,6 +291,184 @@ void oracle_update_aux_free_bias(float* router_bias, size_t E, size_t top_k, con
         const float diff = target_load - actual_load;
         router_bias[i] += gamma * diff;
     }
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Backward of the MoE sub-layer: part A of the per-block loop of PrichsModel::forward_backward
+// (crates/prichs-model/src/model.rs:566-783). Restated for the next stage of the GPU work (the layer's backward
+// pass); the helpers follow
+//   crates/prichs-core/src/ops.rs:64-82      matmul_at_b   dW[i,j] += sum_t a[t,i] * b[t,j]   (t ascending, accumulates)
+//   crates/prichs-core/src/ops.rs:86-104     matmul_a_bt   dX[i,j]  = sum_c dy[i,c] * w[j,c]  (c ascending, overwrites)
+//   crates/prichs-core/src/backward.rs:247-266  swiglu_activation_backward
+//   crates/prichs-core/src/backward.rs:269-287  moe_router_unbiased_backward
+
+namespace {
+
+// ops.rs:64-82, CPU branch (rows of dW in parallel, t ascending inside).
+void matmul_at_b(const float* a, const float* b, float* dw, size_t m, size_t k, size_t n) {
+    parallel_for(k, [=](size_t i) {
+        float* dw_row = dw + i * n;
+        for (size_t t = 0; t < m; ++t) {
+            const float a_val = a[t * k + i];
+            const float* b_row = b + t * n;
+            for (size_t j = 0; j < n; ++j) dw_row[j] += a_val * b_row[j];
+        }
+    });
+}
+
+// ops.rs:86-104, CPU branch.
+void matmul_a_bt(const float* dy, const float* w, float* dx, size_t m, size_t k, size_t n) {
+    parallel_for(m, [=](size_t i) {
+        const float* dy_row = dy + i * k;
+        for (size_t j = 0; j < n; ++j) {
+            const float* w_row = w + j * k;
+            float dot = 0.0f;
+            for (size_t c = 0; c < k; ++c) dot += dy_row[c] * w_row[c];
+            dx[i * n + j] = dot;
+        }
+    });
+}
+
+// backward.rs:247-266
+void swiglu_activation_backward(const float* d_y, const float* gate_pre_act, const float* up_proj, float* d_gate,
+                                float* d_up, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        const float g = gate_pre_act[i], u = up_proj[i], dy = d_y[i];
+        const float sig_g = 1.0f / (1.0f + std::exp(-g));
+        const float silu_g = g * sig_g;
+        const float d_silu_g = sig_g * (1.0f + g * (1.0f - sig_g));
+        d_up[i] = dy * silu_g;
+        d_gate[i] = dy * u * d_silu_g;
+    }
+}
+
+// Expert MLP backward shared by the shared expert (model.rs:571-635) and a routed expert (model.rs:664-719):
+// given the expert's input rows xe [n,d], its stashed gate/up/act [n,f] and the gradient of its output dy [n,d],
+// accumulates dW_gate, dW_up, dW_down and writes dx = d_gate . W_gate^T and dx_tmp = d_up . W_up^T (kept apart:
+// the callers add them in the reference's order).
+void expert_backward(const float* xe, const float* gate, const float* up, const float* act, const float* dy,
+                     const float* wg, const float* wu, const float* wd, float* gwg, float* gwu, float* gwd, float* dx,
+                     float* dx_tmp, size_t n, size_t d, size_t f) {
+    matmul_at_b(act, dy, gwd, n, f, d);
+    std::vector<float> d_act(n * f), d_gate(n * f), d_up(n * f);
+    matmul_a_bt(dy, wd, d_act.data(), n, d, f);
+    swiglu_activation_backward(d_act.data(), gate, up, d_gate.data(), d_up.data(), n * f);
+    matmul_at_b(xe, d_gate.data(), gwg, n, d, f);
+    matmul_at_b(xe, d_up.data(), gwu, n, d, f);
+    matmul_a_bt(d_gate.data(), wg, dx, n, f, d);
+    matmul_a_bt(d_up.data(), wu, dx_tmp, n, f, d);
+}
+
+}  // namespace
+
+extern "C" {
+
+// backward.rs:269-287
+void oracle_moe_router_unbiased_backward(const float* d_expert_weights, const float* gating_weights,
+                                         const size_t* selected_indices, size_t top_k, float* d_router_logits,
+                                         size_t E) {
+    for (size_t e = 0; e < E; ++e) d_router_logits[e] = 0.0f;
+    float weighted_sum = 0.0f;
+    for (size_t k = 0; k < top_k; ++k) weighted_sum += gating_weights[k] * d_expert_weights[k];
+    for (size_t k = 0; k < top_k; ++k) {
+        const float g_i = gating_weights[k];
+        const float dl_dg = d_expert_weights[k];
+        d_router_logits[selected_indices[k]] = g_i * (dl_dg - weighted_sum);
+    }
+}
+
+// MoE part of the backward pass of one block (model.rs:566-766), for a layer input x [T,d] (`normed2` there) and
+// the gradient d_out [T,d] of the layer's output (`d_moe`). The forward stashes (moe.rs:103-111,166-175,186-208)
+// are recomputed here with the same arithmetic as oracle_moe_forward_train.
+//   grads: 1 + 3*(1+E) buffers in the parameter order of `weights`; the gradients are ACCUMULATED into them, as the
+//          reference accumulates into grads.grads[base_idx + 6 ...] (matmul_at_b adds).
+//   d_x [T,d]: overwritten with d_normed2 = shared + routed (experts ascending) + router contributions.
+// The router-bias update that the reference performs at this point (model.rs:768-775) is oracle_update_aux_free_bias.
+int oracle_moe_backward(const float* const* weights, const float* router_bias, size_t d, size_t f, size_t E,
+                        size_t top_k, const float* x, size_t T, const float* concept_bias, size_t n_concept,
+                        const float* d_out, float* const* grads, float* d_x) {
+    if (top_k > E) return -1;
+    const float* router = weights[0];
+    std::vector<size_t> selected(T * top_k), counts(E);
+    std::vector<float> gating(T * top_k);
+    oracle_route(x, router, router_bias, concept_bias, n_concept, T, d, E, top_k, nullptr, nullptr, selected.data(),
+                 gating.data(), counts.data());
+
+    std::vector<float> d_normed2(T * d, 0.0f);
+
+    // 1. shared expert (model.rs:571-635)
+    {
+        std::vector<float> gate(T * f), up(T * f), act(T * f), dx(T * d), dx_tmp(T * d);
+        matmul_2d(x, weights[1], gate.data(), T, d, f);
+        matmul_2d(x, weights[2], up.data(), T, d, f);
+        swiglu(gate.data(), up.data(), act.data(), T * f);
+        expert_backward(x, gate.data(), up.data(), act.data(), d_out, weights[1], weights[2], weights[3], grads[1],
+                        grads[2], grads[3], dx.data(), dx_tmp.data(), T, d, f);
+        for (size_t i = 0; i < T * d; ++i) d_normed2[i] += dx[i] + dx_tmp[i];
+    }
+
+    // 2. routed experts, ascending, empty ones skipped (model.rs:637-733)
+    std::vector<float> token_expert_scalars(T * E, 0.0f);
+    for (size_t e = 0; e < E; ++e) {
+        std::vector<size_t> tok_idx;
+        std::vector<float> w;
+        for (size_t t = 0; t < T; ++t)
+            for (size_t j = 0; j < top_k; ++j)
+                if (selected[t * top_k + j] == e) {
+                    tok_idx.push_back(t);
+                    w.push_back(gating[t * top_k + j]);
+                }
+        const size_t n = tok_idx.size();
+        if (n == 0) continue;
+        const float *wg = weights[4 + 3 * e], *wu = weights[5 + 3 * e], *wd = weights[6 + 3 * e];
+        std::vector<float> xe(n * d), gate(n * f), up(n * f), act(n * f), ye(n * d);
+        for (size_t i = 0; i < n; ++i) std::memcpy(&xe[i * d], x + tok_idx[i] * d, d * sizeof(float));
+        matmul_2d(xe.data(), wg, gate.data(), n, d, f);
+        matmul_2d(xe.data(), wu, up.data(), n, d, f);
+        swiglu(gate.data(), up.data(), act.data(), n * f);
+        matmul_2d(act.data(), wd, ye.data(), n, f, d);
+
+        // dY_e = gate weight * d_out[token]; scalar = <expert output row, d_out[token]> (model.rs:647-659)
+        std::vector<float> d_y_e(n * d);
+        for (size_t i = 0; i < n; ++i) {
+            const float* d_moe_row = d_out + tok_idx[i] * d;
+            const float* exp_out_row = &ye[i * d];
+            float dot = 0.0f;
+            for (size_t c = 0; c < d; ++c) {
+                d_y_e[i * d + c] = w[i] * d_moe_row[c];
+                dot += exp_out_row[c] * d_moe_row[c];
+            }
+            token_expert_scalars[tok_idx[i] * E + e] = dot;
+        }
+        std::vector<float> dx(n * d), dx_tmp(n * d);
+        expert_backward(xe.data(), gate.data(), up.data(), act.data(), d_y_e.data(), wg, wu, wd, grads[4 + 3 * e],
+                        grads[5 + 3 * e], grads[6 + 3 * e], dx.data(), dx_tmp.data(), n, d, f);
+        // scatter-add into d_normed2 (model.rs:724-732). dY_e above already carries the gate weight, so the
+        // reference's input gradient of a routed expert ends up scaled by w twice (w^2 J^T d_out instead of the
+        // gradient w J^T d_out); restated as the reference computes it. The weight gradients are not affected.
+        for (size_t i = 0; i < n; ++i) {
+            float* out_row = &d_normed2[tok_idx[i] * d];
+            for (size_t c = 0; c < d; ++c) out_row[c] += w[i] * (dx[i * d + c] + dx_tmp[i * d + c]);
+        }
+    }
+
+    // 3. router VJP (model.rs:735-766)
+    std::vector<float> d_router_logits(T * E, 0.0f);
+    for (size_t t = 0; t < T; ++t) {
+        std::vector<float> d_expert_weights(top_k);
+        for (size_t j = 0; j < top_k; ++j) d_expert_weights[j] = token_expert_scalars[t * E + selected[t * top_k + j]];
+        oracle_moe_router_unbiased_backward(d_expert_weights.data(), &gating[t * top_k], &selected[t * top_k], top_k,
+                                            &d_router_logits[t * E], E);
+    }
+    matmul_at_b(x, d_router_logits.data(), grads[0], T, d, E);
+    std::vector<float> d_normed2_router(T * d);
+    matmul_a_bt(d_router_logits.data(), router, d_normed2_router.data(), T, E, d);
+    for (size_t i = 0; i < T * d; ++i) d_normed2[i] += d_normed2_router[i];
+
+    std::memcpy(d_x, d_normed2.data(), T * d * sizeof(float));
+    return 0;
 }
 
 }  // extern "C"

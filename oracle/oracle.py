@@ -9,6 +9,8 @@ The functions mirror the reference one to one:
   matmul_2d, swiglu, top_k_gating_unbiased, add_tensors      crates/prichs-core/src/ops.rs:8-61,142-159,219-248,250-267
   rms_norm                                                    crates/prichs-core/src/ops.rs:109-135
   moe_forward_train, update_aux_free_bias                     crates/prichs-model/src/moe.rs:93-211,228-245
+  moe_backward, moe_router_unbiased_backward                  crates/prichs-model/src/model.rs:566-766,
+                                                              crates/prichs-core/src/backward.rs:247-287
 """
 from __future__ import annotations
 
@@ -49,6 +51,9 @@ def lib():
         L.oracle_moe_forward_train.restype = C.c_int
         L.oracle_update_aux_free_bias.argtypes = [fp, sz, sz, zp, sz, C.c_float]
         L.oracle_rms_norm.argtypes = [fp, fp, C.c_float, fp, sz, sz]
+        L.oracle_moe_router_unbiased_backward.argtypes = [fp, fp, zp, sz, fp, sz]
+        L.oracle_moe_backward.argtypes = [C.POINTER(fp), fp, sz, sz, sz, sz, fp, sz, fp, sz, fp, C.POINTER(fp), fp]
+        L.oracle_moe_backward.restype = C.c_int
         _lib = L
     return _lib
 
@@ -205,3 +210,45 @@ def update_aux_free_bias(router_bias, expert_token_counts, total_tokens, gamma, 
                                       c.ctypes.data_as(C.POINTER(C.c_size_t)), int(total_tokens),
                                       C.c_float(gamma))
     return b
+
+
+def moe_router_unbiased_backward(d_expert_weights, gating_weights, selected_indices, num_experts):
+    """backward.rs:269-287: d logits [E] of one token from the k scalars <expert_i(x), d_out>."""
+    dw, pdw = _f(d_expert_weights)
+    gw, pgw = _f(gating_weights)
+    idx = np.ascontiguousarray(selected_indices, dtype=np.uintp)
+    out = np.empty(num_experts, np.float32)
+    lib().oracle_moe_router_unbiased_backward(pdw, pgw, idx.ctypes.data_as(C.POINTER(C.c_size_t)), idx.size,
+                                              out.ctypes.data_as(C.POINTER(C.c_float)), num_experts)
+    return out
+
+
+def moe_backward(weights, router_bias, top_k, x, d_out, concept_bias=None, grads=None):
+    """MoE part of the block's backward pass (model.rs:566-766). Returns dict(d_x [T,d], grads = list of arrays in
+    the order and shapes of `weights`). Gradients are accumulated into `grads` when given (the reference adds into
+    its gradient buffers), else into zeros."""
+    ws = [np.ascontiguousarray(w, dtype=np.float32) for w in weights]
+    d, E = ws[0].shape
+    f = ws[1].shape[1]
+    assert len(ws) == 1 + 3 * (1 + E)
+    fp = C.POINTER(C.c_float)
+    arr = (fp * len(ws))(*[w.ctypes.data_as(fp) for w in ws])
+    gs = [np.zeros_like(w) for w in ws] if grads is None else [np.ascontiguousarray(g, dtype=np.float32) for g in grads]
+    assert all(g.shape == w.shape for g, w in zip(gs, ws))
+    garr = (fp * len(gs))(*[g.ctypes.data_as(fp) for g in gs])
+    bias, pbias = _f(router_bias)
+    x, px = _f(x)
+    dy, pdy = _f(d_out)
+    T = x.shape[0]
+    assert x.shape == (T, d) and dy.shape == (T, d)
+    if concept_bias is not None:
+        cb, pcb = _f(concept_bias)
+        ncb = cb.size
+    else:
+        pcb, ncb = _fnull(), 0
+    dx = np.empty((T, d), np.float32)
+    rc = lib().oracle_moe_backward(arr, pbias, d, f, E, top_k, px, T, pcb, ncb, pdy, garr, dx.ctypes.data_as(fp))
+    if rc != 0:
+        raise ValueError("k must be <= logits length")
+    return dict(d_x=dx, grads=gs)
+

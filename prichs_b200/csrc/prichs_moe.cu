@@ -287,6 +287,10 @@ struct prichs_moe {
     float *w_r8, *bias;
     bf16 *xs, *xp, *hbuf;
     void* xnorm;  // normalised activations of the block entry point: bf16 [Tmax,d] (fp32 in the fp32-fidelity mode)
+    const float* norm_w;  // set while the block entry point runs with the pre-norm folded into the router's read
+    float norm_eps;
+    bool fuse_norm;
+    bool fuse_scan;  // single-GPU forward: scan + plan run at the tail of the router launch
     void* ybuf;
     float *logits, *gates;
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
@@ -364,7 +368,7 @@ int translate_status(int s) {
 // ---- launch helpers shared by the single-GPU and the expert-parallel forward ---------------------------
 // Router over T tokens starting at `x_dev`; routing arrays are the caller's (already offset) pointers.
 int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::ConceptBias& cb, int T, float* logits, int* sel,
-                  float* gates, int* tile_counts, cudaStream_t st, bool pdl = false) {
+                  float* gates, int* tile_counts, cudaStream_t st, bool pdl = false, const route::ScanTail& tail = route::ScanTail{}) {
     const int d = h->d, E = h->E;
     const int ntiles_all = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     // PRICHS_ROUTER_CTAS_PER_SM caps the router grid (the kernel strides over tiles); 0 = one CTA per tile
@@ -375,17 +379,21 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
                                                         logits, sel, gates, tile_counts);
     } else {
         constexpr int RT = route::ROUTER_WARPS * 32;
-        if (x_dtype == PRICHS_DTYPE_F32) {
-            if (h->rt_nsplit == 1)
-                LAUNCH_K(pdl, (route::router_mma_kernel<1, true>), ntiles, RT, 0, st, (const void*)x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
-            else
-                LAUNCH_K(pdl, (route::router_mma_kernel<3, true>), ntiles, RT, 0, st, (const void*)x_dev, h->xs, h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
-        } else {
-            if (h->rt_nsplit == 1)
-                LAUNCH_K(pdl, (route::router_mma_kernel<1, false>), ntiles, RT, 0, st, (const void*)x_dev, (bf16*)nullptr, (const bf16*)h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
-            else
-                LAUNCH_K(pdl, (route::router_mma_kernel<3, false>), ntiles, RT, 0, st, (const void*)x_dev, (bf16*)nullptr, (const bf16*)h->w_rt, h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
-        }
+        const bool xf32 = x_dtype == PRICHS_DTYPE_F32, norm = h->norm_w != nullptr;
+        bf16* xs = (xf32 || norm) ? h->xs : nullptr;  // bf16 (and normalised) copy of the rows for the expert GEMMs
+#define PRICHS_ROUTER_CASE(NS, XF, NM)                                                                                              \
+    if (h->rt_nsplit == NS && xf32 == XF && norm == NM)                                                                             \
+        LAUNCH_K(pdl, (route::router_mma_kernel<NS, XF, NM>), ntiles, RT, 0, st, (const void*)x_dev, xs, (const bf16*)h->w_rt,      \
+                 (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->norm_w, h->norm_eps, tail);
+        PRICHS_ROUTER_CASE(1, false, false)
+        PRICHS_ROUTER_CASE(1, true, false)
+        PRICHS_ROUTER_CASE(3, false, false)
+        PRICHS_ROUTER_CASE(3, true, false)
+        PRICHS_ROUTER_CASE(1, false, true)
+        PRICHS_ROUTER_CASE(1, true, true)
+        PRICHS_ROUTER_CASE(3, false, true)
+        PRICHS_ROUTER_CASE(3, true, true)
+#undef PRICHS_ROUTER_CASE
     }
     LAUNCH_CHECK("router");
     return PRICHS_OK;
@@ -530,7 +538,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
                int y_dtype, int T, cudaStream_t st) {
     const int E = h->E, W = h->n_waves;
     const bool f32mode = h->mode == PRICHS_MODE_F32;
-    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 || h->norm_w ? h->xs : reinterpret_cast<const bf16*>(x_dev);
     CUtensorMap tm_x;
     int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
     if (rc != PRICHS_OK) return rc;
@@ -668,6 +676,13 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     h->K1 = d * mul; h->K2 = f * mul;
     h->Tcap = round_up(h->Tmax, SEG_PAD);
     h->resid_dtype = -1;
+    {
+        // PRICHS_FUSED_NORM=0 keeps the block entry point's pre-norm as a launch of its own (for comparison)
+        const char* fn = getenv("PRICHS_FUSED_NORM");
+        h->fuse_norm = !(fn && atoi(fn) == 0);
+        const char* fs = getenv("PRICHS_FUSED_SCAN");
+        h->fuse_scan = !(fs && atoi(fs) == 0);
+    }
     h->n_waves = 1;
     if (world > 1) {
         const int want = cfg->ep_waves > 0 ? cfg->ep_waves : h->Tmax / 8192;
@@ -721,7 +736,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->tile_counts, ntiles * route::MAX_E));
     A(dalloc(&h->tile_prefix, ntiles * route::MAX_E));
     A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
-    A(dalloc(&h->status, 1));
+    A(dalloc(&h->status, 2));  // [0] status word, [1] finished-CTA counter of the router's scan tail
     A(dalloc(&h->meta, 1));
     A(dalloc(&h->ep_zero, 8));
     for (int w = 0; w < h->n_waves && world > 1; ++w) {
@@ -734,7 +749,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         return rc;
     }
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
-    cudaMemset(h->status, 0, sizeof(int));
+    cudaMemset(h->status, 0, 2 * sizeof(int));
     cudaMemset(h->pos, 0, (size_t)h->Tmax * 2 * sizeof(int));  // stale row maps always stay inside the buffers
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
     cudaMemset(h->ep_zero, 0, 8 * sizeof(int));
@@ -946,7 +961,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     if (h->world > 1) return forward_ep(h, x_dev, x_dtype, resid_dev, cb, y_dev, y_dtype, T, st);
 
     const bool f32mode = h->mode == PRICHS_MODE_F32;
-    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    const bf16* a_shared = f32mode || x_dtype == PRICHS_DTYPE_F32 || h->norm_w ? h->xs : reinterpret_cast<const bf16*>(x_dev);
     CUtensorMap tm_x;
     int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
     if (rc != PRICHS_OK) return rc;
@@ -960,13 +975,28 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     mark();
     // 1. router
     const bool pdl = h->pdl;
-    rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st, pdl);
+    // 2. prefix sums + placement plan: by the last CTA of the router launch, or as a launch of their own
+    //    (fp32-fidelity router, or PRICHS_FUSED_SCAN=0)
+    const bool scan_in_router = h->fuse_scan && !f32mode;
+    route::ScanTail tail{};
+    if (scan_in_router) {
+        tail.done = h->status + 1;
+        tail.tile_prefix = h->tile_prefix;
+        tail.meta = h->meta;
+        tail.mtile_slot = h->mtile_slot;
+        tail.El = h->El;
+        tail.cap_rows = h->Rcap;
+        tail.pad_rows = SEG_PAD;
+        tail.status = h->status;
+    }
+    rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st, pdl, tail);
     if (rc != PRICHS_OK) return rc;
     mark();
-    // 2. prefix sums + placement plan
-    LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0,
-             h->Rcap, 1, SEG_PAD, h->status);
-    LAUNCH_CHECK("scan");
+    if (!scan_in_router) {
+        LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0,
+                 h->Rcap, 1, SEG_PAD, h->status);
+        LAUNCH_CHECK("scan");
+    }
     mark();
     // 3. dispatch
     route::PeerPtrs xp_peers, y_peers;
@@ -1007,7 +1037,10 @@ int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype
         return fail(PRICHS_ERR_BAD_ARG, "activation and weight pointers must be 16-byte aligned");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     const bool of32 = h->mode == PRICHS_MODE_F32;
-    if (T > 0) {
+    // bf16 mode, whole row in one router pass: the norm is folded into the router kernel's read of the rows, which
+    // then also writes the normalised bf16 rows the dispatch and the shared expert consume
+    const bool fused = h->fuse_norm && !of32 && h->d <= route::ROUTER_KB * route::ROUTER_WARPS * 32 && h->d % 256 == 0;
+    if (T > 0 && !fused) {
         DeviceGuard guard(h->device);
         const int grid = (T + 7) / 8;
         if (x_dtype == PRICHS_DTYPE_F32) {
@@ -1020,8 +1053,16 @@ int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype
     }
     // the normalised rows are the layer's input, the un-normalised ones its fused residual (block.rs:64-67)
     h->resid_dtype = x_dtype;  // the residual keeps the caller's element type even when the normalised input is bf16
-    const int rc = prichs_moe_forward(h, h->xnorm, of32 ? PRICHS_DTYPE_F32 : PRICHS_DTYPE_BF16, x_res_dev, concept_bias, n_concept,
-                                      y_dev, y_dtype, T, stream_);
+    int rc;
+    if (fused) {
+        h->norm_w = norm_weight_dev;
+        h->norm_eps = eps;
+        rc = prichs_moe_forward(h, x_res_dev, x_dtype, x_res_dev, concept_bias, n_concept, y_dev, y_dtype, T, stream_);
+        h->norm_w = nullptr;
+    } else {
+        rc = prichs_moe_forward(h, h->xnorm, of32 ? PRICHS_DTYPE_F32 : PRICHS_DTYPE_BF16, x_res_dev, concept_bias, n_concept, y_dev,
+                                y_dtype, T, stream_);
+    }
     h->resid_dtype = -1;
     return rc;
 }
@@ -1438,8 +1479,8 @@ extern "C" int prichs_moe_route_static(const void* x_dev, const float* router_de
     route::ConceptBias cb;
     for (int e = 0; e < route::MAX_E; ++e) cb.v[e] = 0.0f;
     const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
-    route::router_mma_kernel<3, false><<<ntiles, route::ROUTER_WARPS * 32, 0, st>>>(x_dev, nullptr, wrt, bias0, cb, T, d, E, top_k, logits8, sel2,
-                                                                        gates2, tcount);
+    route::router_mma_kernel<3, false, false><<<ntiles, route::ROUTER_WARPS * 32, 0, st>>>(x_dev, nullptr, wrt, bias0, cb, T, d, E, top_k, logits8,
+                                                                                         sel2, gates2, tcount, nullptr, 0.0f, route::ScanTail{});
     LAUNCH_CHECK("router");
     const int cap_rows = (int)((RS_MAX_T * 2 + route::MAX_E * 128) / 128 * 128);
     route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, E, E, 1, 0, cap_rows, 1, 128, status);

@@ -137,23 +137,49 @@ __device__ __forceinline__ void route_finish(const float (&L)[MAX_E], bool activ
 // 2^-24), NSPLIT = 1 is used when the weights are bf16 values already.
 // XF32: x is fp32 [T,d]; it is rounded to bf16 (RNE) for the product and the bf16 copy is written to `xs`
 // for the expert GEMMs (saves a separate conversion pass).
+// NORM: the rows are RMS-normalised (weight norm_w, epsilon norm_eps) before they are rounded to bf16; `xs`
+// receives the normalised rows. The un-normalised rows stay the caller's residual.
 constexpr int ROUTER_WARPS = 8;
+constexpr int ROUTER_KB = 6;
 
-template <int NSPLIT, bool XF32>
+template <int NT, int SCAN_KEEP>
+__device__ __forceinline__ const int* scan_tiles(const int* tile_counts, int* __restrict__ tile_prefix, int ntiles,
+                                                 RouteMeta* meta, int rank);
+__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world,
+                                               int rank, int cap_rows, int pad_rows, int* __restrict__ status,
+                                               const int* local_counts);
+
+// Work the last CTA of the router launch does when all experts are local: the prefix sums over the tile
+// histograms and the placement plan, which would otherwise be a one-CTA launch of their own between the router
+// and the dispatch. `done` counts finished CTAs (zero before the launch, reset by the last CTA); null = no tail.
+struct ScanTail {
+    int* done;
+    int* tile_prefix;
+    RouteMeta* meta;
+    int* mtile_slot;
+    int El, cap_rows, pad_rows;
+    int* status;
+};
+
+template <int NSPLIT, bool XF32, bool NORM>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ wrt,
                   const float* __restrict__ bias, const ConceptBias cb, int T, int d, int E, int top_k,
                   float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ gates,
-                  int* __restrict__ tile_counts) {
-    __shared__ float4 partial[ROUTER_WARPS][32];
+                  int* tile_counts, const float* __restrict__ norm_w, float norm_eps, const ScanTail tail) {
+    __shared__ float4 partial[2][ROUTER_WARPS][32];
+    __shared__ float ssq[NORM ? TILE_TOKENS : 1][32], inv_rms_s[TILE_TOKENS];
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
-    // grid-stride over tiles: with fewer CTAs than tiles the CTAs of an SM drift out of phase, so the loads of
-    // one overlap the reduction and selection of another
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    constexpr int KSTEP = ROUTER_WARPS * 32;  // elements of a row the CTA covers per slice
+    constexpr int XV = XF32 ? 4 : 2;          // 16-byte vectors a lane reads per slice (rows g and g + 8)
+    // grid-stride over tiles; `partial` is double buffered, so a tile costs one barrier and warps 1..7 start the
+    // loads of the next tile while warp 0 still selects for this one
+    int buf = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, buf ^= 1) {
     const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
     const size_t r0c = (size_t)min(r0, T - 1), r1c = (size_t)min(r1, T - 1);
 
@@ -168,32 +194,131 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
     const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
     const size_t wsplit = (size_t)MAX_E * d;
 
-#pragma unroll 6
-    for (int kk = warp * 32; kk < d; kk += ROUTER_WARPS * 32) {
-        uint4 a0, a1;
-        if (XF32) {
-            const float* x0 = reinterpret_cast<const float*>(x) + r0c * d + kk + 8 * q;
-            const float* x1 = reinterpret_cast<const float*>(x) + r1c * d + kk + 8 * q;
-            const uint4 p0 = ptx::ld_stream_16(x0), p1 = ptx::ld_stream_16(x0 + 4);
-            const uint4 p2 = ptx::ld_stream_16(x1), p3 = ptx::ld_stream_16(x1 + 4);
-            auto pk = [](uint32_t lo, uint32_t hi) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
-                return *reinterpret_cast<uint32_t*>(&v);
-            };
-            a0 = make_uint4(pk(p0.x, p0.y), pk(p0.z, p0.w), pk(p1.x, p1.y), pk(p1.z, p1.w));
-            a1 = make_uint4(pk(p2.x, p2.y), pk(p2.z, p2.w), pk(p3.x, p3.y), pk(p3.z, p3.w));
-            if (r0 < T) *reinterpret_cast<uint4*>(xs + (size_t)r0 * d + kk + 8 * q) = a0;
-            if (r1 < T) *reinterpret_cast<uint4*>(xs + (size_t)r1 * d + kk + 8 * q) = a1;
-        } else {
-            const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-            a0 = ptx::ld_stream_16(xb + r0c * d + kk + 8 * q);
-            a1 = ptx::ld_stream_16(xb + r1c * d + kk + 8 * q);
+    // A pass covers ROUTER_KB slices (the whole row for d <= 1536). All of its loads are issued before the first
+    // MMA, so a warp has up to ROUTER_KB * XV 16-byte requests in flight instead of one slice's worth: with
+    // ~3 KB per token and no reuse, memory-level parallelism is what sets the speed of this kernel.
+    for (int kb = warp * 32; kb < d; kb += ROUTER_KB * KSTEP) {
+        uint4 xv[ROUTER_KB][XV], wv[ROUTER_KB][NSPLIT];
+#pragma unroll
+        for (int i = 0; i < ROUTER_KB; ++i) {
+            const int kk = kb + i * KSTEP;
+            if (kk < d) {
+                if constexpr (XF32) {
+                    const float* x0 = reinterpret_cast<const float*>(x) + r0c * d + kk + 8 * q;
+                    const float* x1 = reinterpret_cast<const float*>(x) + r1c * d + kk + 8 * q;
+                    xv[i][0] = ptx::ld_stream_16(x0);
+                    xv[i][1] = ptx::ld_stream_16(x0 + 4);
+                    xv[i][2] = ptx::ld_stream_16(x1);
+                    xv[i][3] = ptx::ld_stream_16(x1 + 4);
+                } else {
+                    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+                    xv[i][0] = ptx::ld_stream_16(xb + r0c * d + kk + 8 * q);
+                    xv[i][1] = ptx::ld_stream_16(xb + r1c * d + kk + 8 * q);
+                }
+#pragma unroll
+                for (int s = 0; s < NSPLIT; ++s) wv[i][s] = __ldg(reinterpret_cast<const uint4*>(wl + s * wsplit + kk));
+            }
+        }
+        // the 8 consecutive elements of row half `hf` (0: row g, 1: row g + 8) in slice i, widened to fp32
+        auto unpack8 = [&](int i, int hf, float (&v)[8]) {
+            if constexpr (XF32) {
+                const uint4 a = xv[i][(2 * hf) % XV], b = xv[i][(2 * hf + 1) % XV];
+                v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+                v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+            } else {
+                const uint4 a = xv[i][hf];
+                const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[2 * j] = __uint_as_float(w[j] << 16);
+                    v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                }
+            }
+        };
+        auto pack8 = [](const float (&v)[8]) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            return make_uint4(w[0], w[1], w[2], w[3]);
+        };
+        // Pre-norm folded into the read (rms_norm of crates/prichs-core/src/ops.rs:109-135 ahead of the layer,
+        // crates/prichs-model/src/block.rs:64). Thread (warp, q) holds for its two rows exactly the elements lane
+        // 4 * warp + q of rmsnorm_rows_kernel holds, and sums their squares in the same order; the 32 partial sums
+        // of a row then go through the same butterfly, so inv_rms and the normalised bf16 rows are bit-identical to
+        // the stand-alone kernel's. Needs the whole row in one pass (d <= ROUTER_KB * 256).
+        float inv0 = 1.f, inv1 = 1.f;
+        if constexpr (NORM) {
+            float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < ROUTER_KB; ++i) {
+                if (kb + i * KSTEP < d) {
+                    float v0[8], v1[8];
+                    unpack8(i, 0, v0);
+                    unpack8(i, 1, v1);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        ss0 = fmaf(v0[j], v0[j], ss0);
+                        ss1 = fmaf(v1[j], v1[j], ss1);
+                    }
+                }
+            }
+            ssq[g][4 * warp + q] = ss0;
+            ssq[g + 8][4 * warp + q] = ss1;
+            __syncthreads();
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                float sv = ssq[2 * warp + rr][lane];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sv += __shfl_xor_sync(0xffffffffu, sv, o);
+                if (lane == 0) inv_rms_s[2 * warp + rr] = 1.0f / sqrtf(sv / (float)d + norm_eps);
+            }
+            __syncthreads();
+            inv0 = inv_rms_s[g];
+            inv1 = inv_rms_s[g + 8];
         }
 #pragma unroll
-        for (int s = 0; s < NSPLIT; ++s) {
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(wl + s * wsplit + kk));
-            ptx::mma_m16n8k16_bf16(acc[s][0], a0.x, a1.x, a0.y, a1.y, w.x, w.y);
-            ptx::mma_m16n8k16_bf16(acc[s][1], a0.z, a1.z, a0.w, a1.w, w.z, w.w);
+        for (int i = 0; i < ROUTER_KB; ++i) {
+            const int kk = kb + i * KSTEP;
+            if (kk < d) {
+                uint4 a0, a1;
+                if constexpr (NORM) {
+                    const float4 n0 = __ldg(reinterpret_cast<const float4*>(norm_w + kk + 8 * q));
+                    const float4 n1 = __ldg(reinterpret_cast<const float4*>(norm_w + kk + 8 * q + 4));
+                    const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+                    float v0[8], v1[8];
+                    unpack8(i, 0, v0);
+                    unpack8(i, 1, v1);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v0[j] = __fmul_rn(__fmul_rn(v0[j], inv0), nw[j]);
+                        v1[j] = __fmul_rn(__fmul_rn(v1[j], inv1), nw[j]);
+                    }
+                    a0 = pack8(v0);
+                    a1 = pack8(v1);
+                } else if constexpr (XF32) {
+                    float v0[8], v1[8];
+                    unpack8(i, 0, v0);
+                    unpack8(i, 1, v1);
+                    a0 = pack8(v0);
+                    a1 = pack8(v1);
+                } else {
+                    a0 = xv[i][0];
+                    a1 = xv[i][1];
+                }
+                if constexpr (NORM || XF32) {
+                    if (r0 < T) *reinterpret_cast<uint4*>(xs + (size_t)r0 * d + kk + 8 * q) = a0;
+                    if (r1 < T) *reinterpret_cast<uint4*>(xs + (size_t)r1 * d + kk + 8 * q) = a1;
+                }
+#pragma unroll
+                for (int s = 0; s < NSPLIT; ++s) {
+                    const uint4 w = wv[i][s];
+                    ptx::mma_m16n8k16_bf16(acc[s][0], a0.x, a1.x, a0.y, a1.y, w.x, w.y);
+                    ptx::mma_m16n8k16_bf16(acc[s][1], a0.z, a1.z, a0.w, a1.w, w.z, w.w);
+                }
+            }
         }
     }
     // c[0..1]: row g, experts 2q, 2q+1; c[2..3]: row g+8. Small parts are summed first.
@@ -205,12 +330,12 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
         for (int s = NSPLIT - 1; s >= 0; --s) v += acc[s][0][i] + acc[s][1][i];
         c[i] = v;
     }
-    partial[warp][lane] = make_float4(c[0], c[1], c[2], c[3]);
+    partial[buf][warp][lane] = make_float4(c[0], c[1], c[2], c[3]);
     __syncthreads();
     if (warp == 0) {
 #pragma unroll
     for (int w = 1; w < ROUTER_WARPS; ++w) {
-        const float4 p = partial[w][lane];
+        const float4 p = partial[buf][w][lane];
         c[0] += p.x; c[1] += p.y; c[2] += p.z; c[3] += p.w;
     }
     // lanes q = 0 / q = 1 of each quad take row g / g + 8; gather the row's 8 logits from the quad
@@ -232,7 +357,21 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
     const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
     route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
     }
-    __syncthreads();  // `partial` is reused by the next tile
+    }
+    if (tail.done != nullptr) {
+        // last-CTA-done: every CTA publishes its histograms (fence) and takes a ticket; the CTA that draws the last
+        // ticket sees all of them and finishes the routing metadata
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(tail.done, 1) == (int)gridDim.x - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int* totals = scan_tiles<ROUTER_WARPS * 32, 8>(tile_counts, tail.tile_prefix, ntiles, tail.meta, 0);
+            plan_from_cmat(tail.meta, tail.mtile_slot, E, tail.El, 1, 0, tail.cap_rows, tail.pad_rows, tail.status, totals);
+            if (threadIdx.x == 0) *tail.done = 0;
+        }
     }
 }
 
@@ -306,17 +445,24 @@ router_f32_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, c
 //   total[e] = sum_s cmat[s][e],  src_off[e] = sum_{s < rank} cmat[s][e],
 //   seg_base[e] = sum of the padded totals (to pad_rows, a multiple of 128) of the owner's lower experts.
 // For the local experts it also fills the m-tile -> weight-slot table the grouped GEMM walks.
+// `local_counts` (single rank only): the totals in shared memory, straight from the scan, so that this plan
+// reads nothing back from global memory; null = take them from meta->cmat.
 __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El,
-                                               int world, int rank, int cap_rows, int pad_rows, int* __restrict__ status) {
-    __shared__ int s_total[MAX_E], s_base[MAX_E + 1];
+                                               int world, int rank, int cap_rows, int pad_rows, int* __restrict__ status,
+                                               const int* local_counts) {
+    __shared__ int s_total[MAX_E], s_base[MAX_E + 1], s_over;
     const int tid = threadIdx.x;
     if (tid < MAX_E) {
         int tot = 0, off = 0;
         if (tid < E) {
-            for (int s = 0; s < world; ++s) {
-                const int c = meta->cmat[s * MAX_E + tid];
-                tot += c;
-                if (s < rank) off += c;
+            if (local_counts != nullptr) {
+                tot = local_counts[tid];
+            } else {
+                for (int s = 0; s < world; ++s) {
+                    const int c = meta->cmat[s * MAX_E + tid];
+                    tot += c;
+                    if (s < rank) off += c;
+                }
             }
         }
         s_total[tid] = tot;
@@ -344,13 +490,14 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
                 local_rows = base;
             }
         }
+        s_over = over;
         meta->overflow = over;
         meta->recv_rows = recv;
         meta->n_routed_mtiles = over ? 0 : local_rows / 128;
         if (over) atomicExch(status, -2);
     }
     __syncthreads();
-    const int ntiles = meta->overflow ? 0 : s_base[El] / 128;
+    const int ntiles = s_over ? 0 : s_base[El] / 128;
     for (int i = tid; i < ntiles; i += blockDim.x) {
         int le = 0;
         while (le + 1 < El && i * 128 >= s_base[le + 1]) ++le;
@@ -360,27 +507,44 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
     }
 }
 
-// Exclusive prefix sum of the per-tile histograms over tiles (one CTA of 1024 threads; each thread owns a
-// contiguous run of tiles), totals into meta->counts and row `rank` of meta->cmat. With `fuse_plan` (single
-// rank) the placement plan follows in the same launch.
-__global__ void __launch_bounds__(1024)
-scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, int ntiles, RouteMeta* meta,
-            int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
-            int pad_rows, int* __restrict__ status) {
-    __shared__ int warp_tot[32][MAX_E];
-    ptx::grid_dep_launch();
-    ptx::grid_dep_wait();
+// Exclusive prefix sum of the per-tile histograms over tiles by one CTA of NT threads (each thread owns a
+// contiguous run of tiles), totals into meta->counts and row `rank` of meta->cmat; returns the totals in shared
+// memory (valid for all threads after the next barrier; this function ends with one). The histograms are read
+// with ld.global.cg: when this runs at the tail of the router kernel they were written by other CTAs of the same
+// launch. A run of up to SCAN_KEEP tiles stays in registers between the two passes, so the CTA makes one trip to
+// memory, not two.
+template <int NT, int SCAN_KEEP>
+__device__ __forceinline__ const int* scan_tiles(const int* tile_counts, int* __restrict__ tile_prefix, int ntiles,
+                                                 RouteMeta* meta, int rank) {
+    constexpr int NW = NT / 32;
+    __shared__ int warp_tot[NW][MAX_E];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int per = (ntiles + 1023) / 1024;
+    const int per = (ntiles + NT - 1) / NT;
     const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
+    const bool keep = per <= SCAN_KEEP;
+    int4 ka[SCAN_KEEP], kb[SCAN_KEEP];
     int tot[MAX_E];
 #pragma unroll
     for (int e = 0; e < MAX_E; ++e) tot[e] = 0;
-    for (int t = t0; t < t1; ++t) {
-        const int4 a = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E);
-        const int4 b = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4);
-        tot[0] += a.x; tot[1] += a.y; tot[2] += a.z; tot[3] += a.w;
-        tot[4] += b.x; tot[5] += b.y; tot[6] += b.z; tot[7] += b.w;
+    auto add = [&](const int4& a, const int4& b, int (&v)[MAX_E]) {
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < SCAN_KEEP; ++j) {
+            ka[j] = kb[j] = make_int4(0, 0, 0, 0);
+            if (t0 + j < t1) {
+                ka[j] = __ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)(t0 + j) * MAX_E));
+                kb[j] = __ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)(t0 + j) * MAX_E + 4));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < SCAN_KEEP; ++j) add(ka[j], kb[j], tot);
+    } else {
+        for (int t = t0; t < t1; ++t)
+            add(__ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E)),
+                __ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4)), tot);
     }
     int inc[MAX_E];
 #pragma unroll
@@ -398,43 +562,64 @@ scan_kernel(const int* __restrict__ tile_counts, int* __restrict__ tile_prefix, 
     if (warp == 0) {
 #pragma unroll
         for (int e = 0; e < MAX_E; ++e) {
-            int v = warp_tot[lane][e];
+            int v = lane < NW ? warp_tot[lane][e] : 0;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int n = __shfl_up_sync(0xffffffffu, v, o);
                 if (lane >= o) v += n;
             }
-            warp_tot[lane][e] = v;  // inclusive over warps
+            if (lane < NW) warp_tot[lane][e] = v;  // inclusive over warps
         }
     }
     __syncthreads();
     int run[MAX_E];
 #pragma unroll
     for (int e = 0; e < MAX_E; ++e) run[e] = inc[e] - tot[e] + (warp > 0 ? warp_tot[warp - 1][e] : 0);
-    for (int t = t0; t < t1; ++t) {
-        const int4 a = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E);
-        const int4 b = *reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4);
+    auto put = [&](int t) {
         *reinterpret_cast<int4*>(tile_prefix + (size_t)t * MAX_E) = make_int4(run[0], run[1], run[2], run[3]);
         *reinterpret_cast<int4*>(tile_prefix + (size_t)t * MAX_E + 4) = make_int4(run[4], run[5], run[6], run[7]);
-        run[0] += a.x; run[1] += a.y; run[2] += a.z; run[3] += a.w;
-        run[4] += b.x; run[5] += b.y; run[6] += b.z; run[7] += b.w;
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < SCAN_KEEP; ++j) {
+            if (t0 + j < t1) {
+                put(t0 + j);
+                add(ka[j], kb[j], run);
+            }
+        }
+    } else {
+        for (int t = t0; t < t1; ++t) {
+            put(t);
+            add(__ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E)),
+                __ldcg(reinterpret_cast<const int4*>(tile_counts + (size_t)t * MAX_E + 4)), run);
+        }
     }
     if (tid < MAX_E) {
-        const int c = warp_tot[31][tid];
+        const int c = warp_tot[NW - 1][tid];
         meta->counts[tid] = c;
         meta->cmat[rank * MAX_E + tid] = c;
     }
-    if (fuse_plan) {
-        __syncthreads();
-        plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status);
-    }
+    __syncthreads();
+    return &warp_tot[NW - 1][0];
+}
+
+// The scan as its own launch (one CTA of 1024 threads). With `fuse_plan` (single rank) the placement plan follows
+// in the same launch.
+__global__ void __launch_bounds__(1024)
+scan_kernel(const int* tile_counts, int* __restrict__ tile_prefix, int ntiles, RouteMeta* meta,
+            int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
+            int pad_rows, int* __restrict__ status) {
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
+    const int* totals = scan_tiles<1024, 2>(tile_counts, tile_prefix, ntiles, meta, rank);
+    if (fuse_plan) plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status, world == 1 ? totals : nullptr);
 }
 
 // Placement plan as its own launch (expert-parallel mode, after the counts of all ranks were gathered).
 __global__ void __launch_bounds__(256)
 plan_kernel(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows,
             int pad_rows, int* __restrict__ status) {
-    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status);
+    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -308,6 +308,57 @@ def test_block_sublayer_prenorm_moe_residual(torch_cuda, oracle, mode, x_kind):
     assert_close(y[agree], exp[agree], tol, "block output")
 
 
+@pytest.mark.parametrize("x_kind,d,T", [("bf16", 512, 300), ("f32", 512, 300), ("bf16", 1536, 77), ("f32", 1536, 1030)])
+def test_prenorm_folded_into_router_equals_separate_norm_kernel(torch_cuda, monkeypatch, x_kind, d, T):
+    """In bf16 mode the block entry point folds the RMSNorm into the router kernel's read of the rows. The result
+    (logits, routing, output) must be bit-identical to running the norm as a kernel of its own, which the
+    environment switch PRICHS_FUSED_NORM=0 (read when the handle is created) selects."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    f, E, k, eps = 256, 8, 2, 1e-5
+    ws = synth.layer_weights(71, d, f, E, std=0.03, bf16=True)
+    x_res = synth.normal(72, 0, (T, d), 0.0, 2.0)
+    if x_kind == "bf16":
+        x_res = synth.round_bf16(x_res)
+    w = (1.0 + 0.1 * synth.normal(73, 0, (d,))).astype(np.float32)
+    outs = []
+    for fused in ("1", "0"):
+        monkeypatch.setenv("PRICHS_FUSED_NORM", fused)
+        m = MoELayer.from_weights(ws, k, mode="bf16")
+        m.router_bias = synth.router_bias(71, E, -0.1, 0.1)
+        y = _to_host(m.block_forward(_to_dev(torch, x_res, x_kind), torch.from_numpy(w), eps))
+        m.sync_status()
+        st = m.last_stash()
+        outs.append((y, st.router_logits.copy(), st.selected_experts.copy(), st.gating_weights.copy()))
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("T", [1, 37, 5000])
+def test_scan_at_router_tail_equals_separate_scan_launch(torch_cuda, monkeypatch, T):
+    """With all experts local the last CTA of the router launch computes the prefix sums and the placement plan.
+    PRICHS_FUSED_SCAN=0 (read when the handle is created) keeps them as a launch of their own; counts, row map,
+    placement metadata and output must be identical."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    d, f, E, k = 512, 256, 8, 2
+    ws = synth.layer_weights(81, d, f, E, std=0.03, bf16=True)
+    x = synth.round_bf16(synth.normal(82, 0, (T, d)))
+    outs = []
+    for fused in ("1", "0"):
+        monkeypatch.setenv("PRICHS_FUSED_SCAN", fused)
+        m = MoELayer.from_weights(ws, k, mode="bf16")
+        m.router_bias = synth.router_bias(81, E, -0.1, 0.1)
+        for _ in range(2):  # twice: the finished-CTA counter must be back at zero after a forward
+            y = _to_host(m.forward(_to_dev(torch, x, "bf16")))
+        m.sync_status()
+        st = m.last_stash()
+        outs.append((y, st.expert_token_counts.copy(), m.debug_buffer(4, T * 2 * 4).copy(), m.debug_buffer(5, 4 * 36).copy(),
+                     m.debug_buffer(7, ((T + 15) // 16) * 8 * 4).copy()))
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
+
+
 def test_rmsnorm_reference_fixture_values(torch_cuda, oracle):
     """The reference's RMSNorm fixture (crates/prichs-cuda/src/engine.rs:3032-3064): rows [1,2,3,4] and [2,2,2,2],
     weight 1 -- here tiled to the supported width; checked through the block entry point with zero expert weights,
