@@ -1,7 +1,8 @@
 // libprichs_moe.so -- C ABI (include/prichs_moe.h) over the sm_100a kernels of the PRICHS MoE-layer forward.
 //
 // One handle = the device state of one MoELayer (crates/prichs-model/src/moe.rs:58-64): repacked weights,
-// router bias, workspace for max_tokens, TMA descriptors. With all experts local a forward is six launches on
+// router bias, workspace for max_tokens, TMA descriptors. With all experts local a forward is six launches (five
+// for batches under 1024 tokens, where the scan rides at the tail of the router launch) on
 // the caller's stream:
 //   router -> scan/plan -> dispatch -> grouped gate|up GEMM (+SwiGLU) -> grouped down GEMM -> combine.
 // The expert-parallel forward (forward_ep) runs the same kernels in token waves on several streams and
@@ -290,7 +291,7 @@ struct prichs_moe {
     const float* norm_w;  // set while the block entry point runs with the pre-norm folded into the router's read
     float norm_eps;
     bool fuse_norm;
-    bool fuse_scan;  // single-GPU forward: scan + plan run at the tail of the router launch
+    int fuse_scan;  // single-GPU forward, scan + plan at the tail of the router launch: 1 always, 0 never, -1 for small batches
     void* ybuf;
     float *logits, *gates;
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
@@ -321,6 +322,7 @@ struct prichs_moe {
     // host-buffer path
     float *stage_x, *stage_r, *stage_y;
     int* counts_acc;
+    bool host_ready;  // staging buffers, streams and events of the host-buffer path exist
     cudaStream_t own_stream, in_stream, out_stream;
     cudaEvent_t* chunk_ev;
 
@@ -371,8 +373,11 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
                   float* gates, int* tile_counts, cudaStream_t st, bool pdl = false, const route::ScanTail& tail = route::ScanTail{}) {
     const int d = h->d, E = h->E;
     const int ntiles_all = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
-    // PRICHS_ROUTER_CTAS_PER_SM caps the router grid (the kernel strides over tiles); 0 = one CTA per tile
-    static const int cap_per_sm = [] { const char* e = getenv("PRICHS_ROUTER_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+    // The router kernel strides over tiles, so its grid can be capped. With the scan at its tail every CTA ends on a
+    // fence and a ticket, which is cheap for two persistent CTAs per SM and costly for one short-lived CTA per
+    // tile; without the tail one CTA per tile balances best. PRICHS_ROUTER_CTAS_PER_SM overrides (0 = per tile).
+    static const int cap_env = [] { const char* e = getenv("PRICHS_ROUTER_CTAS_PER_SM"); return e ? atoi(e) : -1; }();
+    const int cap_per_sm = cap_env >= 0 ? cap_env : (tail.done != nullptr ? 2 : 0);
     const int ntiles = cap_per_sm > 0 && h->mode != PRICHS_MODE_F32 ? std::min(ntiles_all, cap_per_sm * h->sm_count) : ntiles_all;
     if (h->mode == PRICHS_MODE_F32) {
         route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
@@ -681,7 +686,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         const char* fn = getenv("PRICHS_FUSED_NORM");
         h->fuse_norm = !(fn && atoi(fn) == 0);
         const char* fs = getenv("PRICHS_FUSED_SCAN");
-        h->fuse_scan = !(fs && atoi(fs) == 0);
+        h->fuse_scan = fs ? (atoi(fs) != 0) : -1;
     }
     h->n_waves = 1;
     if (world > 1) {
@@ -809,19 +814,17 @@ int prichs_moe_destroy(prichs_moe_t* h) {
     if (!h) return PRICHS_OK;
     DeviceGuard guard(h->device);
     cudaDeviceSynchronize();
-    if (h->ep_ready) {
-        for (int r = 0; r < h->world; ++r) {
-            if (r == h->rank) continue;
-            if (h->xp_peer[r]) cudaIpcCloseMemHandle(h->xp_peer[r]);
-            if (h->y_peer[r]) cudaIpcCloseMemHandle(h->y_peer[r]);
-        }
-        if (h->side_stream) cudaStreamDestroy(h->side_stream);
-        if (h->ev_router) cudaEventDestroy(h->ev_router);
-        if (h->ev_shared) cudaEventDestroy(h->ev_shared);
-        if (h->tl_base) cudaEventDestroy(h->tl_base);
-        if (h->tl_side[0]) cudaEventDestroy(h->tl_side[0]);
-        if (h->tl_side[1]) cudaEventDestroy(h->tl_side[1]);
+    // expert-parallel resources: released one by one, so that a set-up that stopped half way leaks nothing
+    for (int r = 0; r < route::MAX_RANKS; ++r) {
+        if (h->xp_peer[r] && h->xp_peer[r] != h->xp) cudaIpcCloseMemHandle(h->xp_peer[r]);
+        if (h->y_peer[r] && h->y_peer[r] != h->ybuf) cudaIpcCloseMemHandle(h->y_peer[r]);
     }
+    if (h->side_stream) cudaStreamDestroy(h->side_stream);
+    if (h->ev_router) cudaEventDestroy(h->ev_router);
+    if (h->ev_shared) cudaEventDestroy(h->ev_shared);
+    if (h->tl_base) cudaEventDestroy(h->tl_base);
+    if (h->tl_side[0]) cudaEventDestroy(h->tl_side[0]);
+    if (h->tl_side[1]) cudaEventDestroy(h->tl_side[1]);
     for (int w = 0; w < MAX_WAVES; ++w) {
         EpWave& wv = h->wave[w];
         if (wv.comm && nccl().ok) nccl().comm_destroy(wv.comm);
@@ -975,9 +978,11 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     mark();
     // 1. router
     const bool pdl = h->pdl;
-    // 2. prefix sums + placement plan: by the last CTA of the router launch, or as a launch of their own
-    //    (fp32-fidelity router, or PRICHS_FUSED_SCAN=0)
-    const bool scan_in_router = h->fuse_scan && !f32mode;
+    // 2. prefix sums + placement plan: by the last CTA of the router launch for small batches (decode), where a
+    //    launch costs more than the work; as a launch of their own for large ones, where the tail would keep the
+    //    whole router grid waiting on one CTA's latency chain for no gain (measured on B200: 2 us of 500 at
+    //    T = 16384) and the fp32-fidelity router. PRICHS_FUSED_SCAN=1 / 0 forces one or the other.
+    const bool scan_in_router = !f32mode && (h->fuse_scan < 0 ? h->small_batch : h->fuse_scan != 0);
     route::ScanTail tail{};
     if (scan_in_router) {
         tail.done = h->status + 1;
@@ -1077,20 +1082,24 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     DeviceGuard guard(h->device);
     const size_t n = (size_t)h->Tmax * h->d;
     constexpr int MAX_CHUNKS = 64;
-    if (!h->stage_x) {
-        int rc = dalloc(&h->stage_x, n);
-        if (rc == PRICHS_OK) rc = dalloc(&h->stage_y, n);
-        if (rc == PRICHS_OK) rc = dalloc(&h->counts_acc, route::MAX_E);
-    if (rc != PRICHS_OK) return rc;
-        CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
-        CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
-        CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
-        h->chunk_ev = new cudaEvent_t[2 * MAX_CHUNKS];
-        for (int i = 0; i < 2 * MAX_CHUNKS; ++i) CUDA_TRY(cudaEventCreateWithFlags(&h->chunk_ev[i], cudaEventDisableTiming));
+    if (!h->host_ready) {
+        // every resource is created only if it is still missing, so a call that failed half way can be repeated
+        int rc = PRICHS_OK;
+        if (!h->stage_x) rc = dalloc(&h->stage_x, n);
+        if (rc == PRICHS_OK && !h->stage_y) rc = dalloc(&h->stage_y, n);
+        if (rc == PRICHS_OK && !h->counts_acc) rc = dalloc(&h->counts_acc, route::MAX_E);
+        if (rc != PRICHS_OK) return rc;
+        if (!h->own_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+        if (!h->in_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+        if (!h->out_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+        if (!h->chunk_ev) h->chunk_ev = new cudaEvent_t[2 * MAX_CHUNKS]();
+        for (int i = 0; i < 2 * MAX_CHUNKS; ++i)
+            if (!h->chunk_ev[i]) CUDA_TRY(cudaEventCreateWithFlags(&h->chunk_ev[i], cudaEventDisableTiming));
+        h->host_ready = true;
     }
     if (resid_host && !h->stage_r) {
         int rc = dalloc(&h->stage_r, n);
-    if (rc != PRICHS_OK) return rc;
+        if (rc != PRICHS_OK) return rc;
     }
     // Tokens are independent, so a large batch is fed through in chunks: the upload of chunk i+1 and the
     // download of chunk i-1 overlap the kernels of chunk i (three streams). Results are bit-identical to one
