@@ -291,6 +291,8 @@ struct prichs_moe {
     const float* norm_w;  // set while the block entry point runs with the pre-norm folded into the router's read
     float norm_eps;
     bool fuse_norm;
+    bool router_tma;      // large bf16 batches use the shared-memory-staged router kernel (opt-in)
+    int router_stages;    // depth of its ring of tile buffers
     int fuse_scan;  // single-GPU forward, scan + plan at the tail of the router launch: 1 always, 0 never, -1 for small batches
     void* ybuf;
     float *logits, *gates;
@@ -385,6 +387,19 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
     } else {
         constexpr int RT = route::ROUTER_WARPS * 32;
         const bool xf32 = x_dtype == PRICHS_DTYPE_F32, norm = h->norm_w != nullptr;
+        if (h->router_tma && !xf32 && !norm && tail.done == nullptr && ntiles_all >= h->sm_count) {
+            // large bf16 batch: persistent CTAs, rows staged through shared memory by bulk copies
+            const int grid = std::min(ntiles_all, h->sm_count);
+            const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
+            if (h->rt_nsplit == 1)
+                LAUNCH_K(pdl, route::router_tma_kernel<1>, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
+                         (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
+            else
+                LAUNCH_K(pdl, route::router_tma_kernel<3>, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
+                         (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
+            LAUNCH_CHECK("router");
+            return PRICHS_OK;
+        }
         bf16* xs = (xf32 || norm) ? h->xs : nullptr;  // bf16 (and normalised) copy of the rows for the expert GEMMs
 #define PRICHS_ROUTER_CASE(NS, XF, NM)                                                                                              \
     if (h->rt_nsplit == NS && xf32 == XF && norm == NM)                                                                             \
@@ -798,6 +813,20 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->pdl = pd && atoi(pd) != 0;
         const char* cm = getenv("PRICHS_EP_COMBINE_MODE");
         h->ep_combine_mode = cm ? atoi(cm) : 1;
+        // PRICHS_ROUTER=staged routes large bf16 batches with the kernel that stages the rows through shared memory
+        // (bit-identical results). Off by default: measured on B200 it is slower than the register-staged kernel
+        // (23.5 vs 19.3 us at T = 16384, 39.9 vs 30.1 us at T = 32768).
+        const char* rk = getenv("PRICHS_ROUTER");
+        h->router_stages = std::min(route::ROUTER_TMA_MAX_STAGES, (200 * 1024) / route::router_tma_stage_bytes(d));
+        const char* rst = getenv("PRICHS_ROUTER_STAGES");  // a shallower ring (2..4), for tests
+        if (rst && atoi(rst) >= 2) h->router_stages = std::min(h->router_stages, atoi(rst));
+        h->router_tma = rk && strcmp(rk, "staged") == 0 && h->mode != PRICHS_MODE_F32 && h->router_stages >= 2;
+        if (h->router_tma && rc == PRICHS_OK) {
+            const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
+            if (cudaFuncSetAttribute(route::router_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+                cudaFuncSetAttribute(route::router_tma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+                rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the router", bytes);
+        }
     }
     for (int i = 0; i < 7 && rc == PRICHS_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = fail(PRICHS_ERR_CUDA, "cudaEventCreate failed");
