@@ -292,6 +292,7 @@ struct prichs_moe {
     float norm_eps;
     bool fuse_norm;
     bool router_tma;      // large bf16 batches use the shared-memory-staged router kernel (opt-in)
+    bool router_warp;     // large bf16 batches with bf16-exact router weights use the warp-per-tile router kernel (opt-in)
     int router_stages;    // depth of its ring of tile buffers
     int fuse_scan;  // single-GPU forward, scan + plan at the tail of the router launch: 1 always, 0 never, -1 for small batches
     void* ybuf;
@@ -387,16 +388,19 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
     } else {
         constexpr int RT = route::ROUTER_WARPS * 32;
         const bool xf32 = x_dtype == PRICHS_DTYPE_F32, norm = h->norm_w != nullptr;
-        if (h->router_tma && !xf32 && !norm && tail.done == nullptr && ntiles_all >= h->sm_count) {
+        if (h->router_warp && !xf32 && !norm && tail.done == nullptr && h->rt_nsplit == 1 && ntiles_all >= h->sm_count) {
+            const int grid = (ntiles_all + route::ROUTER_WARP_CTA_WARPS - 1) / route::ROUTER_WARP_CTA_WARPS;
+            LAUNCH_K(pdl, route::router_warp_kernel, grid, route::ROUTER_WARP_CTA_WARPS * 32, 0, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
+                     (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
+            LAUNCH_CHECK("router");
+            return PRICHS_OK;
+        }
+        if (h->router_tma && !xf32 && !norm && tail.done == nullptr && h->rt_nsplit == 1 && ntiles_all >= h->sm_count) {
             // large bf16 batch: persistent CTAs, rows staged through shared memory by bulk copies
             const int grid = std::min(ntiles_all, h->sm_count);
             const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
-            if (h->rt_nsplit == 1)
-                LAUNCH_K(pdl, route::router_tma_kernel<1>, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
-                         (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
-            else
-                LAUNCH_K(pdl, route::router_tma_kernel<3>, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
-                         (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
+            LAUNCH_K(pdl, route::router_tma_kernel, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
+                     (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
             LAUNCH_CHECK("router");
             return PRICHS_OK;
         }
@@ -813,18 +817,20 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->pdl = pd && atoi(pd) != 0;
         const char* cm = getenv("PRICHS_EP_COMBINE_MODE");
         h->ep_combine_mode = cm ? atoi(cm) : 1;
-        // PRICHS_ROUTER=staged routes large bf16 batches with the kernel that stages the rows through shared memory
-        // (bit-identical results). Off by default: measured on B200 it is slower than the register-staged kernel
-        // (23.5 vs 19.3 us at T = 16384, 39.9 vs 30.1 us at T = 32768).
+        // Large bf16 batches with bf16-exact router weights can be routed by two alternative kernels, both
+        // bit-identical to the default one (eight warps in lock step per tile): PRICHS_ROUTER=warp (one independent
+        // warp per tile) and PRICHS_ROUTER=staged (rows streamed through a shared-memory ring with bulk copies, one
+        // consumer warp per stage). Measured on B200 all three take 20-21 us for 16384 tokens and 30-35 us for 32768
+        // inside a forward, so neither replaces the default.
         const char* rk = getenv("PRICHS_ROUTER");
-        h->router_stages = std::min(route::ROUTER_TMA_MAX_STAGES, (200 * 1024) / route::router_tma_stage_bytes(d));
+        h->router_stages = std::min(route::ROUTER_TMA_MAX_STAGES, (227 * 1024 - route::router_tma_weight_bytes(d) - 128) / route::router_tma_stage_bytes(d));
         const char* rst = getenv("PRICHS_ROUTER_STAGES");  // a shallower ring (2..4), for tests
         if (rst && atoi(rst) >= 2) h->router_stages = std::min(h->router_stages, atoi(rst));
         h->router_tma = rk && strcmp(rk, "staged") == 0 && h->mode != PRICHS_MODE_F32 && h->router_stages >= 2;
+        h->router_warp = rk && strcmp(rk, "warp") == 0 && h->mode != PRICHS_MODE_F32;
         if (h->router_tma && rc == PRICHS_OK) {
             const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
-            if (cudaFuncSetAttribute(route::router_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
-                cudaFuncSetAttribute(route::router_tma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+            if (cudaFuncSetAttribute(route::router_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
                 rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the router", bytes);
         }
     }

@@ -376,27 +376,117 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Alternative router for large bf16 batches (opt-in): the same arithmetic as router_mma_kernel<NSPLIT, false,
-// false> (bit-identical logits), but the rows reach the SM through shared memory. One persistent CTA per SM; a
-// producer thread streams the 16-token tiles (16 contiguous rows) with untiled bulk copies, one per row, into a
-// ring of `stages` buffers that completes on an mbarrier per stage. Eight consumer warps split K as before, read
-// their MMA fragments from the stage (rows padded by 64 bytes: the two rows a quarter-warp touches fall on
-// disjoint banks), release the stage, and meet at a named barrier; the warps take turns to add the partial sums
-// and select. Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag, all consumers
-// leave together after the next barrier, the producer lets its copies land, and the status word reports it.
-// Measured on B200 this kernel is slower than the register-staged one (23.5 vs 19.3 us for 16384 tokens), so the
-// library does not select it unless asked to.
-constexpr int ROUTER_TMA_THREADS = (ROUTER_WARPS + 1) * 32;
+// Router for large bf16 batches with bf16-exact router weights: one WARP per 16-token tile, no shared memory and
+// no barrier. The warp walks the tile's K in 32-element slices with eight slices (8 KB) in flight at all times: a
+// ring of eight register slots, each refilled with the slice eight steps ahead as soon as it has been consumed.
+// Slice i feeds accumulator set i % 8, which therefore sees exactly the slices warp i % 8 of router_mma_kernel
+// sees, in the same order, and the eight sets are added in that kernel's warp order: the logits are bit-identical
+// to router_mma_kernel<1, false, false>. Where that kernel runs a tile on eight warps in lock step (loads, then a
+// barrier, then one warp selects while seven wait), here every warp is independent: with ~7-14 tiles in flight
+// per SM the loads of one tile overlap the selection of another, and the time of the launch is close to the time
+// one warp needs to stream its 48 KB.
+constexpr int ROUTER_WARP_CTA_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTER_WARP_CTA_WARPS * 32)
+router_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wrt, const float* __restrict__ bias,
+                   const ConceptBias cb, int T, int d, int E, int top_k, float* __restrict__ logits, int* __restrict__ sel,
+                   float* __restrict__ gates, int* __restrict__ tile_counts) {
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
+    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
+    const int tile = blockIdx.x * ROUTER_WARP_CTA_WARPS + (threadIdx.x >> 5);
+    if (tile >= ntiles) return;
+    const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
+    const __nv_bfloat16* x0 = x + (size_t)min(r0, T - 1) * d + 8 * q;
+    const __nv_bfloat16* x1 = x + (size_t)min(r1, T - 1) * d + 8 * q;
+    const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
+
+    constexpr int RING = ROUTER_WARPS;  // slices in flight = accumulator sets = warps of the lock-step kernel
+    float acc[RING][2][4];
+#pragma unroll
+    for (int w = 0; w < RING; ++w)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[w][hh][i] = 0.f;
+    uint4 xa[RING], xb[RING];
+#pragma unroll
+    for (int w = 0; w < RING; ++w) {  // d is a multiple of 256: the first eight slices always exist
+        xa[w] = ptx::ld_stream_16(x0 + 32 * w);
+        xb[w] = ptx::ld_stream_16(x1 + 32 * w);
+    }
+    for (int kc = 0; kc < d; kc += RING * 32) {
+#pragma unroll
+        for (int w = 0; w < RING; ++w) {
+            const int kk = kc + 32 * w;
+            const uint4 a0 = xa[w], a1 = xb[w];
+            if (kk + RING * 32 < d) {  // refill the slot with the slice eight steps ahead
+                xa[w] = ptx::ld_stream_16(x0 + kk + RING * 32);
+                xb[w] = ptx::ld_stream_16(x1 + kk + RING * 32);
+            }
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wl + kk));
+            ptx::mma_m16n8k16_bf16(acc[w][0], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+            ptx::mma_m16n8k16_bf16(acc[w][1], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+        }
+    }
+    // c[0..1]: row g, experts 2q, 2q+1; c[2..3]: row g+8; sets added in the order the lock-step kernel adds its warps
+    float c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float v = 0.f;
+        v += acc[0][0][i] + acc[0][1][i];
+        c[i] = v;
+    }
+#pragma unroll
+    for (int w = 1; w < RING; ++w)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float v = 0.f;
+            v += acc[w][0][i] + acc[w][1][i];
+            c[i] += v;
+        }
+    float L[MAX_E];
+    const int qbase = lane & ~3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
+        const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
+        const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
+        const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
+        L[2 * j] = (q == 0) ? t0 : t2;
+        L[2 * j + 1] = (q == 0) ? t1 : t3;
+    }
+    const int row = (q == 0) ? r0 : r1;
+    const bool active = (q < 2) && (row < T);
+    const uint32_t below = (1u << (4 * g)) - 1u;
+    const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
+    route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Alternative router for large bf16 batches with bf16-exact router weights (opt-in): the arithmetic of
+// router_mma_kernel<1, false, false> in the same order (bit-identical logits), with the rows streamed through
+// shared memory. One persistent CTA per SM; a producer thread copies the 16-token tiles (16 contiguous rows) with
+// untiled bulk copies, one per row, into a ring of `stages` buffers, each with a full and an empty mbarrier, so
+// the ring's 100-200 KB per SM are in flight whatever the consumers do. Consumer warp w owns stage w: it waits
+// for its tile, walks all of K out of shared memory (router weights are staged there too; rows of both are padded
+// by 64 bytes so that the two rows a quarter-warp touches fall on disjoint banks) into eight accumulator sets --
+// slice i feeds set i % 8, the slices warp i % 8 of the lock-step kernel sees, added in that kernel's warp order --
+// hands the stage back and selects. No CTA-wide barrier inside the loop: the warps are independent.
+// Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag, every role leaves its loop, the
+// producer lets its copies land, and the status word reports it.
 constexpr int ROUTER_TMA_MAX_STAGES = 4;
+constexpr int ROUTER_TMA_THREADS = (ROUTER_TMA_MAX_STAGES + 1) * 32;
 constexpr int ROUTER_TMA_ROW_PAD = 64;
 constexpr long long ROUTER_WAIT_CYCLES = 4000000000LL;
 
 __host__ __device__ inline int router_tma_stage_bytes(int d) { return TILE_TOKENS * (2 * d + ROUTER_TMA_ROW_PAD); }
+__host__ __device__ inline int router_tma_weight_bytes(int d) { return MAX_E * (2 * d + ROUTER_TMA_ROW_PAD); }
 __host__ __device__ inline int router_tma_smem_bytes(int d, int stages) {
-    return stages * router_tma_stage_bytes(d) + 2 * ROUTER_TMA_MAX_STAGES * 8 + 2 * ROUTER_WARPS * 32 * 16 + 16;
+    return stages * router_tma_stage_bytes(d) + router_tma_weight_bytes(d) + 2 * ROUTER_TMA_MAX_STAGES * 8 + 16;
 }
 
-template <int NSPLIT>
 __global__ void __launch_bounds__(ROUTER_TMA_THREADS, 1)
 router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wrt, const float* __restrict__ bias,
                   const ConceptBias cb, int T, int d, int E, int top_k, float* __restrict__ logits, int* __restrict__ sel,
@@ -404,11 +494,10 @@ router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     extern __shared__ __align__(128) uint8_t rsm[];
     const int rowb = 2 * d + ROUTER_TMA_ROW_PAD;
     const int stage_bytes = TILE_TOKENS * rowb;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(rsm + (size_t)stages * stage_bytes);
+    uint8_t* wsm = rsm + (size_t)stages * stage_bytes;  // router weights, [8][rowb]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(wsm + MAX_E * rowb);
     uint64_t* empty_bar = full_bar + ROUTER_TMA_MAX_STAGES;
-    float4* partial = reinterpret_cast<float4*>(empty_bar + ROUTER_TMA_MAX_STAGES);  // [2][ROUTER_WARPS][32]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(partial + 2 * ROUTER_WARPS * 32);
-    volatile int* abort_seen = abort_flag + 1;  // [2]: the flag as thread 0 saw it before the tile's barrier
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + ROUTER_TMA_MAX_STAGES);
 
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
@@ -416,22 +505,26 @@ router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
-            ptx::mbar_init(&empty_bar[s], ROUTER_WARPS);
+            ptx::mbar_init(&empty_bar[s], 1);
         }
         *abort_flag = 0;
-        abort_seen[0] = abort_seen[1] = 0;
         ptx::fence_barrier_init();
+    }
+    // the transposed router weights [8][d] into padded shared-memory rows, 16 bytes per thread and step
+    for (int i = threadIdx.x; i < MAX_E * (d / 8); i += ROUTER_TMA_THREADS) {
+        const int e = i / (d / 8), c = i - e * (d / 8);
+        *reinterpret_cast<uint4*>(wsm + (size_t)e * rowb + 16 * c) = __ldg(reinterpret_cast<const uint4*>(wrt + (size_t)e * d) + c);
     }
     __syncthreads();
     const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
     const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
-    if (warp == ROUTER_WARPS) {
+    if (warp == ROUTER_TMA_MAX_STAGES) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int it = 0; ok && it < my_tiles; ++it) {
+            for (int it = 0; it < my_tiles; ++it) {
                 const int s = it % stages;
                 const uint32_t ph = (uint32_t)((it / stages) & 1);
                 if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, ROUTER_WAIT_CYCLES)) {
@@ -456,81 +549,70 @@ router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
                 }
             }
         }
-    } else {
-        // ---------------------------------------------------------------- consumers
+    } else if (warp < stages) {
+        // ---------------------------------------------------------------- consumer warp of stage `warp`
         const int g = lane >> 2, q = lane & 3;
-        const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
-        const size_t wsplit = (size_t)MAX_E * d;
-        for (int it = 0; it < my_tiles; ++it) {
-            const int s = it % stages, buf = it & 1;
-            const uint32_t ph = (uint32_t)((it / stages) & 1);
+        const uint8_t* r0p = rsm + (size_t)warp * stage_bytes + (size_t)g * rowb + 16 * q;
+        const uint8_t* r1p = r0p + 8 * (size_t)rowb;
+        const uint8_t* wp = wsm + (size_t)g * rowb + 16 * q;
+        for (int it = warp, n = 0; it < my_tiles; it += stages, ++n) {
             const int tile = blockIdx.x + it * gridDim.x;
-            // a wait that gives up still falls through to the barrier below: nobody may leave before it
-            ptx::mbar_wait_bounded(&full_bar[s], ph, abort_flag, ROUTER_WAIT_CYCLES);
-            const uint8_t* r0p = rsm + (size_t)s * stage_bytes + (size_t)g * rowb + 16 * q;
-            const uint8_t* r1p = r0p + 8 * (size_t)rowb;
-
-            float acc[NSPLIT][2][4];
+            if (!ptx::mbar_wait_bounded(&full_bar[warp], (uint32_t)(n & 1), abort_flag, ROUTER_WAIT_CYCLES)) break;
+            float acc[ROUTER_WARPS][2][4];
 #pragma unroll
-            for (int sp = 0; sp < NSPLIT; ++sp)
+            for (int w = 0; w < ROUTER_WARPS; ++w)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[sp][hh][i] = 0.f;
-#pragma unroll 6
-            for (int kk = warp * 32; kk < d; kk += ROUTER_WARPS * 32) {
-                const uint4 a0 = *reinterpret_cast<const uint4*>(r0p + 2 * kk);
-                const uint4 a1 = *reinterpret_cast<const uint4*>(r1p + 2 * kk);
+                    for (int i = 0; i < 4; ++i) acc[w][hh][i] = 0.f;
+            for (int kc = 0; kc < d; kc += ROUTER_WARPS * 32) {
 #pragma unroll
-                for (int sp = 0; sp < NSPLIT; ++sp) {
-                    const uint4 w = __ldg(reinterpret_cast<const uint4*>(wl + sp * wsplit + kk));
-                    ptx::mma_m16n8k16_bf16(acc[sp][0], a0.x, a1.x, a0.y, a1.y, w.x, w.y);
-                    ptx::mma_m16n8k16_bf16(acc[sp][1], a0.z, a1.z, a0.w, a1.w, w.z, w.w);
+                for (int w = 0; w < ROUTER_WARPS; ++w) {
+                    const int kb = 2 * (kc + 32 * w);
+                    const uint4 a0 = *reinterpret_cast<const uint4*>(r0p + kb);
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(r1p + kb);
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wp + kb);
+                    ptx::mma_m16n8k16_bf16(acc[w][0], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+                    ptx::mma_m16n8k16_bf16(acc[w][1], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
                 }
             }
-            // this warp is done with the stage
+            // the tile has been read: hand the stage back to the producer
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty_bar[s]);
+            if (lane == 0) ptx::mbar_arrive(&empty_bar[warp]);
 
+            // sets added in the order the lock-step kernel adds its warps
             float c[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float v = 0.f;
-#pragma unroll
-                for (int sp = NSPLIT - 1; sp >= 0; --sp) v += acc[sp][0][i] + acc[sp][1][i];
+                v += acc[0][0][i] + acc[0][1][i];
                 c[i] = v;
             }
-            partial[(buf * ROUTER_WARPS + warp) * 32 + lane] = make_float4(c[0], c[1], c[2], c[3]);
-            if (threadIdx.x == 0) abort_seen[buf] = *abort_flag;
-            asm volatile("bar.sync 1, %0;" ::"n"(ROUTER_WARPS * 32) : "memory");
-            if (abort_seen[buf]) break;  // the same value for all consumers
-            if (warp == (it & (ROUTER_WARPS - 1))) {
-                // partial sums in warp order 0..7, as the register-staged kernel adds them
-                float4 p = partial[(buf * ROUTER_WARPS + 0) * 32 + lane];
-                c[0] = p.x; c[1] = p.y; c[2] = p.z; c[3] = p.w;
 #pragma unroll
-                for (int w = 1; w < ROUTER_WARPS; ++w) {
-                    p = partial[(buf * ROUTER_WARPS + w) * 32 + lane];
-                    c[0] += p.x; c[1] += p.y; c[2] += p.z; c[3] += p.w;
-                }
-                float L[MAX_E];
-                const int qbase = lane & ~3;
+            for (int w = 1; w < ROUTER_WARPS; ++w)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
-                    const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
-                    const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
-                    const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
-                    L[2 * j] = (q == 0) ? t0 : t2;
-                    L[2 * j + 1] = (q == 0) ? t1 : t3;
+                for (int i = 0; i < 4; ++i) {
+                    float v = 0.f;
+                    v += acc[w][0][i] + acc[w][1][i];
+                    c[i] += v;
                 }
-                const int r0 = tile * TILE_TOKENS + g;
-                const int row = (q == 0) ? r0 : r0 + 8;
-                const bool active = (q < 2) && (row < T);
-                const uint32_t below = (1u << (4 * g)) - 1u;
-                const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
-                route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
+            float L[MAX_E];
+            const int qbase = lane & ~3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
+                const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
+                const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
+                const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
+                L[2 * j] = (q == 0) ? t0 : t2;
+                L[2 * j + 1] = (q == 0) ? t1 : t3;
             }
+            const int r0 = tile * TILE_TOKENS + g;
+            const int row = (q == 0) ? r0 : r0 + 8;
+            const bool active = (q < 2) && (row < T);
+            const uint32_t below = (1u << (4 * g)) - 1u;
+            const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
+            route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
         }
     }
     __syncthreads();

@@ -360,11 +360,13 @@ def test_scan_at_router_tail_equals_separate_scan_launch(torch_cuda, monkeypatch
 
 
 @pytest.mark.parametrize("d,T,exact_router,stages", [(512, 5003, True, None), (1536, 4096, False, None), (1024, 7001, True, "2")])
-def test_staged_router_kernel_equals_register_staged_kernel(torch_cuda, monkeypatch, d, T, exact_router, stages):
-    """PRICHS_ROUTER=staged (read when the handle is created) routes large bf16 batches with the kernel that stages
-    the rows through shared memory with bulk copies instead of the register-staged kernel. Same arithmetic in
-    the same order: logits, selection, gates, counts and the layer output must be bit-identical. Covers a ragged
-    last tile, a 2-stage ring (PRICHS_ROUTER_STAGES) and both router-weight forms (bf16-exact: 1 part, fp32: 3 parts)."""
+def test_alternative_router_kernels_equal_the_lock_step_kernel(torch_cuda, monkeypatch, d, T, exact_router, stages):
+    """Large bf16 batches can be routed by three kernels (PRICHS_ROUTER, read when the handle is created): `legacy`,
+    eight warps in lock step per 16-token tile (the default); `warp`, one independent warp per tile; `staged`, rows
+    streamed through a shared-memory ring with bulk copies, one consumer warp per stage. Same
+    arithmetic in the same order: logits, selection, gates, counts, tile histograms and the layer output must be
+    bit-identical. Covers a ragged last tile, a 2-stage ring and both router-weight forms (bf16-exact: 1 part,
+    fp32: 3 parts, where `warp` and `staged` fall back to the lock-step kernel)."""
     import torch
     from prichs_b200 import MoELayer, synth
     f, E, k = 256, 8, 2
@@ -372,10 +374,10 @@ def test_staged_router_kernel_equals_register_staged_kernel(torch_cuda, monkeypa
     if not exact_router:
         ws[0] = synth.normal(86, 0, (d, E), 0.0, 0.03).astype(np.float32)
     x = synth.round_bf16(synth.normal(87, 0, (T, d)))
-    outs = []
     if stages:
         monkeypatch.setenv("PRICHS_ROUTER_STAGES", stages)
-    for kind in ("staged", "legacy"):
+    outs = []
+    for kind in ("legacy", "warp", "staged"):
         monkeypatch.setenv("PRICHS_ROUTER", kind)
         m = MoELayer.from_weights(ws, k, mode="bf16")
         m.router_bias = synth.router_bias(85, E, -0.1, 0.1)
@@ -385,8 +387,9 @@ def test_staged_router_kernel_equals_register_staged_kernel(torch_cuda, monkeypa
         st = m.last_stash()
         outs.append((y, st.router_logits.copy(), st.selected_experts.copy(), st.gating_weights.copy(),
                      st.expert_token_counts.copy(), m.debug_buffer(6, ((T + 15) // 16) * 8 * 4).copy()))
-    for a, b in zip(outs[0], outs[1]):
-        assert np.array_equal(a, b)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert np.array_equal(a, b)
 
 
 def test_rmsnorm_reference_fixture_values(torch_cuda, oracle):

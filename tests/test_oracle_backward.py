@@ -161,3 +161,37 @@ def test_token_without_gradient_leaves_its_experts_untouched(oracle):
     assert np.all(a["d_x"][T // 2:] == 0) and np.all(b["d_x"][:T // 2] == 0)
     for ga, gb, gf in zip(a["grads"], b["grads"], full["grads"]):
         np.testing.assert_allclose(ga + gb, gf, rtol=1e-4, atol=1e-5)
+
+
+def test_backward_properties_hypothesis(oracle):
+    """Randomised properties of the backward restatement: linear in d_out, the router-logit gradients of a token sum
+    to zero (so dW_router's columns sum to zero over the experts), experts without tokens get exactly zero gradients,
+    and a top-1 layer (one selected expert: gate = 1/(1+1e-9)) sends no gradient to the router."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=25, deadline=None)
+    @given(st.integers(1, 12), st.integers(2, 6), st.integers(1, 2), st.integers(0, 2**31 - 1))
+    def prop(T, E, k, seed):
+        rng = np.random.default_rng(seed)
+        d, f = 8, 4
+        ws = [rng.standard_normal((d, E)).astype(np.float32) * 0.3]
+        for _ in range(1 + E):
+            ws += [rng.standard_normal((d, f)).astype(np.float32) * 0.3, rng.standard_normal((d, f)).astype(np.float32) * 0.3,
+                   rng.standard_normal((f, d)).astype(np.float32) * 0.3]
+        bias = rng.standard_normal(E).astype(np.float32) * 0.1
+        x = rng.standard_normal((T, d)).astype(np.float32)
+        R = rng.standard_normal((T, d)).astype(np.float32)
+        fwd = oracle.moe_forward_train(ws, bias, k, x)
+        one = oracle.moe_backward(ws, bias, k, x, R)
+        two = oracle.moe_backward(ws, bias, k, x, 2.0 * R)  # scaling by a power of two is exact
+        assert np.array_equal(two["d_x"], 2.0 * one["d_x"])
+        for a, b in zip(two["grads"], one["grads"]):
+            assert np.array_equal(a, 2.0 * b)
+        assert np.abs(one["grads"][0].sum(axis=1)).max() <= 1e-4 * (1.0 + np.abs(one["grads"][0]).max())
+        for e in range(E):
+            if fwd["counts"][e] == 0:
+                assert all(not one["grads"][4 + 3 * e + j].any() for j in range(3))
+        if k == 1:
+            assert np.abs(one["grads"][0]).max() <= 1e-6 * (1.0 + np.abs(R).max() * np.abs(x).max() * 10)
+
+    prop()
