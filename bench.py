@@ -35,6 +35,22 @@ DISPATCH_BYTES = D * 2 + K * D * 2 + K * 4 + K * 4
 COMBINE_BYTES_NORES = (K + 1) * D * 2 + D * 2 + K * 4 + K * 4  # no residual in the benchmarked call
 
 
+def roofline_sum(T, gemm_rows, ms_step, peaks, world=1):
+    """Lower bound of one forward from the rooflines of its stages, and the measured step against it:
+    GEMM flops / tensor peak + (router + dispatch + combine bytes) / HBM peak, plus, for an expert-parallel group,
+    the dispatch and combine rows that cross NVLink at 900 GB/s per direction (un-overlapped: summed; overlapped: the
+    larger of the exchange and everything else)."""
+    t_gemm = gemm_rows * 6 * D * F / (peaks["tf"] * 1e12)
+    t_hbm = T * (ROUTER_BYTES + DISPATCH_BYTES + COMBINE_BYTES_NORES) / (peaks["hbm"] * 1e9)
+    t_comm = 2 * T * K * D * 2 * (world - 1) / world / 900e9 if world > 1 else 0.0
+    serial = (t_gemm + t_hbm + t_comm) * 1e3
+    overlapped = max(t_gemm + t_hbm, t_comm) * 1e3
+    out = {"ms": serial, "frac": serial / ms_step, "gemm_ms": t_gemm * 1e3, "hbm_ms": t_hbm * 1e3}
+    if world > 1:
+        out.update({"comm_ms": t_comm * 1e3, "ms_overlapped": overlapped, "frac_overlapped": overlapped / ms_step})
+    return out
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -470,6 +486,7 @@ def main():
                 "api": "MoELayer.forward(numpy fp32 [T,d]) -> prichs_moe_forward_host, pinned host buffers"},
         "gpu_launches": launches, "roofline": roofline, "stages": stages, "ep_timeline": timeline,
         "layer_tflops": tokens * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,
+        "roofline_sum": roofline_sum(T, rows, ms_step, peaks, world),
         "clocks": clocks.summary(),
     }
     if world > 1 and args.config == 4:

@@ -29,3 +29,25 @@ def test_reference_arm_other_ranks_do_no_work():
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
                           "--warmup", "0"], capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_roofline_sum_arithmetic():
+    """`roofline_sum` of the bench line: GEMM flops over the tensor peak plus stage bytes over the HBM peak, with the
+    NVLink term only for an expert-parallel group."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    peaks = dict(hbm=6000.0, tf=1500.0, tf_sustained=1400.0, source="test")
+    T = 16384
+    r = bench.roofline_sum(T, 3 * T, 0.5, peaks)
+    gemm = 3 * T * 6 * 1536 * 1280 / 1500e12 * 1e3
+    hbm = T * (3088 + 9232 + 12304) / 6000e9 * 1e3
+    assert abs(r["gemm_ms"] - gemm) < 1e-9 and abs(r["hbm_ms"] - hbm) < 1e-9
+    assert abs(r["ms"] - (gemm + hbm)) < 1e-9 and abs(r["frac"] - (gemm + hbm) / 0.5) < 1e-9
+    assert "comm_ms" not in r
+    r8 = bench.roofline_sum(T, 3 * T, 1.0, peaks, world=8)
+    comm = 2 * T * 2 * 1536 * 2 * 7 / 8 / 900e9 * 1e3
+    assert abs(r8["comm_ms"] - comm) < 1e-9
+    assert abs(r8["ms_overlapped"] - max(gemm + hbm, comm)) < 1e-9
