@@ -144,6 +144,26 @@ PRICHS_API int prichs_moe_get_routing(prichs_moe_t* h, float* logits_host, int32
 
 /* ---- aux-loss-free bias update ------------------------------------------------------------------- */
 
+/* Backward of the last forward on this handle: the MoE section of the reference's per-block backward pass
+ * (crates/prichs-model/src/model.rs:566-766; helpers crates/prichs-core/src/ops.rs:64-104 matmul_at_b / matmul_a_bt,
+ * crates/prichs-core/src/backward.rs:247-287 swiglu_activation_backward / moe_router_unbiased_backward; the engine's
+ * counterparts are gpu_moe_backward_* in crates/prichs-cuda/src/engine.rs:2242-2789).
+ *   x_dev     the layer input of that forward, [T,d] of x_dtype, unchanged since (`normed2` in the reference)
+ *   dy_dev    gradient of the layer output, [T,d] of dy_dtype (`d_moe`)
+ *   dx_dev    [T,d] fp32, overwritten with the gradient of the layer input (`d_normed2`): shared expert + routed
+ *             experts in ascending order + router. As in the reference, a routed expert's input gradient carries the
+ *             gate weight twice (dY_e = w * d_out, model.rs:647-656, and w * dX_e in the scatter-add, model.rs:724-732)
+ *   grads_dev n_grads = 1 + 3 * (1 + E) device pointers to fp32 buffers in the order and [in, out] layouts of
+ *             prichs_moe_upload_weights (router [d,E], shared gate [d,f], up [d,f], down [f,d], expert e ...); the
+ *             gradients are ADDED to them (the reference's matmul_at_b accumulates). Null entries are skipped; a null
+ *             array computes dx only. Experts that received no token are left untouched (model.rs:641-643).
+ * All experts local (ep_world = 1), bf16 mode, intermediate_dim a multiple of 256. T is the T of the last forward.
+ * Operands are bf16 with fp32 accumulation; the gate/up pre-activations are recomputed, not stashed. The call
+ * waits for the forward, reads its placement, enqueues its work on `stream` and returns when that has finished;
+ * its workspace is allocated by the first call. */
+PRICHS_API int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* dy_dev, int dy_dtype,
+                                   float* dx_dev, float* const* grads_dev, int n_grads, void* stream);
+
 /* MoELayer::update_aux_free_bias(expert_token_counts, total_tokens, gamma) (moe.rs:228-245) with host
  * counts, as the reference's call sites pass them (model.rs:786-792,1541-1548):
  *   b_i += gamma * (top_k/E - counts[i]/total_tokens);   no-op when total_tokens == 0. */

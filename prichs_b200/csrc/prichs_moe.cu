@@ -27,6 +27,7 @@
 #include "expert_gemm_pair_sm100.cuh"
 #include "expert_gemm_sm100.cuh"
 #include "route_sm100.cuh"
+#include "backward_sm100.cuh"
 
 namespace {
 
@@ -96,14 +97,16 @@ EncodeTiledFn get_encode_fn() {
 
 // Row-major matrix [rows, cols] of bf16 (or fp32) -> tensor map whose box is 128 bytes wide (64 bf16 or 32
 // fp32 elements) and box_rows tall, with the 128-byte swizzle.
-int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int box_rows, bool f32 = false) {
+// `pitch` (elements, 0 = cols): distance between rows when the map covers a window of a wider matrix.
+int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int box_rows, bool f32 = false, size_t pitch = 0) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(PRICHS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const size_t esz = f32 ? 4 : 2;
-    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (cols * esz) % 16 != 0)
+    if (pitch == 0) pitch = cols;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch * esz) % 16 != 0)
         return fail(PRICHS_ERR_BAD_ARG, "tensor map base and row pitch must be 16-byte aligned");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(cols * esz)};
+    cuuint64_t strides[1] = {(cuuint64_t)(pitch * esz)};
     cuuint32_t box[2] = {(cuuint32_t)(128 / esz), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
@@ -329,8 +332,18 @@ struct prichs_moe {
     cudaStream_t own_stream, in_stream, out_stream;
     cudaEvent_t* chunk_ev;
 
+    // backward pass (allocated by the first prichs_moe_backward): recomputed pre-activations, gradient buffers in
+    // the forward's row space, transposed copies for the weight-gradient products, un-transposed weight copies
+    struct Bwd {
+        bool ready, nat_valid;
+        bf16 *gu, *dyall, *dh, *dgu, *dxall, *xT, *hT, *dyT, *dguT, *w_dn_nat, *w_gu_nat;
+        float *scal, *dlog, *dwr_part, *stage_dn, *stage_gu;
+        CUtensorMap tm_dyall, tm_dgu, tm_gu_out, tm_dh_out, tm_dxall_out, tm_wdn_nat, tm_wgu_nat, tm_stage_dn, tm_stage_gu;
+    } bwd;
+
     cudaStream_t last_stream;
     int last_T;
+    bool last_chunked;  // the last forward went through the host-buffer pipeline in chunks: only its last chunk's rows remain
     int tok_base;  // see prichs_moe_forward
     int resid_dtype;  // element type of the residual when it differs from x (block entry point), else -1
     bool timing;
@@ -887,6 +900,12 @@ int prichs_moe_destroy(prichs_moe_t* h) {
         delete[] h->chunk_ev;
     }
     if (h->counts_acc) cudaFree(h->counts_acc);
+    {
+        void* bp[] = {h->bwd.gu, h->bwd.dyall, h->bwd.dh, h->bwd.dgu, h->bwd.dxall, h->bwd.xT, h->bwd.hT, h->bwd.dyT, h->bwd.dguT,
+                      h->bwd.w_dn_nat, h->bwd.w_gu_nat, h->bwd.scal, h->bwd.dlog, h->bwd.dwr_part, h->bwd.stage_dn, h->bwd.stage_gu};
+        for (void* q : bp)
+            if (q) cudaFree(q);
+    }
     delete h;
     return PRICHS_OK;
 }
@@ -937,6 +956,7 @@ int prichs_moe_upload_weights(prichs_moe_t* h, const float* const* host_ptrs, in
     }
     cudaFree(stage);
     if (rc == PRICHS_OK) h->weights_ready = true;
+    h->bwd.nat_valid = false;
     return rc;
 }
 
@@ -975,6 +995,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     h->last_stream = st;
     h->last_T = T;
+    h->last_chunked = false;
     if (T == 0) {
         if (h->world > 1) return fail(PRICHS_ERR_BAD_SHAPE, "in expert-parallel mode every rank must pass at least one token");
         return PRICHS_OK;
@@ -1177,6 +1198,7 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     }
     h->last_T = T;
     h->last_stream = st;
+    h->last_chunked = nchunks > 1;
     cudaError_t e1 = cudaStreamSynchronize(h->in_stream), e2 = cudaStreamSynchronize(st), e3 = cudaStreamSynchronize(h->out_stream);
     if (rc != PRICHS_OK) return rc;
     if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
@@ -1342,6 +1364,245 @@ int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows) {
     CUDA_TRY(cudaMemcpy(&m, h->meta, sizeof(m), cudaMemcpyDeviceToHost));
     *rows = m.recv_rows;
     return PRICHS_OK;
+}
+
+// ---- backward pass ---------------------------------------------------------------------------------------
+namespace {
+
+int bwd_alloc(prichs_moe* h) {
+    prichs_moe::Bwd& b = h->bwd;
+    if (b.ready) return PRICHS_OK;
+    const size_t R = (size_t)h->Tcap + h->Rcap, d = h->d, f = h->f;
+    int rc = PRICHS_OK;
+    auto A = [&](int r) { if (rc == PRICHS_OK) rc = r; };
+    if (!b.gu) A(dalloc(&b.gu, R * 2 * f));
+    if (!b.dyall) A(dalloc(&b.dyall, R * d));
+    if (!b.dh) A(dalloc(&b.dh, R * f));
+    if (!b.dgu) A(dalloc(&b.dgu, R * 2 * f));
+    if (!b.dxall) A(dalloc(&b.dxall, R * d));
+    if (!b.xT) A(dalloc(&b.xT, d * R));
+    if (!b.hT) A(dalloc(&b.hT, f * R));
+    if (!b.dyT) A(dalloc(&b.dyT, d * R));
+    if (!b.dguT) A(dalloc(&b.dguT, 2 * f * R));
+    if (!b.w_dn_nat) A(dalloc(&b.w_dn_nat, (size_t)h->n_slots * f * d));
+    if (!b.w_gu_nat) A(dalloc(&b.w_gu_nat, (size_t)h->n_slots * d * 2 * f));
+    if (!b.scal) A(dalloc(&b.scal, (size_t)h->Tmax * 2));
+    if (!b.dlog) A(dalloc(&b.dlog, (size_t)h->Tmax * route::MAX_E));
+    if (!b.dwr_part) A(dalloc(&b.dwr_part, (size_t)bwd::DWR_SPLITS * d * route::MAX_E));
+    if (!b.stage_dn) A(dalloc(&b.stage_dn, f * d));
+    if (!b.stage_gu) A(dalloc(&b.stage_gu, d * 2 * f));
+    if (rc != PRICHS_OK) return rc;
+    // rows that no kernel of a backward pass writes (padding of the permuted region) must stay finite
+    CUDA_TRY(cudaMemset(b.dyall, 0, R * d * sizeof(bf16)));
+    CUDA_TRY(cudaMemset(b.gu, 0, R * 2 * f * sizeof(bf16)));
+    CUDA_TRY(cudaMemset(b.dh, 0, R * f * sizeof(bf16)));
+    CUDA_TRY(cudaMemset(b.dgu, 0, R * 2 * f * sizeof(bf16)));
+    CUDA_TRY(cudaMemset(b.dxall, 0, R * d * sizeof(bf16)));
+    A(make_tmap(&b.tm_dyall, b.dyall, R, d, egemm::BM));
+    A(make_tmap(&b.tm_dgu, b.dgu, R, 2 * f, egemm::BM));
+    A(make_tmap(&b.tm_gu_out, b.gu, R, 2 * f, 32));
+    A(make_tmap(&b.tm_dh_out, b.dh, R, f, 32));
+    A(make_tmap(&b.tm_dxall_out, b.dxall, R, d, 32));
+    A(make_tmap(&b.tm_wdn_nat, b.w_dn_nat, (size_t)h->n_slots * f, d, egemm::BN));
+    A(make_tmap(&b.tm_wgu_nat, b.w_gu_nat, (size_t)h->n_slots * d, 2 * f, egemm::BN));
+    A(make_tmap(&b.tm_stage_dn, b.stage_dn, f, d, 32, true));
+    A(make_tmap(&b.tm_stage_gu, b.stage_gu, d, 2 * f, 32, true));
+    if (rc == PRICHS_OK) b.ready = true;
+    return rc;
+}
+
+int bwd_transpose(const bf16* src, bf16* dst, long long rows, int cols, long long src_pitch, long long dst_pitch, cudaStream_t st) {
+    if (rows <= 0) return PRICHS_OK;
+    const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+    bwd::transpose_bf16_kernel<<<grid, 256, 0, st>>>(src, dst, rows, cols, src_pitch, dst_pitch);
+    LAUNCH_CHECK("transpose");
+    return PRICHS_OK;
+}
+
+// One launch of the one-CTA grouped GEMM with a plain epilogue.
+int bwd_gemm(prichs_moe* h, const CUtensorMap& tm_a_shared, const CUtensorMap& tm_a_routed, const CUtensorMap& tm_b,
+             const CUtensorMap& tm_out, const egemm::Args& a, cudaStream_t st, const char* what) {
+    LAUNCH_K(false, egemm::expert_gemm_kernel<egemm::EPI_PLAIN>, h->sm_count, egemm::NUM_THREADS, egemm::SMEM_BYTES, st, tm_a_shared,
+             tm_a_routed, tm_b, tm_out, a);
+    LAUNCH_CHECK(what);
+    return PRICHS_OK;
+}
+
+}  // namespace
+
+int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* dy_dev, int dy_dtype, float* dx_dev,
+                        float* const* grads_dev, int n_grads, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (h->world > 1) return fail(PRICHS_ERR_BAD_ARG, "the backward pass runs with all experts local (ep_world = 1)");
+    if (h->mode != PRICHS_MODE_BF16) return fail(PRICHS_ERR_BAD_ARG, "the backward pass runs in the bf16 mode");
+    if (h->f % 256 != 0) return fail(PRICHS_ERR_BAD_SHAPE, "the backward pass needs intermediate_dim to be a multiple of 256 (got %d)", h->f);
+    if (!x_dev || !dy_dev || !dx_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation or gradient pointer");
+    if ((x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) || (dy_dtype != PRICHS_DTYPE_F32 && dy_dtype != PRICHS_DTYPE_BF16))
+        return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    if (grads_dev && n_grads != 1 + 3 * (1 + h->E))
+        return fail(PRICHS_ERR_BAD_SHAPE, "expected %d gradient buffers (router, shared g/u/d, then g/u/d per expert), got %d", 1 + 3 * (1 + h->E), n_grads);
+    if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (reinterpret_cast<uintptr_t>(dy_dev) & 15) || (reinterpret_cast<uintptr_t>(dx_dev) & 15))
+        return fail(PRICHS_ERR_BAD_ARG, "activation and gradient pointers must be 16-byte aligned");
+    const int T = h->last_T;
+    if (T <= 0) return fail(PRICHS_ERR_BAD_ARG, "no forward pass to differentiate: call prichs_moe_forward first");
+    if (h->last_chunked) return fail(PRICHS_ERR_BAD_ARG, "the last forward went through host buffers in chunks; run prichs_moe_forward on device buffers before the backward pass");
+    DeviceGuard guard(h->device);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+    int rc = bwd_alloc(h);
+    if (rc != PRICHS_OK) return rc;
+    prichs_moe::Bwd& b = h->bwd;
+    const int d = h->d, f = h->f, E = h->E;
+    const long long tcap = h->Tcap;
+    const size_t R = (size_t)h->Tcap + h->Rcap;
+
+    // The forward's routing decides every size below: wait for it and read the placement.
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));
+    if (st != h->last_stream) CUDA_TRY(cudaStreamSynchronize(st));
+    route::RouteMeta meta;
+    CUDA_TRY(cudaMemcpy(&meta, h->meta, sizeof(meta), cudaMemcpyDeviceToHost));
+    if (meta.overflow) return fail(PRICHS_ERR_CAPACITY, "the forward pass overflowed its permuted region");
+    const long long routed_rows = 128LL * meta.n_routed_mtiles;
+
+    // un-transposed weight copies ([f,d] and [d,2f] per slot, K-major for the input-gradient products)
+    if (!b.nat_valid) {
+        for (int s = 0; s < h->n_slots; ++s) {
+            rc = bwd_transpose(h->w_dn + (size_t)s * d * h->K2, b.w_dn_nat + (size_t)s * f * d, d, f, h->K2, d, st);
+            if (rc != PRICHS_OK) return rc;
+            rc = bwd_transpose(h->w_gu + (size_t)s * 2 * f * h->K1, b.w_gu_nat + (size_t)s * d * 2 * f, 2 * f, d, h->K1, 2 * f, st);
+            if (rc != PRICHS_OK) return rc;
+        }
+        b.nat_valid = true;
+    }
+
+    // the layer input as the forward used it: the caller's bf16 rows, or the bf16 copy the router wrote
+    const bf16* a_shared = x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    CUtensorMap tm_x;
+    rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)d, egemm::BM);
+    if (rc != PRICHS_OK) return rc;
+
+    // 1. d_out into the forward's row space (gate-weighted for routed rows) + the router's scalars
+    if (dy_dtype == PRICHS_DTYPE_F32)
+        bwd::dy_prepare_kernel<true><<<(T + 7) / 8, 256, 0, st>>>(dy_dev, reinterpret_cast<const bf16*>(h->ybuf), h->sel, h->gates, h->pos, b.dyall, b.scal, T, d, tcap);
+    else
+        bwd::dy_prepare_kernel<false><<<(T + 7) / 8, 256, 0, st>>>(dy_dev, reinterpret_cast<const bf16*>(h->ybuf), h->sel, h->gates, h->pos, b.dyall, b.scal, T, d, tcap);
+    LAUNCH_CHECK("d_out preparation");
+
+    egemm::Args base;
+    memset(&base, 0, sizeof(base));
+    base.shared_mtiles = (T + 127) / 128;
+    base.routed_base_tiles = h->Tcap / 128;
+    base.n_routed_mtiles = &h->meta->n_routed_mtiles;
+    base.mtile_slot = h->mtile_slot;
+    base.status = h->status;
+
+    // 2. pre-activations again: [gate | up] = x . W_gu (the forward keeps only silu(gate) * up)
+    {
+        egemm::Args a = base;
+        a.nk = d / egemm::BK;
+        a.n_ntiles = 2 * f / egemm::BN;
+        a.a_routed_tile_off = 0;
+        a.w_rows = 2 * f;
+        rc = bwd_gemm(h, tm_x, h->tm_xp, h->tm_wgu, b.tm_gu_out, a, st, "pre-activation GEMM");
+        if (rc != PRICHS_OK) return rc;
+    }
+    // 3. d_act = dY . W_down^T   (model.rs:580-588, 672-680)
+    {
+        egemm::Args a = base;
+        a.nk = d / egemm::BK;
+        a.n_ntiles = f / egemm::BN;
+        a.a_routed_tile_off = h->Tcap / 128;
+        a.w_rows = f;
+        rc = bwd_gemm(h, b.tm_dyall, b.tm_dyall, b.tm_wdn_nat, b.tm_dh_out, a, st, "d_act GEMM");
+        if (rc != PRICHS_OK) return rc;
+    }
+    // 4. SwiGLU backward
+    bwd::swiglu_bwd_kernel<<<4 * h->sm_count, 256, 0, st>>>(b.dh, b.gu, b.dgu, T, f, tcap, &h->meta->n_routed_mtiles);
+    LAUNCH_CHECK("SwiGLU backward");
+    // 5. dX = d_gate . W_gate^T + d_up . W_up^T as one product over K = 2f   (model.rs:612-631, 702-722)
+    {
+        egemm::Args a = base;
+        a.nk = 2 * f / egemm::BK;
+        a.n_ntiles = d / egemm::BN;
+        a.a_routed_tile_off = h->Tcap / 128;
+        a.w_rows = d;
+        rc = bwd_gemm(h, b.tm_dgu, b.tm_dgu, b.tm_wgu_nat, b.tm_dxall_out, a, st, "dX GEMM");
+        if (rc != PRICHS_OK) return rc;
+    }
+    // 6. router VJP, 7. d_x
+    bwd::router_vjp_kernel<<<(T + 255) / 256, 256, 0, st>>>(h->sel, h->gates, b.scal, b.dlog, T);
+    LAUNCH_CHECK("router VJP");
+    bwd::dx_combine_kernel<<<(T + 7) / 8, 256, 0, st>>>(b.dxall, h->sel, h->gates, h->pos, b.dlog, h->w_r8, dx_dev, T, d, tcap);
+    LAUNCH_CHECK("d_x combine");
+    if (!grads_dev) {
+        CUDA_TRY(cudaStreamSynchronize(st));
+        return prichs_moe_sync_status(h);
+    }
+
+    // 8. dW_router += X^T d_logits
+    if (grads_dev[0]) {
+        bwd::dwr_partial_kernel<<<dim3(d / 64, bwd::DWR_SPLITS), 512, 0, st>>>(a_shared, b.dlog, b.dwr_part, T, d);
+        LAUNCH_CHECK("router weight gradient (partial sums)");
+        bwd::dwr_reduce_kernel<<<(d * route::MAX_E + 255) / 256, 256, 0, st>>>(b.dwr_part, grads_dev[0], d, E);
+        LAUNCH_CHECK("router weight gradient");
+    }
+
+    // 9. transposed copies: the weight-gradient products contract over rows
+    rc = bwd_transpose(a_shared, b.xT, T, d, d, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(h->xp, b.xT + tcap, routed_rows, d, h->K1, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(h->hbuf, b.hT, T, f, h->K2, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(h->hbuf + (size_t)tcap * h->K2, b.hT + tcap, routed_rows, f, h->K2, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(b.dyall, b.dyT, T, d, d, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(b.dyall + (size_t)tcap * d, b.dyT + tcap, routed_rows, d, d, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(b.dgu, b.dguT, T, 2 * f, 2 * f, R, st);
+    if (rc == PRICHS_OK) rc = bwd_transpose(b.dgu + (size_t)tcap * 2 * f, b.dguT + tcap, routed_rows, 2 * f, 2 * f, R, st);
+    if (rc != PRICHS_OK) return rc;
+
+    // 10. weight gradients, one expert at a time: its rows are the K window [k0, k0 + n) of the transposed copies
+    //     (columns beyond n read as zero through the tensor map's bounds)
+    for (int slot = 0; slot < h->n_slots; ++slot) {
+        const int e = slot - 1;
+        const long long k0 = slot == 0 ? 0 : tcap + meta.seg_base[e];
+        const int n = slot == 0 ? T : meta.counts[e];
+        float* gg = grads_dev[1 + 3 * slot];
+        float* gu_ = grads_dev[2 + 3 * slot];
+        float* gd = grads_dev[3 + 3 * slot];
+        if (n <= 0 || (!gg && !gu_ && !gd)) continue;  // an expert without tokens gets no gradient (model.rs:641-643)
+        egemm::Args a;
+        memset(&a, 0, sizeof(a));
+        a.nk = (n + egemm::BK - 1) / egemm::BK;
+        a.n_routed_mtiles = h->ep_zero;
+        a.mtile_slot = h->mtile_slot;
+        a.out_f32 = 1;
+        a.status = h->status;
+        CUtensorMap tm_a, tm_b;
+        if (gd) {
+            // dW_down [f, d] = act^T . dY   (model.rs:572-579, 662-670)
+            rc = make_tmap(&tm_a, b.hT + k0, f, (size_t)n, egemm::BM, false, R);
+            if (rc == PRICHS_OK) rc = make_tmap(&tm_b, b.dyT + k0, d, (size_t)n, egemm::BN, false, R);
+            if (rc != PRICHS_OK) return rc;
+            a.shared_mtiles = f / egemm::BM;
+            a.n_ntiles = d / egemm::BN;
+            rc = bwd_gemm(h, tm_a, tm_a, tm_b, b.tm_stage_dn, a, st, "down-projection weight gradient");
+            if (rc != PRICHS_OK) return rc;
+            bwd::grad_accumulate_kernel<<<2 * h->sm_count, 256, 0, st>>>(b.stage_dn, gd, (size_t)f * d);
+            LAUNCH_CHECK("down-projection gradient accumulation");
+        }
+        if (gg || gu_) {
+            // dW_gate, dW_up [d, f] = x^T . d_gate, x^T . d_up as one product with N = 2f   (model.rs:600-611, 690-700)
+            rc = make_tmap(&tm_a, b.xT + k0, d, (size_t)n, egemm::BM, false, R);
+            if (rc == PRICHS_OK) rc = make_tmap(&tm_b, b.dguT + k0, 2 * f, (size_t)n, egemm::BN, false, R);
+            if (rc != PRICHS_OK) return rc;
+            a.shared_mtiles = d / egemm::BM;
+            a.n_ntiles = 2 * f / egemm::BN;
+            rc = bwd_gemm(h, tm_a, tm_a, tm_b, b.tm_stage_gu, a, st, "gate/up weight gradient");
+            if (rc != PRICHS_OK) return rc;
+            bwd::grad_unpack_gate_up_kernel<<<4 * h->sm_count, 256, 0, st>>>(b.stage_gu, gg, gu_, d, f);
+            LAUNCH_CHECK("gate/up gradient accumulation");
+        }
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    h->last_stream = st;
+    return prichs_moe_sync_status(h);
 }
 
 int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes) {

@@ -261,6 +261,36 @@ class MoELayer:
         self._T_last = T
         return y
 
+    def backward(self, x, d_out, grads=None, stream=None):
+        """MoE section of the reference's block backward pass (crates/prichs-model/src/model.rs:566-766) for the last
+        forward of this layer. `x` is that forward's input and `d_out` the gradient of its output, CUDA torch tensors
+        [T, hidden_dim] (fp32 or bf16). Returns d_x [T, hidden_dim] fp32. `grads`: list of 1 + 3 * (1 + E) CUDA fp32
+        tensors (or None entries) in the order and layouts of the weights; the gradients are added to them."""
+        import torch
+        if not (isinstance(x, torch.Tensor) and x.is_cuda and isinstance(d_out, torch.Tensor) and d_out.is_cuda):
+            raise PrichsError(_capi.ERR_BAD_ARG, "x and d_out must be CUDA tensors")
+        if x.dim() != 2 or x.shape[1] != self.hidden_dim or tuple(d_out.shape) != tuple(x.shape):
+            raise PrichsError(_capi.ERR_BAD_SHAPE, "x and d_out must both be [T, hidden_dim]")
+        if not self._h or x.shape[0] != self._T_last:
+            raise PrichsError(_capi.ERR_BAD_ARG, "backward needs the forward of the same batch to have run last")
+        dts = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
+        x, d_out = x.contiguous(), d_out.contiguous()
+        dx = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        n = 1 + 3 * (1 + self._num_experts)
+        if grads is not None:
+            if len(grads) != n:
+                raise PrichsError(_capi.ERR_BAD_SHAPE, f"expected {n} gradient buffers, got {len(grads)}")
+            for g in grads:
+                if g is not None and not (g.is_cuda and g.dtype == torch.float32 and g.is_contiguous()):
+                    raise PrichsError(_capi.ERR_BAD_ARG, "gradient buffers must be contiguous CUDA fp32 tensors")
+            arr = (C.c_void_p * n)(*[C.c_void_p(g.data_ptr()) if g is not None else C.c_void_p(0) for g in grads])
+        else:
+            arr = None
+        st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
+        _check(_capi.lib().prichs_moe_backward(self._h, x.data_ptr(), dts[x.dtype], d_out.data_ptr(), dts[d_out.dtype], dx.data_ptr(),
+                                               arr, n if grads is not None else 0, st))
+        return dx
+
     def forward_train(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, **kw):
         out = self.forward_with_memory(x, starkdb_concept_bias, **kw)
         return out, self.last_stash()
