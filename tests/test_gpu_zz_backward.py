@@ -18,6 +18,13 @@ pytestmark = [pytest.mark.gpu,
 TOL = 3e-2  # bf16 operands, fp32 accumulation, two chained products
 
 
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a GPU"
+    return torch
+
+
 def _run(torch, oracle, seed, T, d, f, E, k, bias=None, x_kind="bf16", dy_kind="f32"):
     from prichs_b200 import MoELayer, synth
     ws = synth.layer_weights(seed, d, f, E, std=0.05, bf16=True)
