@@ -379,6 +379,36 @@ void oracle_moe_router_unbiased_backward(const float* d_expert_weights, const fl
     }
 }
 
+// rmsnorm_backward (backward.rs:94-131): per row, sum of squares and dot(d_out * gamma, x) in index order, then
+//   d_gamma[i] += d_out[i] * x[i] * rms_inv,   d_x[i] += gamma[i] * rms_inv * (d_out[i] - x[i] * coeff),
+//   coeff = (dot / d) * rms_inv^2.  Both outputs ACCUMULATE: the caller seeds d_x with the gradient that reaches the
+// residual connection (model.rs:777-789: d_x_res starts as a clone of the block's output gradient). Rows in order on
+// one thread, as in the reference (d_gamma is shared between rows). Note: the x-term of d_x carries gamma[i], which
+// the gradient of x * rms_inv * gamma does not (it is -x[i] * coeff * rms_inv); the two agree for gamma = 1, the
+// reference's initial norm weight. Restated as the reference computes it.
+void oracle_rmsnorm_backward(const float* d_out, const float* x, const float* gamma, float* d_x, float* d_gamma,
+                             size_t rows, size_t d_model, float eps) {
+    const float inv_d = 1.0f / (float)d_model;
+    for (size_t t = 0; t < rows; ++t) {
+        const float* x_row = x + t * d_model;
+        const float* dout_row = d_out + t * d_model;
+        float* dx_row = d_x + t * d_model;
+        float sum_sq = 0.0f, dot_dout_gamma_x = 0.0f;
+        for (size_t i = 0; i < d_model; ++i) {
+            const float xi = x_row[i];
+            sum_sq += xi * xi;
+            dot_dout_gamma_x += dout_row[i] * gamma[i] * xi;
+        }
+        const float rms_inv = 1.0f / std::sqrt(sum_sq * inv_d + eps);
+        const float coeff = (dot_dout_gamma_x * inv_d) * (rms_inv * rms_inv);
+        for (size_t i = 0; i < d_model; ++i) {
+            const float xi = x_row[i], di = dout_row[i];
+            d_gamma[i] += di * xi * rms_inv;
+            dx_row[i] += gamma[i] * rms_inv * (di - xi * coeff);
+        }
+    }
+}
+
 // MoE part of the backward pass of one block (model.rs:566-766), for a layer input x [T,d] (`normed2` there) and
 // the gradient d_out [T,d] of the layer's output (`d_moe`). The forward stashes (moe.rs:103-111,166-175,186-208)
 // are recomputed here with the same arithmetic as oracle_moe_forward_train.

@@ -54,6 +54,7 @@ def lib():
         L.oracle_moe_router_unbiased_backward.argtypes = [fp, fp, zp, sz, fp, sz]
         L.oracle_moe_backward.argtypes = [C.POINTER(fp), fp, sz, sz, sz, sz, fp, sz, fp, sz, fp, C.POINTER(fp), fp]
         L.oracle_moe_backward.restype = C.c_int
+        L.oracle_rmsnorm_backward.argtypes = [fp, fp, fp, fp, fp, sz, sz, C.c_float]
         _lib = L
     return _lib
 
@@ -251,4 +252,19 @@ def moe_backward(weights, router_bias, top_k, x, d_out, concept_bias=None, grads
     if rc != 0:
         raise ValueError("k must be <= logits length")
     return dict(d_x=dx, grads=gs)
+
+
+def rmsnorm_backward(d_out, x, gamma, eps, d_x=None, d_gamma=None):
+    """backward.rs:94-131. Returns (d_x, d_gamma); both ACCUMULATE into the arrays given (zeros otherwise): the
+    reference seeds d_x with the gradient that flows through the residual connection (model.rs:777-789)."""
+    dy, pdy = _f(d_out)
+    x, px = _f(x)
+    g, pg = _f(gamma)
+    rows, d = x.shape
+    assert dy.shape == x.shape and g.size == d
+    dx = np.zeros((rows, d), np.float32) if d_x is None else np.array(d_x, dtype=np.float32, copy=True)
+    dg = np.zeros(d, np.float32) if d_gamma is None else np.array(d_gamma, dtype=np.float32, copy=True)
+    fp = C.POINTER(C.c_float)
+    lib().oracle_rmsnorm_backward(pdy, px, pg, dx.ctypes.data_as(fp), dg.ctypes.data_as(fp), rows, d, C.c_float(eps))
+    return dx, dg
 

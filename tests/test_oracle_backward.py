@@ -310,3 +310,53 @@ def test_gpu_decomposition_of_the_backward_pass_equals_the_oracle(oracle):
     np.testing.assert_allclose(dx, ref["d_x"], rtol=2e-3, atol=2e-4)
     for i, (g, r) in enumerate(zip(grads, ref["grads"])):
         np.testing.assert_allclose(g, r, rtol=2e-3, atol=2e-4, err_msg=f"gradient {i}")
+
+
+def test_rmsnorm_backward_matches_float64_central_differences(oracle):
+    """backward.rs:94-131 against numeric gradients of y = x / sqrt(mean(x^2) + eps) * gamma, and its accumulate-into
+    behaviour (the residual path seeds d_x, model.rs:777-789). With gamma = 1 (the reference's initial norm weight) the
+    reference's d_x is the true gradient; for other gamma its second term carries gamma once too often
+    (gamma_j * r * (d_j - x_j * coeff) instead of gamma_j * r * d_j - x_j * coeff * r): restated as the reference
+    computes it, so the general case is checked against that closed form and shown to differ from the true gradient.
+    d_gamma is the true gradient in both cases."""
+    rows, d, eps = 5, 12, 1e-5
+    x = synth.normal(120, 0, (rows, d)).astype(np.float32)
+    R = synth.normal(122, 0, (rows, d)).astype(np.float32)
+    x64, R64 = x.astype(np.float64), R.astype(np.float64)
+    f64 = lambda xx, gg: float((xx / np.sqrt((xx ** 2).mean(axis=1, keepdims=True) + eps) * gg * R64).sum())
+
+    def numeric(g64):
+        h = 1e-6
+        ndx = np.zeros((rows, d))
+        for i in range(rows):
+            for j in range(d):
+                a = x64.copy(); a[i, j] += h
+                b = x64.copy(); b[i, j] -= h
+                ndx[i, j] = (f64(a, g64) - f64(b, g64)) / (2 * h)
+        ndg = np.zeros(d)
+        for j in range(d):
+            a = g64.copy(); a[j] += h
+            b = g64.copy(); b[j] -= h
+            ndg[j] = (f64(x64, a) - f64(x64, b)) / (2 * h)
+        return ndx, ndg
+
+    ones = np.ones(d, np.float32)
+    dx, dg = oracle.rmsnorm_backward(R, x, ones, eps)
+    ndx, ndg = numeric(ones.astype(np.float64))
+    np.testing.assert_allclose(dx, ndx, rtol=2e-3, atol=2e-4)
+    np.testing.assert_allclose(dg, ndg, rtol=2e-3, atol=2e-4)
+
+    gamma = (1.0 + 0.2 * synth.normal(121, 0, (d,))).astype(np.float32)
+    g64 = gamma.astype(np.float64)
+    dx, dg = oracle.rmsnorm_backward(R, x, gamma, eps)
+    ndx, ndg = numeric(g64)
+    np.testing.assert_allclose(dg, ndg, rtol=2e-3, atol=2e-4)
+    r = 1.0 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + eps)
+    coeff = ((R64 * g64 * x64).sum(axis=1, keepdims=True) / d) * r * r
+    np.testing.assert_allclose(dx, g64 * r * (R64 - x64 * coeff), rtol=1e-4, atol=1e-5)
+    assert np.abs(dx - ndx).max() > 1e-2  # not the true gradient once gamma differs from 1
+
+    seed_dx = synth.normal(123, 0, (rows, d)).astype(np.float32)
+    dx2, dg2 = oracle.rmsnorm_backward(R, x, gamma, eps, d_x=seed_dx, d_gamma=np.ones(d, np.float32))
+    np.testing.assert_allclose(dx2, seed_dx + dx, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(dg2, 1.0 + dg, rtol=1e-5, atol=1e-6)
