@@ -232,7 +232,10 @@ PRICHS_API int prichs_moe_get_ep_timeline(prichs_moe_t* h, float* ms, int n);
  *          5 routing summary (struct of ints: counts[8], seg_base[8], src_off[8], total[8], n_mtiles,
  *            recv_rows, overflow, pad, cmat[64])   6 per-tile histograms [ceil(T/16),8] int32
  *          7 their exclusive prefix sums           8 m-tile -> weight slot table int32
- *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 128. */
+ *          after prichs_moe_backward, in the same row space: 9 recomputed [gate | up] [Tcap+Rcap,2f] bf16 (blocks of
+ *          128 gate then 128 up columns)   10 dY rows [.,d] bf16   11 d_act [.,f] bf16   12 [d_gate | d_up] [.,2f] bf16
+ *          13 dX rows [.,d] bf16   14 <expert row, d_out> [T,2] fp32   15 d_logits [T,8] fp32
+ *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 256. */
 PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes);
 
 /* ---- routing without any allocation ---------------------------------------------------------------

@@ -1622,8 +1622,17 @@ int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void*
         case 6: base = h->tile_counts; size = ntiles * route::MAX_E * 4; break;
         case 7: base = h->tile_prefix; size = ntiles * route::MAX_E * 4; break;
         case 8: base = h->mtile_slot; size = ((size_t)h->Rcap / 128 + 1) * 4; break;
+        // intermediates of the last backward pass (null until prichs_moe_backward has run)
+        case 9: base = h->bwd.gu; size = rows_all * 2 * h->f * 2; break;
+        case 10: base = h->bwd.dyall; size = rows_all * h->d * 2; break;
+        case 11: base = h->bwd.dh; size = rows_all * h->f * 2; break;
+        case 12: base = h->bwd.dgu; size = rows_all * 2 * h->f * 2; break;
+        case 13: base = h->bwd.dxall; size = rows_all * h->d * 2; break;
+        case 14: base = h->bwd.scal; size = (size_t)h->Tmax * 2 * 4; break;
+        case 15: base = h->bwd.dlog; size = (size_t)h->Tmax * route::MAX_E * 4; break;
         default: return fail(PRICHS_ERR_BAD_ARG, "unknown buffer id %d", which);
     }
+    if (!base) return fail(PRICHS_ERR_BAD_ARG, "buffer %d does not exist yet (no backward pass has run)", which);
     if (offset_bytes > size || bytes > size - offset_bytes) return fail(PRICHS_ERR_BAD_SHAPE, "range exceeds the buffer (%zu bytes)", size);
     CUDA_TRY(cudaStreamSynchronize(h->last_stream));
     CUDA_TRY(cudaMemcpy(host_dst, static_cast<const char*>(base) + offset_bytes, bytes, cudaMemcpyDeviceToHost));

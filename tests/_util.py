@@ -104,3 +104,104 @@ def golden_small_inputs():
     bias = grid_tensor(11, 1000, (E,), 4, 32)
     cb = np.array([0.25, -0.125, 0.0], np.float32)
     return dict(ws=ws, x=x, bias=bias, concept_bias=cb, top_k=k)
+
+
+def np_backward_decomposed(ws, x, R, sel, gates, counts, pad=256):
+    """fp32 numpy model of the steps prichs_moe_backward performs, in its row space: shared rows [0,T), permuted row
+    Tcap + pos; [gate | up] in blocks of 256 columns (128 gate then 128 up of the same hidden units). Returns the
+    intermediates (gu, hall, yall, dyall, scal, dh, dgu, dxall, dlog), the row map (Tcap, seg_base, pos, live rows) and
+    the results (dx, grads in the order of `ws`)."""
+    T, d = x.shape
+    E = ws[0].shape[1]
+    f = ws[1].shape[1]
+    k = sel.shape[1]
+    seg_base = np.zeros(E, np.int64)
+    for e in range(1, E):
+        seg_base[e] = seg_base[e - 1] + (counts[e - 1] + pad - 1) // pad * pad
+    Tcap = (T + pad - 1) // pad * pad
+    Rtot = Tcap + int(seg_base[-1] + (counts[-1] + pad - 1) // pad * pad)
+    pos = np.full((T, k), -1, np.int64)
+    fill = np.zeros(E, np.int64)
+    row_expert = np.full(Rtot, -1, np.int64)
+    for t in range(T):
+        for j in range(k):
+            e = sel[t, j]
+            pos[t, j] = seg_base[e] + fill[e]
+            row_expert[Tcap + pos[t, j]] = e
+            fill[e] += 1
+    row_expert[:T] = -2  # shared expert
+
+    def blocked(wg, wu):
+        out = np.zeros((d, 2 * f), np.float32)
+        for b in range(f // 128):
+            out[:, 256 * b:256 * b + 128] = wg[:, 128 * b:128 * b + 128]
+            out[:, 256 * b + 128:256 * b + 256] = wu[:, 128 * b:128 * b + 128]
+        return out
+
+    wgu = [blocked(ws[1 + 3 * s], ws[2 + 3 * s]) for s in range(1 + E)]  # slot 0 = shared
+    wdn = [ws[3 + 3 * s] for s in range(1 + E)]
+    slot_of_row = np.where(row_expert == -2, 0, row_expert + 1)
+    silu = lambda g: g / (1.0 + np.exp(-g))
+
+    xall = np.zeros((Rtot, d), np.float32)
+    xall[:T] = x
+    for t in range(T):
+        for j in range(k):
+            xall[Tcap + pos[t, j]] = x[t]
+    live = np.where(row_expert != -1)[0]
+    gu = np.zeros((Rtot, 2 * f), np.float32)
+    hall = np.zeros((Rtot, f), np.float32)
+    yall = np.zeros((Rtot, d), np.float32)
+    for r in live:
+        s = slot_of_row[r]
+        gu[r] = xall[r] @ wgu[s]
+        gb = gu[r].reshape(-1, 256)
+        hall[r] = (silu(gb[:, :128]) * gb[:, 128:]).reshape(-1)
+        yall[r] = hall[r] @ wdn[s]
+    # 1. d_out into the row space + the router's scalars
+    dyall = np.zeros((Rtot, d), np.float32)
+    dyall[:T] = R
+    scal = np.zeros((T, k), np.float32)
+    for t in range(T):
+        for j in range(k):
+            r = Tcap + pos[t, j]
+            dyall[r] = gates[t, j] * R[t]
+            scal[t, j] = yall[r] @ R[t]
+    # 3. d_act, 4. SwiGLU backward in the blocked order, 5. dX over K = 2f
+    dh = np.zeros((Rtot, f), np.float32)
+    dgu = np.zeros_like(gu)
+    dxall = np.zeros((Rtot, d), np.float32)
+    for r in live:
+        s = slot_of_row[r]
+        dh[r] = dyall[r] @ wdn[s].T
+        gb = gu[r].reshape(-1, 256)
+        g, u = gb[:, :128], gb[:, 128:]
+        dhb = dh[r].reshape(-1, 128)
+        sig = 1.0 / (1.0 + np.exp(-g))
+        dgu[r] = np.concatenate([dhb * u * (sig * (1.0 + g * (1.0 - sig))), dhb * (g * sig)], axis=1).reshape(-1)
+        dxall[r] = dgu[r] @ wgu[s].T
+    # 6. router VJP, 7. d_x: shared + experts ascending (gate weight once more, as the reference) + router
+    dlog = np.zeros((T, E), np.float32)
+    for t in range(T):
+        weighted = float((gates[t] * scal[t]).sum())
+        for j in range(k):
+            dlog[t, sel[t, j]] = gates[t, j] * (scal[t, j] - weighted)
+    dx = dxall[:T].copy()
+    for t in range(T):
+        for j in np.argsort(sel[t]):
+            dx[t] += gates[t, j] * dxall[Tcap + pos[t, j]]
+    dx += dlog @ ws[0].T
+    # 8./10. weight gradients: router, then per slot a K window of the transposed copies
+    grads = [np.zeros_like(w) for w in ws]
+    grads[0] = x.T @ dlog
+    xT, hT, dyT, dguT = xall.T, hall.T, dyall.T, dgu.T
+    for s in range(1 + E):
+        k0, n = (0, T) if s == 0 else (Tcap + int(seg_base[s - 1]), int(counts[s - 1]))
+        if n == 0:
+            continue
+        grads[3 + 3 * s] = hT[:, k0:k0 + n] @ dyT[:, k0:k0 + n].T
+        sb = (xT[:, k0:k0 + n] @ dguT[:, k0:k0 + n].T).reshape(d, -1, 256)  # [d, 2f], blocked columns
+        grads[1 + 3 * s] = sb[:, :, :128].reshape(d, f)
+        grads[2 + 3 * s] = sb[:, :, 128:].reshape(d, f)
+    return dict(Tcap=Tcap, seg_base=seg_base, pos=pos, live=live, gu=gu, hall=hall, yall=yall, dyall=dyall, scal=scal, dh=dh,
+                dgu=dgu, dxall=dxall, dlog=dlog, dx=dx, grads=grads)

@@ -50,6 +50,47 @@ def _rel(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b) / (np.linalg.norm(b.astype(np.float64)) + 1e-30))
 
 
+def test_backward_intermediates_stage_by_stage(torch_cuda, oracle):
+    """Every intermediate of the backward pass against the numpy model of its decomposition, in execution order, so
+    that a wrong kernel shows up at its own stage: recomputed [gate | up], dY rows, scalars, d_act, [d_gate | d_up],
+    dX rows, d_logits."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    from _util import np_backward_decomposed
+    T, d, f, E, k = 200, 256, 256, 8, 2
+    ws = synth.layer_weights(231, d, f, E, std=0.05, bf16=True)
+    bias = synth.router_bias(231, E, -0.1, 0.1)
+    x = synth.round_bf16(synth.normal(232, 0, (T, d)))
+    R = synth.round_bf16(synth.normal(233, 0, (T, d)))
+    m = MoELayer.from_weights(ws, k, mode="bf16")
+    m.router_bias = bias
+    xd = torch.from_numpy(x).cuda().bfloat16()
+    m.forward(xd)
+    st = m.last_stash()
+    sel = st.selected_experts.reshape(T, k).astype(np.int64)
+    gates = st.gating_weights.reshape(T, k).astype(np.float32)
+    dx = m.backward(xd, torch.from_numpy(R).cuda(), [torch.zeros(w.shape, device="cuda") for w in ws]).cpu().numpy()
+    m.sync_status()
+    model = np_backward_decomposed(ws, x, R, sel, gates, st.expert_token_counts.astype(np.int64))
+    pos = m.debug_buffer(4, T * 2 * 4).view(np.int32).reshape(T, 2)
+    assert np.array_equal(pos, model["pos"]), "row map of the forward"
+    live = model["live"]
+    rows = int(live.max()) + 1
+
+    def bf(which, width):
+        return synth.from_bf16_bits(m.debug_buffer(which, rows * width * 2).view(np.uint16)).reshape(rows, width)
+
+    for which, width, key in ((9, 2 * f, "gu"), (10, d, "dyall")):
+        assert_close(bf(which, width)[live], model[key][live], TOL, key)
+    scal = m.debug_buffer(14, T * 2 * 4).view(np.float32).reshape(T, 2)
+    assert_close(scal, model["scal"], TOL, "scalars <expert row, d_out>")
+    for which, width, key in ((11, f, "dh"), (12, 2 * f, "dgu"), (13, d, "dxall")):
+        assert_close(bf(which, width)[live], model[key][live], TOL, key)
+    dlog = m.debug_buffer(15, T * 8 * 4).view(np.float32).reshape(T, 8)[:, :E]
+    assert_close(dlog, model["dlog"], TOL, "d_logits")
+    assert_close(dx, model["dx"], TOL, "d_x")
+
+
 def test_backward_matches_oracle(torch_cuda, oracle):
     import torch
     T, d, f, E, k = 300, 512, 256, 8, 2

@@ -201,114 +201,21 @@ def test_gpu_decomposition_of_the_backward_pass_equals_the_oracle(oracle):
     """The CUDA backward (prichs_moe_backward) does not follow the reference expert by expert: it works in the forward's
     row space (shared rows [0,T), permuted rows in per-expert segments padded to 256), recomputes [gate | up] with the
     blocked column order of the forward's first GEMM (128 gate then 128 up columns per 256), runs three grouped
-    products over all rows, and takes each expert's weight gradients from a window of transposed copies. This numpy
-    model performs exactly those steps in fp32 and must agree with the oracle; it pins the decomposition (row maps,
-    column orders, the double gate weight, the order of the d_x sum) independently of the kernels."""
-    d, f, E, k, T, PAD = 16, 256, 4, 2, 37, 256
+    products over all rows, and takes each expert's weight gradients from a window of transposed copies. The numpy
+    model of exactly those steps (tests/_util.py: np_backward_decomposed) must agree with the oracle; it pins the
+    decomposition (row maps, column orders, the double gate weight, the order of the d_x sum) independently of the
+    kernels, and the GPU tests compare the kernels' intermediates against the same model."""
+    from _util import np_backward_decomposed
+    d, f, E, k, T = 16, 256, 4, 2, 37
     ws = _layer(110, d, f, E, std=0.2)
     bias = synth.router_bias(110, E, -0.1, 0.1)
     x = synth.normal(111, 0, (T, d)).astype(np.float32)
     R = synth.normal(112, 0, (T, d)).astype(np.float32)
     fwd = oracle.moe_forward_train(ws, bias, k, x)
-    sel, gates, counts = fwd["selected"], fwd["gating"], fwd["counts"]
-
-    # placement of the forward: segments padded to PAD rows, tokens ascending inside a segment
-    seg_base = np.zeros(E, np.int64)
-    for e in range(1, E):
-        seg_base[e] = seg_base[e - 1] + (counts[e - 1] + PAD - 1) // PAD * PAD
-    Tcap = (T + PAD - 1) // PAD * PAD
-    Rtot = Tcap + int(seg_base[-1] + (counts[-1] + PAD - 1) // PAD * PAD)
-    pos = np.full((T, k), -1, np.int64)
-    fill = np.zeros(E, np.int64)
-    row_expert = np.full(Rtot, -1, np.int64)
-    for t in range(T):
-        for j in range(k):
-            e = sel[t, j]
-            pos[t, j] = seg_base[e] + fill[e]
-            row_expert[Tcap + pos[t, j]] = e
-            fill[e] += 1
-    row_expert[:T] = -2  # shared expert
-
-    # blocked column order of the first GEMM: block b holds gate units [128b, 128b+128) then the same up units
-    def blocked(wg, wu):
-        out = np.zeros((d, 2 * f), np.float32)
-        for b in range(f // 128):
-            out[:, 256 * b:256 * b + 128] = wg[:, 128 * b:128 * b + 128]
-            out[:, 256 * b + 128:256 * b + 256] = wu[:, 128 * b:128 * b + 128]
-        return out
-
-    wgu = [blocked(ws[1 + 3 * s], ws[2 + 3 * s]) for s in range(1 + E)]   # slot 0 = shared
-    wdn = [ws[3 + 3 * s] for s in range(1 + E)]
-    slot_of_row = np.where(row_expert == -2, 0, row_expert + 1)
-
-    xall = np.zeros((Rtot, d), np.float32)
-    xall[:T] = x
-    dyall = np.zeros((Rtot, d), np.float32)
-    dyall[:T] = R
-    yall = np.zeros((Rtot, d), np.float32)
-    silu = lambda g: g / (1.0 + np.exp(-g))
-    for t in range(T):
-        for j in range(k):
-            xall[Tcap + pos[t, j]] = x[t]
-    live = np.where(row_expert != -1)[0]
-    gu = np.zeros((Rtot, 2 * f), np.float32)
-    hall = np.zeros((Rtot, f), np.float32)
-    for r in live:
-        s = slot_of_row[r]
-        gu[r] = xall[r] @ wgu[s]
-        g = gu[r].reshape(-1, 256)[:, :128].reshape(-1)
-        u = gu[r].reshape(-1, 256)[:, 128:].reshape(-1)
-        hall[r] = silu(g) * u
-        yall[r] = hall[r] @ wdn[s]
-    # 1. d_out into the row space + scalars
-    scal = np.zeros((T, k), np.float32)
-    for t in range(T):
-        for j in range(k):
-            r = Tcap + pos[t, j]
-            dyall[r] = gates[t, j] * R[t]
-            scal[t, j] = yall[r] @ R[t]
-    # 3. d_act, 4. SwiGLU backward in the blocked order, 5. dX over K = 2f
-    dgu = np.zeros_like(gu)
-    dxall = np.zeros((Rtot, d), np.float32)
-    for r in live:
-        s = slot_of_row[r]
-        dh = dyall[r] @ wdn[s].T
-        gb = gu[r].reshape(-1, 256)
-        g, u = gb[:, :128], gb[:, 128:]
-        dhb = dh.reshape(-1, 128)
-        sig = 1.0 / (1.0 + np.exp(-g))
-        dg = dhb * u * (sig * (1.0 + g * (1.0 - sig)))
-        du = dhb * (g * sig)
-        dgu[r] = np.concatenate([dg, du], axis=1).reshape(-1)
-        dxall[r] = dgu[r] @ wgu[s].T
-    # 6. router VJP, 7. d_x: shared + experts ascending (gate weight once more) + router
-    dlog = np.zeros((T, E), np.float32)
-    for t in range(T):
-        weighted = float((gates[t] * scal[t]).sum())
-        for j in range(k):
-            dlog[t, sel[t, j]] = gates[t, j] * (scal[t, j] - weighted)
-    dx = dxall[:T].copy()
-    for t in range(T):
-        for j in np.argsort(sel[t]):
-            dx[t] += gates[t, j] * dxall[Tcap + pos[t, j]]
-    dx += dlog @ ws[0].T
-    # 8./10. weight gradients: router, then per slot a K window of the transposed copies
-    grads = [np.zeros_like(w) for w in ws]
-    grads[0] = x.T @ dlog
-    xT, hT, dyT, dguT = xall.T, hall.T, dyall.T, dgu.T
-    for s in range(1 + E):
-        k0, n = (0, T) if s == 0 else (Tcap + int(seg_base[s - 1]), int(counts[s - 1]))
-        if n == 0:
-            continue
-        grads[3 + 3 * s] = hT[:, k0:k0 + n] @ dyT[:, k0:k0 + n].T
-        stage = xT[:, k0:k0 + n] @ dguT[:, k0:k0 + n].T           # [d, 2f], blocked columns
-        sb = stage.reshape(d, -1, 256)
-        grads[1 + 3 * s] = sb[:, :, :128].reshape(d, f)
-        grads[2 + 3 * s] = sb[:, :, 128:].reshape(d, f)
-
+    m = np_backward_decomposed(ws, x, R, fwd["selected"], fwd["gating"], fwd["counts"])
     ref = oracle.moe_backward(ws, bias, k, x, R)
-    np.testing.assert_allclose(dx, ref["d_x"], rtol=2e-3, atol=2e-4)
-    for i, (g, r) in enumerate(zip(grads, ref["grads"])):
+    np.testing.assert_allclose(m["dx"], ref["d_x"], rtol=2e-3, atol=2e-4)
+    for i, (g, r) in enumerate(zip(m["grads"], ref["grads"])):
         np.testing.assert_allclose(g, r, rtol=2e-3, atol=2e-4, err_msg=f"gradient {i}")
 
 
