@@ -164,6 +164,18 @@ PRICHS_API int prichs_moe_get_routing(prichs_moe_t* h, float* logits_host, int32
 PRICHS_API int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* dy_dev, int dy_dtype,
                                    float* dx_dev, float* const* grads_dev, int n_grads, void* stream);
 
+/* Backward of the last prichs_moe_block_forward on this handle: prichs_moe_backward on the normalised rows, then the
+ * pre-norm's backward (rmsnorm_backward, crates/prichs-core/src/backward.rs:94-131, as called at
+ * crates/prichs-model/src/model.rs:777-789):
+ *   dx_res = dy + gamma * rms_inv * (d_normed - x_res * coeff),  d_norm_weight += sum_t d_normed * x_res * rms_inv
+ * dy_dev [T,d] is the gradient of the sub-layer's output; it reaches dx_res_dev [T,d] (fp32, overwritten) directly
+ * through the residual connection and through the sub-layer. d_norm_weight_dev: [d] fp32, accumulated, may be null.
+ * As in the reference the x-term of dx_res carries gamma (the true gradient for gamma = 1, its initial value).
+ * grads_dev / n_grads as in prichs_moe_backward. Same restrictions; hidden_dim <= 2048. */
+PRICHS_API int prichs_moe_block_backward(prichs_moe_t* h, const void* x_res_dev, int x_dtype, const float* norm_weight_dev,
+                                         float eps, const void* dy_dev, int dy_dtype, float* dx_res_dev,
+                                         float* d_norm_weight_dev, float* const* grads_dev, int n_grads, void* stream);
+
 /* MoELayer::update_aux_free_bias(expert_token_counts, total_tokens, gamma) (moe.rs:228-245) with host
  * counts, as the reference's call sites pass them (model.rs:786-792,1541-1548):
  *   b_i += gamma * (top_k/E - counts[i]/total_tokens);   no-op when total_tokens == 0. */

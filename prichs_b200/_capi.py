@@ -35,6 +35,8 @@ SYMBOLS = {
                                            C.c_int, C.c_int, C.c_void_p]),
     "prichs_moe_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_void_p),
                                       C.c_int, C.c_void_p]),
+    "prichs_moe_block_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_void_p,
+                                            C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p]),
     "prichs_moe_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, _fp, C.c_int, C.c_void_p, C.c_int]),
     "prichs_moe_sync_status": (C.c_int, [C.c_void_p]),
     "prichs_moe_get_counts": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int]),

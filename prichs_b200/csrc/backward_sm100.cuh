@@ -12,6 +12,7 @@
 //   dx_combine_kernel   d_x = shared dX + sum over the token's experts (ascending) of gate * routed dX + d_logits W_r^T
 //                       (model.rs:629-631, 724-732, 759-766); the gate weight enters a routed expert's input
 //                       gradient twice, once through dY_e and once here, exactly as in the reference
+//   rmsnorm_bwd_rows_kernel / dgamma_*   the block's pre-norm backward after the MoE backward (backward.rs:94-131)
 //   transpose_bf16_kernel   [rows, cols] -> [cols, rows]: the weight-gradient products contract over rows, so both
 //                       of their operands are fed to the K-major GEMM as transposed copies
 //   grad_unpack_*       staged fp32 weight gradients -> accumulated (+=) into the caller's buffers in the reference's
@@ -240,6 +241,106 @@ dx_combine_kernel(const __nv_bfloat16* __restrict__ dxall, const int* __restrict
         op[0] = make_float4(o[0], o[1], o[2], o[3]);
         op[1] = make_float4(o[4], o[5], o[6], o[7]);
     }
+}
+
+// Backward of the block's pre-norm (rmsnorm_backward, backward.rs:94-131) for the MoE sub-layer: one warp per row.
+//   rms_inv = 1 / sqrt(mean(x^2) + eps),  coeff = (sum_i dn_i * gamma_i * x_i / d) * rms_inv^2,
+//   dx_res_i = dy_i + gamma_i * rms_inv * (dn_i - x_i * coeff)
+// dn: gradient of the normalised rows (the MoE backward's d_x), fp32; dy: the gradient that reaches the residual
+// connection (the reference seeds d_x_res with a clone of it, model.rs:777-789). The x-term carries gamma as in the
+// reference. Also writes rms_inv per row for the weight gradient. d is a multiple of 256, at most 256 * MAXC.
+template <bool XF32, bool DYF32, int MAXC>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_rows_kernel(const void* __restrict__ x, const float* __restrict__ dn, const float* __restrict__ gamma,
+                        const void* __restrict__ dy, float eps, float* __restrict__ dx_res, float* __restrict__ rinv, int T,
+                        int d) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    const int nchunk = d / 256;
+    float xv[MAXC][8], dv[MAXC][8];
+    float sum_sq = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        if (i < nchunk) {
+            const int c = i * 256 + lane * 8;
+            if (XF32) {
+                const float* p = reinterpret_cast<const float*>(x) + (size_t)t * d + c;
+                const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+                xv[i][0] = a.x; xv[i][1] = a.y; xv[i][2] = a.z; xv[i][3] = a.w; xv[i][4] = b.x; xv[i][5] = b.y; xv[i][6] = b.z; xv[i][7] = b.w;
+            } else {
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)t * d + c), xv[i]);
+            }
+            const float* q = dn + (size_t)t * d + c;
+            const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + 4);
+            dv[i][0] = a.x; dv[i][1] = a.y; dv[i][2] = a.z; dv[i][3] = a.w; dv[i][4] = b.x; dv[i][5] = b.y; dv[i][6] = b.z; dv[i][7] = b.w;
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+            const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                sum_sq = fmaf(xv[i][j], xv[i][j], sum_sq);
+                dot = fmaf(dv[i][j] * gv[j], xv[i][j], dot);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, o);
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    }
+    const float inv_d = 1.0f / (float)d;
+    const float rms_inv = 1.0f / sqrtf(sum_sq * inv_d + eps);
+    const float coeff = (dot * inv_d) * (rms_inv * rms_inv);
+    if (lane == 0) rinv[t] = rms_inv;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        if (i < nchunk) {
+            const int c = i * 256 + lane * 8;
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+            const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float seed[8];
+            if (DYF32) {
+                const float* p = reinterpret_cast<const float*>(dy) + (size_t)t * d + c;
+                const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+                seed[0] = a.x; seed[1] = a.y; seed[2] = a.z; seed[3] = a.w; seed[4] = b.x; seed[5] = b.y; seed[6] = b.z; seed[7] = b.w;
+            } else {
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(dy) + (size_t)t * d + c), seed);
+            }
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = seed[j] + gv[j] * rms_inv * (dv[i][j] - xv[i][j] * coeff);
+            float4* op = reinterpret_cast<float4*>(dx_res + (size_t)t * d + c);
+            op[0] = make_float4(o[0], o[1], o[2], o[3]);
+            op[1] = make_float4(o[4], o[5], o[6], o[7]);
+        }
+    }
+}
+
+// d_gamma[i] += sum_t dn[t,i] * x[t,i] * rms_inv[t] (backward.rs:127), in a fixed order: grid (d / 256, DWR_SPLITS)
+// sums token ranges into part[s][i]; the reduce kernel adds the splits in ascending order.
+template <bool XF32>
+__global__ void __launch_bounds__(256)
+dgamma_partial_kernel(const void* __restrict__ x, const float* __restrict__ dn, const float* __restrict__ rinv,
+                      float* __restrict__ part, int T, int d) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    const int per = (T + DWR_SPLITS - 1) / DWR_SPLITS;
+    const int t0 = min(T, (int)blockIdx.y * per), t1 = min(T, t0 + per);
+    float acc = 0.f;
+    for (int t = t0; t < t1; ++t) {
+        const float xi = XF32 ? reinterpret_cast<const float*>(x)[(size_t)t * d + i]
+                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[(size_t)t * d + i]);
+        acc += dn[(size_t)t * d + i] * xi * rinv[t];
+    }
+    part[(size_t)blockIdx.y * d + i] = acc;
+}
+
+__global__ void __launch_bounds__(256)
+dgamma_reduce_kernel(const float* __restrict__ part, float* __restrict__ d_gamma, int d) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d) return;
+    float acc = 0.f;
+    for (int s = 0; s < DWR_SPLITS; ++s) acc += part[(size_t)s * d + i];
+    d_gamma[i] += acc;
 }
 
 // dst[c, r] = src[r, c] for r < rows, c < cols (bf16). src row pitch src_pitch, dst row pitch dst_pitch (elements).

@@ -337,13 +337,15 @@ struct prichs_moe {
     struct Bwd {
         bool ready, nat_valid;
         bf16 *gu, *dyall, *dh, *dgu, *dxall, *xT, *hT, *dyT, *dguT, *w_dn_nat, *w_gu_nat;
-        float *scal, *dlog, *dwr_part, *stage_dn, *stage_gu;
+        float *scal, *dlog, *dwr_part, *stage_dn, *stage_gu, *dnorm, *rinv, *dgamma_part;
         CUtensorMap tm_dyall, tm_dgu, tm_gu_out, tm_dh_out, tm_dxall_out, tm_wdn_nat, tm_wgu_nat, tm_stage_dn, tm_stage_gu;
     } bwd;
 
     cudaStream_t last_stream;
     int last_T;
     bool last_chunked;  // the last forward went through the host-buffer pipeline in chunks: only its last chunk's rows remain
+    const bf16* last_a_shared;  // bf16 rows the last single-GPU forward fed to the shared expert and the dispatch
+    bool last_was_block;  // ... and it came through prichs_moe_block_forward
     int tok_base;  // see prichs_moe_forward
     int resid_dtype;  // element type of the residual when it differs from x (block entry point), else -1
     bool timing;
@@ -902,7 +904,8 @@ int prichs_moe_destroy(prichs_moe_t* h) {
     if (h->counts_acc) cudaFree(h->counts_acc);
     {
         void* bp[] = {h->bwd.gu, h->bwd.dyall, h->bwd.dh, h->bwd.dgu, h->bwd.dxall, h->bwd.xT, h->bwd.hT, h->bwd.dyT, h->bwd.dguT,
-                      h->bwd.w_dn_nat, h->bwd.w_gu_nat, h->bwd.scal, h->bwd.dlog, h->bwd.dwr_part, h->bwd.stage_dn, h->bwd.stage_gu};
+                      h->bwd.w_dn_nat, h->bwd.w_gu_nat, h->bwd.scal, h->bwd.dlog, h->bwd.dwr_part, h->bwd.stage_dn, h->bwd.stage_gu,
+                      h->bwd.dnorm, h->bwd.rinv, h->bwd.dgamma_part};
         for (void* q : bp)
             if (q) cudaFree(q);
     }
@@ -996,6 +999,8 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     h->last_stream = st;
     h->last_T = T;
     h->last_chunked = false;
+    h->last_was_block = false;
+    h->last_a_shared = nullptr;
     if (T == 0) {
         if (h->world > 1) return fail(PRICHS_ERR_BAD_SHAPE, "in expert-parallel mode every rank must pass at least one token");
         return PRICHS_OK;
@@ -1024,6 +1029,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     CUtensorMap tm_x;
     int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
     if (rc != PRICHS_OK) return rc;
+    h->last_a_shared = a_shared;
 
     const bool timing = h->timing;
     int evi = 0;
@@ -1125,6 +1131,7 @@ int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype
                                 y_dtype, T, stream_);
     }
     h->resid_dtype = -1;
+    h->last_was_block = rc == PRICHS_OK;
     return rc;
 }
 
@@ -1391,6 +1398,9 @@ int bwd_alloc(prichs_moe* h) {
     if (!b.dwr_part) A(dalloc(&b.dwr_part, (size_t)bwd::DWR_SPLITS * d * route::MAX_E));
     if (!b.stage_dn) A(dalloc(&b.stage_dn, f * d));
     if (!b.stage_gu) A(dalloc(&b.stage_gu, d * 2 * f));
+    if (!b.dnorm) A(dalloc(&b.dnorm, (size_t)h->Tmax * d));
+    if (!b.rinv) A(dalloc(&b.rinv, (size_t)h->Tmax));
+    if (!b.dgamma_part) A(dalloc(&b.dgamma_part, (size_t)bwd::DWR_SPLITS * d));
     if (rc != PRICHS_OK) return rc;
     // rows that no kernel of a backward pass writes (padding of the permuted region) must stay finite
     CUDA_TRY(cudaMemset(b.dyall, 0, R * d * sizeof(bf16)));
@@ -1430,24 +1440,91 @@ int bwd_gemm(prichs_moe* h, const CUtensorMap& tm_a_shared, const CUtensorMap& t
 
 }  // namespace
 
-int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* dy_dev, int dy_dtype, float* dx_dev,
-                        float* const* grads_dev, int n_grads, void* stream_) {
-    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+namespace {
+
+// Checks shared by the two backward entry points; returns the T of the forward to differentiate through *T_out.
+int bwd_check(prichs_moe* h, const void* dy_dev, int dy_dtype, const void* dx_dev, float* const* grads_dev, int n_grads, int* T_out) {
     if (h->world > 1) return fail(PRICHS_ERR_BAD_ARG, "the backward pass runs with all experts local (ep_world = 1)");
     if (h->mode != PRICHS_MODE_BF16) return fail(PRICHS_ERR_BAD_ARG, "the backward pass runs in the bf16 mode");
     if (h->f % 256 != 0) return fail(PRICHS_ERR_BAD_SHAPE, "the backward pass needs intermediate_dim to be a multiple of 256 (got %d)", h->f);
-    if (!x_dev || !dy_dev || !dx_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation or gradient pointer");
-    if ((x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) || (dy_dtype != PRICHS_DTYPE_F32 && dy_dtype != PRICHS_DTYPE_BF16))
-        return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    if (!dy_dev || !dx_dev) return fail(PRICHS_ERR_BAD_ARG, "null gradient pointer");
+    if (dy_dtype != PRICHS_DTYPE_F32 && dy_dtype != PRICHS_DTYPE_BF16) return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
     if (grads_dev && n_grads != 1 + 3 * (1 + h->E))
         return fail(PRICHS_ERR_BAD_SHAPE, "expected %d gradient buffers (router, shared g/u/d, then g/u/d per expert), got %d", 1 + 3 * (1 + h->E), n_grads);
-    if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (reinterpret_cast<uintptr_t>(dy_dev) & 15) || (reinterpret_cast<uintptr_t>(dx_dev) & 15))
-        return fail(PRICHS_ERR_BAD_ARG, "activation and gradient pointers must be 16-byte aligned");
-    const int T = h->last_T;
-    if (T <= 0) return fail(PRICHS_ERR_BAD_ARG, "no forward pass to differentiate: call prichs_moe_forward first");
+    if ((reinterpret_cast<uintptr_t>(dy_dev) & 15) || (reinterpret_cast<uintptr_t>(dx_dev) & 15))
+        return fail(PRICHS_ERR_BAD_ARG, "gradient pointers must be 16-byte aligned");
+    if (h->last_T <= 0 || !h->last_a_shared) return fail(PRICHS_ERR_BAD_ARG, "no forward pass to differentiate: call prichs_moe_forward first");
     if (h->last_chunked) return fail(PRICHS_ERR_BAD_ARG, "the last forward went through host buffers in chunks; run prichs_moe_forward on device buffers before the backward pass");
+    *T_out = h->last_T;
+    return PRICHS_OK;
+}
+
+int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int dy_dtype, float* dx_dev, float* const* grads_dev,
+                  cudaStream_t st);
+
+}  // namespace
+
+int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* dy_dev, int dy_dtype, float* dx_dev,
+                        float* const* grads_dev, int n_grads, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (!x_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation pointer");
+    if (x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    int T = 0;
+    int rc = bwd_check(h, dy_dev, dy_dtype, dx_dev, grads_dev, n_grads, &T);
+    if (rc != PRICHS_OK) return rc;
+    if (h->last_was_block) return fail(PRICHS_ERR_BAD_ARG, "the last forward was prichs_moe_block_forward: use prichs_moe_block_backward");
+    // the layer input as the forward used it: the caller's bf16 rows, or the bf16 copy the router wrote
+    const bf16* a_shared = x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
+    if (a_shared != h->last_a_shared) return fail(PRICHS_ERR_BAD_ARG, "x_dev is not the input of the last forward on this handle");
+    DeviceGuard guard(h->device);
+    return backward_impl(h, a_shared, dy_dev, dy_dtype, dx_dev, grads_dev, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+int prichs_moe_block_backward(prichs_moe_t* h, const void* x_res_dev, int x_dtype, const float* norm_weight_dev, float eps,
+                              const void* dy_dev, int dy_dtype, float* dx_res_dev, float* d_norm_weight_dev,
+                              float* const* grads_dev, int n_grads, void* stream_) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (!x_res_dev || !norm_weight_dev) return fail(PRICHS_ERR_BAD_ARG, "null activation or norm-weight pointer");
+    if (x_dtype != PRICHS_DTYPE_F32 && x_dtype != PRICHS_DTYPE_BF16) return fail(PRICHS_ERR_BAD_ARG, "unknown element type");
+    if ((reinterpret_cast<uintptr_t>(x_res_dev) & 15) || (reinterpret_cast<uintptr_t>(norm_weight_dev) & 15))
+        return fail(PRICHS_ERR_BAD_ARG, "activation and weight pointers must be 16-byte aligned");
+    if (h->d > 2048) return fail(PRICHS_ERR_BAD_SHAPE, "the block entry points support hidden_dim up to 2048");
+    int T = 0;
+    int rc = bwd_check(h, dy_dev, dy_dtype, dx_res_dev, grads_dev, n_grads, &T);
+    if (rc != PRICHS_OK) return rc;
+    if (!h->last_was_block) return fail(PRICHS_ERR_BAD_ARG, "the last forward was not prichs_moe_block_forward");
     DeviceGuard guard(h->device);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+    rc = bwd_alloc(h);
+    if (rc != PRICHS_OK) return rc;
+    prichs_moe::Bwd& b = h->bwd;
+    // gradient of the normalised rows (the MoE layer's input) ...
+    rc = backward_impl(h, h->last_a_shared, dy_dev, dy_dtype, b.dnorm, grads_dev, st);
+    if (rc != PRICHS_OK) return rc;
+    // ... through the pre-norm, seeded with the gradient that bypasses the sub-layer on the residual connection
+    const int d = h->d, grid = (T + 7) / 8;
+    const bool xf = x_dtype == PRICHS_DTYPE_F32, df = dy_dtype == PRICHS_DTYPE_F32;
+    if (xf && df) bwd::rmsnorm_bwd_rows_kernel<true, true, 8><<<grid, 256, 0, st>>>(x_res_dev, b.dnorm, norm_weight_dev, dy_dev, eps, dx_res_dev, b.rinv, T, d);
+    else if (xf) bwd::rmsnorm_bwd_rows_kernel<true, false, 8><<<grid, 256, 0, st>>>(x_res_dev, b.dnorm, norm_weight_dev, dy_dev, eps, dx_res_dev, b.rinv, T, d);
+    else if (df) bwd::rmsnorm_bwd_rows_kernel<false, true, 8><<<grid, 256, 0, st>>>(x_res_dev, b.dnorm, norm_weight_dev, dy_dev, eps, dx_res_dev, b.rinv, T, d);
+    else bwd::rmsnorm_bwd_rows_kernel<false, false, 8><<<grid, 256, 0, st>>>(x_res_dev, b.dnorm, norm_weight_dev, dy_dev, eps, dx_res_dev, b.rinv, T, d);
+    LAUNCH_CHECK("pre-norm backward");
+    if (d_norm_weight_dev) {
+        if (xf) bwd::dgamma_partial_kernel<true><<<dim3(d / 256, bwd::DWR_SPLITS), 256, 0, st>>>(x_res_dev, b.dnorm, b.rinv, b.dgamma_part, T, d);
+        else bwd::dgamma_partial_kernel<false><<<dim3(d / 256, bwd::DWR_SPLITS), 256, 0, st>>>(x_res_dev, b.dnorm, b.rinv, b.dgamma_part, T, d);
+        LAUNCH_CHECK("norm weight gradient (partial sums)");
+        bwd::dgamma_reduce_kernel<<<(d + 255) / 256, 256, 0, st>>>(b.dgamma_part, d_norm_weight_dev, d);
+        LAUNCH_CHECK("norm weight gradient");
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    return prichs_moe_sync_status(h);
+}
+
+namespace {
+
+int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int dy_dtype, float* dx_dev, float* const* grads_dev,
+                  cudaStream_t st) {
+    const int T = h->last_T;
     int rc = bwd_alloc(h);
     if (rc != PRICHS_OK) return rc;
     prichs_moe::Bwd& b = h->bwd;
@@ -1474,8 +1551,6 @@ int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const v
         b.nat_valid = true;
     }
 
-    // the layer input as the forward used it: the caller's bf16 rows, or the bf16 copy the router wrote
-    const bf16* a_shared = x_dtype == PRICHS_DTYPE_F32 ? h->xs : reinterpret_cast<const bf16*>(x_dev);
     CUtensorMap tm_x;
     rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)d, egemm::BM);
     if (rc != PRICHS_OK) return rc;
@@ -1604,6 +1679,8 @@ int prichs_moe_backward(prichs_moe_t* h, const void* x_dev, int x_dtype, const v
     h->last_stream = st;
     return prichs_moe_sync_status(h);
 }
+
+}  // namespace
 
 int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes) {
     if (!h || !host_dst) return fail(PRICHS_ERR_BAD_ARG, "null handle or destination");

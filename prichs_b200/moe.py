@@ -291,6 +291,36 @@ class MoELayer:
                                                arr, n if grads is not None else 0, st))
         return dx
 
+    def block_backward(self, x_residual, post_attn_norm, eps: float, d_out, grads=None, d_norm=None, stream=None):
+        """Backward of the last `block_forward` (crates/prichs-model/src/model.rs:566-789): MoE backward on the
+        normalised rows, then rmsnorm_backward with the residual gradient seeded in. Returns d_x_residual [T, d] fp32.
+        `grads` as in `backward`; `d_norm` ([d] fp32 CUDA tensor or None) accumulates the norm weight's gradient."""
+        import torch
+        x = x_residual
+        if not (isinstance(x, torch.Tensor) and x.is_cuda and isinstance(d_out, torch.Tensor) and d_out.is_cuda):
+            raise PrichsError(_capi.ERR_BAD_ARG, "x_residual and d_out must be CUDA tensors")
+        if x.dim() != 2 or x.shape[1] != self.hidden_dim or tuple(d_out.shape) != tuple(x.shape):
+            raise PrichsError(_capi.ERR_BAD_SHAPE, "x_residual and d_out must both be [T, hidden_dim]")
+        if not self._h or x.shape[0] != self._T_last:
+            raise PrichsError(_capi.ERR_BAD_ARG, "block_backward needs block_forward of the same batch to have run last")
+        dts = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
+        x, d_out = x.contiguous(), d_out.contiguous()
+        w = post_attn_norm.to(device=x.device, dtype=torch.float32).contiguous()
+        dx = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        n = 1 + 3 * (1 + self._num_experts)
+        arr = None
+        if grads is not None:
+            if len(grads) != n:
+                raise PrichsError(_capi.ERR_BAD_SHAPE, f"expected {n} gradient buffers, got {len(grads)}")
+            arr = (C.c_void_p * n)(*[C.c_void_p(g.data_ptr()) if g is not None else C.c_void_p(0) for g in grads])
+        if d_norm is not None and not (d_norm.is_cuda and d_norm.dtype == torch.float32 and d_norm.numel() == self.hidden_dim):
+            raise PrichsError(_capi.ERR_BAD_ARG, "d_norm must be a CUDA fp32 tensor of hidden_dim elements")
+        st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
+        _check(_capi.lib().prichs_moe_block_backward(self._h, x.data_ptr(), dts[x.dtype], w.data_ptr(), C.c_float(eps), d_out.data_ptr(),
+                                                     dts[d_out.dtype], dx.data_ptr(), d_norm.data_ptr() if d_norm is not None else None,
+                                                     arr, n if grads is not None else 0, st))
+        return dx
+
     def forward_train(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, **kw):
         out = self.forward_with_memory(x, starkdb_concept_bias, **kw)
         return out, self.last_stash()

@@ -134,3 +134,40 @@ def test_backward_dx_only_and_errors(torch_cuda, oracle):
     assert_close(dx, ref["d_x"], TOL, "d_x without weight gradients")
     with pytest.raises(PrichsError):
         m.backward(xd[:10], torch.from_numpy(R[:10]).cuda())  # not the batch of the last forward
+
+
+@pytest.mark.parametrize("x_kind", ["bf16", "f32"])
+def test_block_backward_matches_oracle(torch_cuda, oracle, x_kind):
+    """x_res -> rms_norm -> MoE -> + x_res, backwards: oracle.moe_backward on the normalised rows, then
+    oracle.rmsnorm_backward seeded with d_out (model.rs:566-789)."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    T, d, f, E, k, eps = 150, 512, 256, 8, 2, 1e-5
+    ws = synth.layer_weights(241, d, f, E, std=0.05, bf16=True)
+    bias = synth.router_bias(241, E, -0.1, 0.1)
+    x_res = synth.normal(242, 0, (T, d), 0.0, 2.0)
+    if x_kind == "bf16":
+        x_res = synth.round_bf16(x_res)
+    R = synth.round_bf16(synth.normal(243, 0, (T, d)))
+    w = (1.0 + 0.1 * synth.normal(244, 0, (d,))).astype(np.float32)
+    m = MoELayer.from_weights(ws, k, mode="bf16")
+    m.router_bias = bias
+    xd = torch.from_numpy(x_res).cuda().to({"bf16": torch.bfloat16, "f32": torch.float32}[x_kind])
+    wd = torch.from_numpy(w).cuda()
+    m.block_forward(xd, wd, eps)
+    st = m.last_stash()
+    grads = [torch.zeros(wt.shape, dtype=torch.float32, device="cuda") for wt in ws]
+    d_norm = torch.zeros(d, dtype=torch.float32, device="cuda")
+    dx = m.block_backward(xd, wd, eps, torch.from_numpy(R).cuda(), grads, d_norm).cpu().numpy()
+    m.sync_status()
+    xn = synth.round_bf16(oracle.rms_norm(x_res, w, eps))  # the layer's input in bf16 mode
+    ref_fwd = oracle.moe_forward_train(ws, bias, k, xn)
+    assert np.all(ref_fwd["selected"] == st.selected_experts.reshape(T, k)), "pick another seed: routing must agree"
+    ref = oracle.moe_backward(ws, bias, k, xn, R)
+    ref_dx, ref_dg = oracle.rmsnorm_backward(ref["d_x"], x_res, w, eps, d_x=R)
+    assert_close(dx, ref_dx, TOL, "d_x_residual")
+    assert _rel(d_norm.cpu().numpy(), ref_dg) <= TOL
+    for i, (g, r) in enumerate(zip(grads, ref["grads"])):
+        assert _rel(g.cpu().numpy(), r) <= TOL, (i, _rel(g.cpu().numpy(), r))
+    with pytest.raises(Exception):
+        m.backward(xd, torch.from_numpy(R).cuda())  # the last forward was the block entry point
