@@ -1,9 +1,9 @@
 """GPU parity of prichs_moe_backward against the oracle's restatement of the reference's MoE backward pass
 (crates/prichs-model/src/model.rs:566-766).
 
-The backward path was written after this build's GPU time had run out: it compiles for sm_100a and its entry point is
-exported, but it has not yet run on a B200. Until it has, these tests only run when PRICHS_TEST_BACKWARD=1 is set, so
-that an unvalidated kernel cannot take the validated forward suite down with it."""
+The backward path compiles for sm_100a and its entry points are exported, but it has not yet run on a B200. Until it
+has, these tests only run when PRICHS_TEST_BACKWARD=1 is set, so that an unvalidated kernel cannot take the validated
+forward suite down with it."""
 import os
 
 import numpy as np
