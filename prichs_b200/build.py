@@ -14,7 +14,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG, "csrc")
 LIB_PATH = os.path.join(_PKG, "libprichs_moe.so")
 SOURCES = ["prichs_moe.cu"]
-HEADERS = ["ptx_sm100.cuh", "expert_gemm_sm100.cuh", "expert_gemm_pair_sm100.cuh", "route_sm100.cuh", "../../include/prichs_moe.h"]
+HEADERS = sorted(f for f in os.listdir(_CSRC) if f.endswith(".cuh")) + ["../../include/prichs_moe.h"]
 
 NVCC_FLAGS = [
     "-ldl",

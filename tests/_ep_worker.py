@@ -1,4 +1,4 @@
-"""Expert-parallel parity worker, one process per GPU (launched by tests/test_gpu_ep.py through
+"""Expert-parallel parity worker, one process per GPU (launched by tests/test_gpu_zep.py through
 torch.distributed.run). Every rank routes its own seeded tokens, the experts are partitioned over the ranks,
 and each rank checks its outputs against the CPU oracle run on the full (unpartitioned) layer."""
 import os
