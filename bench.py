@@ -303,6 +303,10 @@ def main():
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
     ap.add_argument("--streams", type=int, default=8, help="decode config: streams the independent layers are spread over")
+    ap.add_argument("--route-kernel", type=int, default=0, choices=[0, 1, 2],
+                    help="single GPU: 0 = library default, 1 = single-pass routing kernel, 2 = router / scan / dispatch launches")
+    ap.add_argument("--gemm-kernel", type=int, default=0, choices=[0, 1], help="0 = CTA-pair kernel, 1 = one-CTA kernel")
+    ap.add_argument("--pdl", type=int, default=0, choices=[0, 1], help="programmatic dependent launch between the kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -333,7 +337,8 @@ def main():
         seed, T = 1, (args.tokens or 16384)
         ws = synth.layer_weights(seed, D, F, E, bf16=True)
         bias = synth.router_bias(seed, E, -0.1, 0.1)
-        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank)
+        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, route_kernel=args.route_kernel,
+                                      gemm_kernel=args.gemm_kernel, pdl=args.pdl)
     else:
         from prichs_b200 import ep
         skew = args.config == 4
@@ -445,10 +450,18 @@ def main():
         stage_ms = dict(zip(names, [float(v) for v in stage]))
         gu_tf = gu_flops / (stage_ms["gate_up_gemm"] * 1e-3) / 1e12
         dn_tf = rows * 2 * D * F / (stage_ms["down_gemm"] * 1e-3) / 1e12
+        single_pass = stage_ms["dispatch"] < 0.008  # one kernel routed, placed and dispatched: no scan / dispatch stages
+        if single_pass:
+            routing = {"route_dispatch": {"ms": stage_ms["router"], "GB/s": T * (ROUTER_BYTES + DISPATCH_BYTES) / stage_ms["router"] / 1e6,
+                                          "bound": "hbm", "kernel": "route_dispatch_kernel (router + prefix + dispatch in one pass)",
+                                          "algorithmic_bytes_per_token": ROUTER_BYTES + DISPATCH_BYTES,
+                                          "bytes_moved_per_token": ROUTER_BYTES + DISPATCH_BYTES - D * 2}}
+        else:
+            routing = {"router": {"ms": stage_ms["router"], "GB/s": T * ROUTER_BYTES / stage_ms["router"] / 1e6, "bound": "hbm"},
+                       "scan": {"ms": stage_ms["scan"]},
+                       "dispatch": {"ms": stage_ms["dispatch"], "GB/s": T * DISPATCH_BYTES / stage_ms["dispatch"] / 1e6, "bound": "hbm"}}
         stages = {
-            "router": {"ms": stage_ms["router"], "GB/s": T * ROUTER_BYTES / stage_ms["router"] / 1e6, "bound": "hbm"},
-            "scan": {"ms": stage_ms["scan"]},
-            "dispatch": {"ms": stage_ms["dispatch"], "GB/s": T * DISPATCH_BYTES / stage_ms["dispatch"] / 1e6, "bound": "hbm"},
+            **routing,
             "gate_up_gemm": {"ms": stage_ms["gate_up_gemm"], "TFLOP/s": gu_tf, "bound": "tensor"},
             "down_gemm": {"ms": stage_ms["down_gemm"], "TFLOP/s": dn_tf, "bound": "tensor"},
             "combine": {"ms": stage_ms["combine"], "GB/s": T * COMBINE_BYTES_NORES / stage_ms["combine"] / 1e6, "bound": "hbm"},

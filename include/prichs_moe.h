@@ -65,6 +65,23 @@ typedef struct prichs_moe_config {
     int ep_waves;         /* expert-parallel only: the batch is cut into this many token waves (1..4) whose
                              exchanges overlap the other waves' GEMMs; 0 = choose from max_tokens. Must be the
                              same on every rank.                                                          */
+    /* ---- tuning. Zero selects the default everywhere, so a zero-initialised tail is the product path; the
+     *      other values exist so that the alternatives can be measured and tested against each other. The
+     *      library reads no environment variable. ------------------------------------------------------ */
+    int route_kernel;     /* all experts local, bf16 rows: 0 = choose (single pass from 1024 tokens up), 1 = route,
+                             place and dispatch in one pass (one kernel), 2 = router / scan / dispatch launches   */
+    int scan_placement;   /* three-launch path: 0 = prefix sums at the router's tail under 1024 tokens, else a
+                             launch of their own; 1 = always at the tail; 2 = always their own launch          */
+    int separate_prenorm; /* block entry point: 1 = the RMSNorm runs as its own launch (0: folded into the router)  */
+    int gemm_kernel;      /* 0 = CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles), 1 = one-CTA kernel          */
+    int pdl;              /* 1 = programmatic dependent launch between the kernels of a single-GPU forward          */
+    int host_chunk_tokens;/* host-buffer entry point: tokens per pipelined chunk (0 = choose from T)                */
+    int router_ctas_per_sm; /* router grid cap in CTAs per SM (0 = default; -1 = one CTA per 16-token tile)         */
+    int ep_reserve_sms;   /* expert parallel: SMs the GEMM launches leave to the exchange kernels (0 = default 20,
+                             -1 = none)                                                                            */
+    int ep_shared_copy_sms; /* expert parallel: 1 = dispatch / combine may share SMs with GEMM CTAs                 */
+    int ep_combine_mode;  /* expert parallel: which combine launches keep off the GEMM SMs: 0 = all but the last
+                             wave's (default), 1 = all, 2 = none                                                   */
 } prichs_moe_config_t;
 
 /* ---- lifetime ------------------------------------------------------------------------------------ */
@@ -247,8 +264,16 @@ PRICHS_API int prichs_moe_get_ep_timeline(prichs_moe_t* h, float* ms, int n);
  *          after prichs_moe_backward, in the same row space: 9 recomputed [gate | up] [Tcap+Rcap,2f] bf16 (blocks of
  *          128 gate then 128 up columns)   10 dY rows [.,d] bf16   11 d_act [.,f] bf16   12 [d_gate | d_up] [.,2f] bf16
  *          13 dX rows [.,d] bf16   14 <expert row, d_out> [T,2] fp32   15 d_logits [T,8] fp32
- *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 256. */
+ *          16 m-tile -> 128-row tile index inside the permuted region, int32 (all experts local)
+ *   K1 = d, K2 = f (2d, 2f in PRICHS_MODE_F32); Tcap = max_tokens rounded up to 256. With all experts local
+ *   Rcap = E * Tcap: expert e's rows start at row e * Tcap of the permuted region (fixed-capacity segments). */
 PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void* host_dst, size_t bytes);
+
+/* Test knobs of the single-pass routing kernel (no counterpart in the reference). key 0: index of a 16-token tile
+ * that does not publish its counts in the following forwards, so that the look-back of the tiles after it runs out
+ * and the forward reports PRICHS_ERR_TIMEOUT through prichs_moe_sync_status (-1 = none, the default). key 1: budget
+ * of that kernel's bounded waits in clock cycles (default 4e9, about two seconds). */
+PRICHS_API int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value);
 
 /* ---- routing without any allocation ---------------------------------------------------------------
  * This entry point has no counterpart in the reference. It exists for callers that are not allowed to

@@ -18,7 +18,14 @@ MODE_BF16, MODE_F32 = 0, 1
 
 class Config(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("hidden_dim", "intermediate_dim", "num_experts", "top_k", "max_tokens",
-                                       "mode", "device", "ep_world", "ep_rank", "ep_max_recv_rows", "ep_waves")]
+                                       "mode", "device", "ep_world", "ep_rank", "ep_max_recv_rows", "ep_waves",
+                                       # tuning (0 = default): see prichs_moe_config_t
+                                       "route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl",
+                                       "host_chunk_tokens", "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms",
+                                       "ep_combine_mode")]
+
+TUNING_FIELDS = ("route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl", "host_chunk_tokens",
+                 "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms", "ep_combine_mode")
 
 
 # name -> (restype, argtypes); the full export list of include/prichs_moe.h
@@ -53,6 +60,7 @@ SYMBOLS = {
     "prichs_moe_get_stage_ms": (C.c_int, [C.c_void_p, _fp]),
     "prichs_moe_get_ep_timeline": (C.c_int, [C.c_void_p, _fp, C.c_int]),
     "prichs_moe_debug_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "prichs_moe_debug_set": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong]),
     "prichs_moe_route_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "launch_moe_gather": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),

@@ -104,17 +104,23 @@ dy_prepare_kernel(const void* __restrict__ dy, const __nv_bfloat16* __restrict__
 // d_up = d_act * silu(g), d_gate = d_act * u * sig(g) * (1 + g * (1 - sig(g)))   (backward.rs:247-266).
 // gu / dgu: [rows, 2f] bf16 in the column order of the first forward GEMM's B operand: blocks of 256 columns, 128
 // gate columns then 128 up columns of the same hidden units. dh: [rows, f] bf16. Rows [0, T) (shared expert) and
-// [tcap, tcap + 128 * n_routed_mtiles) (permuted region, padding rows included: their d_act is zero).
+// the 128-row tiles of the permuted region the GEMM tile table lists (tile i at row tcap + 128 * mtile_row[i]; padding
+// rows included: nothing reads what is computed for them, the weight-gradient products stop at each expert's row count).
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ dgu,
-                  int T, int f, long long tcap, const int* __restrict__ n_routed_mtiles) {
+                  int T, int f, long long tcap, const int* __restrict__ n_routed_mtiles, const int* __restrict__ mtile_row) {
     const long long routed_rows = 128LL * *n_routed_mtiles;
     const int vec_per_row = f / 8;  // 8 hidden units per thread and step; f is a multiple of 128
     const long long total = ((long long)T + routed_rows) * vec_per_row;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / vec_per_row;
         const int j0 = (int)(i - r * vec_per_row) * 8;
-        const long long row = r < T ? r : tcap + (r - T);
+        long long row = r;
+        if (r >= T) {
+            const long long rr = r - T;
+            const int ti = (int)(rr >> 7);
+            row = tcap + 128LL * (mtile_row ? mtile_row[ti] : ti) + (rr & 127);
+        }
         const int blk = j0 >> 7, within = j0 & 127;
         const size_t gcol = (size_t)blk * 256 + within;
         float dy[8], g[8], u[8], dg[8], du[8];

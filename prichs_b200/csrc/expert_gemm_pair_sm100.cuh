@@ -101,7 +101,8 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
                 const CUtensorMap* tm_a = is_shared ? &tm_a_shared : &tm_a_routed;
                 const int rp = mp - shared_pairs;  // pair index inside the permuted region
                 if (!is_shared && args.mtile_slot[2 * rp] < 0) continue;  // a pair of padding rows only
-                const int a_row = (is_shared ? 2 * mp : args.a_routed_tile_off + 2 * rp) * BM + (int)cta_rank * BM;
+                const int rt = is_shared ? 0 : (args.mtile_row ? args.mtile_row[2 * rp] : 2 * rp);  // first tile of the pair
+                const int a_row = (is_shared ? 2 * mp : args.a_routed_tile_off + rt) * BM + (int)cta_rank * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[2 * rp];
                 const int b_row = slot * args.w_rows + nt * BN + (int)cta_rank * 128;
                 for (int pass = 0; ok && pass < npass; ++pass) {
@@ -202,7 +203,8 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
             // this CTA's 128-row half of the pair, as a tile index of the output row space
-            const int ut = (mp < shared_pairs ? 2 * mp : args.routed_base_tiles + 2 * (mp - shared_pairs)) + (int)cta_rank;
+            const int rp_ = mp - shared_pairs;
+            const int ut = (mp < shared_pairs ? 2 * mp : args.routed_base_tiles + (args.mtile_row ? args.mtile_row[2 * rp_] : 2 * rp_)) + (int)cta_rank;
             const int row0 = ut * BM + quarter * 32;  // first output row of this warp's boxes
             if constexpr (EPI == EPI_SWIGLU) {
 #pragma unroll 1

@@ -71,6 +71,8 @@ struct Args {
                                // routed_base_tiles when A is the previous GEMM's output
     const int* n_routed_mtiles;  // device scalar: m-tiles in the permuted region
     const int* mtile_slot;     // device: permuted m-tile -> routed weight slot (0-based)
+    const int* mtile_row;      // device: permuted m-tile -> its 128-row tile index inside the permuted region; null when
+                               // the region is dense (tile i sits at tile index i)
     int w_rows;                // B rows per weight slot
     int out_split;             // SwiGLU only: also write the bf16 residual (lo) at column offset `out_lo_off`
     int out_lo_off;
@@ -152,7 +154,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                 const bool is_shared = mt < args.shared_mtiles;
                 if (!is_shared && args.mtile_slot[mt - args.shared_mtiles] < 0) continue;  // padding-only tile
                 const CUtensorMap* tm_a = is_shared ? &tm_a_shared : &tm_a_routed;
-                const int a_row = (is_shared ? mt : args.a_routed_tile_off + mt - args.shared_mtiles) * BM;
+                const int rt = is_shared ? 0 : (args.mtile_row ? args.mtile_row[mt - args.shared_mtiles] : mt - args.shared_mtiles);
+                const int a_row = (is_shared ? mt : args.a_routed_tile_off + rt) * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[mt - args.shared_mtiles];
                 const int b_row = slot * args.w_rows + nt * BN;
                 for (int pass = 0; ok && pass < npass; ++pass) {
@@ -252,7 +255,9 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
             if (!__all_sync(0xffffffffu, ready)) break;
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-            const int ut = mt < args.shared_mtiles ? mt : args.routed_base_tiles + mt - args.shared_mtiles;
+            const int ut = mt < args.shared_mtiles
+                               ? mt
+                               : args.routed_base_tiles + (args.mtile_row ? args.mtile_row[mt - args.shared_mtiles] : mt - args.shared_mtiles);
             const int row0 = ut * BM + quarter * 32;  // first output row of this warp's boxes
             if constexpr (EPI == EPI_SWIGLU) {
 #pragma unroll 1

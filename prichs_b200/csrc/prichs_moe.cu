@@ -206,6 +206,14 @@ __global__ void compat_swiglu_kernel(const float* __restrict__ gate, const float
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+// Ring depth of the single-pass routing kernel for hidden_dim d and `nsplit` router-weight parts: the deepest ring of
+// 2..4 tile buffers that fits the 227 KB of shared memory next to the weights, 0 if not even two fit.
+int rd_stages_for(int d, int nsplit) {
+    for (int st = route::RD_MAX_STAGES; st >= 2; --st)
+        if (route::rd_smem_bytes(d, nsplit, st) <= 227 * 1024 - 256) return st;
+    return 0;
+}
+
 // Token waves of the expert-parallel forward shrink towards the end: the last wave's combine is the only
 // exchange nothing can hide, so it is kept small. Cumulative fractions of the batch (per mille) per wave count.
 inline int wave_begin(int T, int n_waves, int w) {
@@ -294,10 +302,17 @@ struct prichs_moe {
     const float* norm_w;  // set while the block entry point runs with the pre-norm folded into the router's read
     float norm_eps;
     bool fuse_norm;
-    bool router_tma;      // large bf16 batches use the shared-memory-staged router kernel (opt-in)
-    bool router_warp;     // large bf16 batches with bf16-exact router weights use the warp-per-tile router kernel (opt-in)
-    int router_stages;    // depth of its ring of tile buffers
+    int route_kernel;     // 0 choose, 1 single-pass route+place+dispatch kernel, 2 three launches
+    int rd_stages[2];     // depth of the single-pass kernel's ring of tile buffers for 1 / 3 router-weight parts (0: does not fit)
     int fuse_scan;  // single-GPU forward, scan + plan at the tail of the router launch: 1 always, 0 never, -1 for small batches
+    int router_ctas_per_sm;  // router grid cap (-1: library default)
+    int host_chunk;       // tokens per chunk of the host-buffer pipeline (0 = choose)
+    int seg_stride;       // all experts local: rows of every expert's fixed-capacity segment (0: dense, expert parallel)
+    int* mtile_row;       // all experts local: GEMM tile table, tile index inside the permuted region
+    uint32_t* tile_state; // single-pass kernel: look-back words [tiles][8], zero between launches
+    int* rd_ctl;          // single-pass kernel: ticket and exit counters, zero between launches
+    long long rd_wait_cycles;  // budget of the single-pass kernel's bounded waits
+    int rd_stall_tile;    // test knob (prichs_moe_debug_set): the tile that never publishes its counts, -1 none
     void* ybuf;
     float *logits, *gates;
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
@@ -380,7 +395,7 @@ int translate_status(int s) {
     switch (s) {
         case 0: return PRICHS_OK;
         case -2: return fail(PRICHS_ERR_CAPACITY, "an expert received more rows than the permuted region holds");
-        case -5: return fail(PRICHS_ERR_TIMEOUT, "a bounded device-side wait gave up in the expert GEMM");
+        case -5: return fail(PRICHS_ERR_TIMEOUT, "a bounded device-side wait gave up (expert GEMM or single-pass routing kernel)");
         default: return fail(PRICHS_ERR_CUDA, "device status word %d", s);
     }
 }
@@ -394,8 +409,7 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
     // The router kernel strides over tiles, so its grid can be capped. With the scan at its tail every CTA ends on a
     // fence and a ticket, which is cheap for two persistent CTAs per SM and costly for one short-lived CTA per
     // tile; without the tail one CTA per tile balances best. PRICHS_ROUTER_CTAS_PER_SM overrides (0 = per tile).
-    static const int cap_env = [] { const char* e = getenv("PRICHS_ROUTER_CTAS_PER_SM"); return e ? atoi(e) : -1; }();
-    const int cap_per_sm = cap_env >= 0 ? cap_env : (tail.done != nullptr ? 2 : 0);
+    const int cap_per_sm = h->router_ctas_per_sm >= 0 ? h->router_ctas_per_sm : (tail.done != nullptr ? 2 : 0);
     const int ntiles = cap_per_sm > 0 && h->mode != PRICHS_MODE_F32 ? std::min(ntiles_all, cap_per_sm * h->sm_count) : ntiles_all;
     if (h->mode == PRICHS_MODE_F32) {
         route::router_f32_kernel<<<ntiles, 512, 0, st>>>(reinterpret_cast<const float*>(x_dev), h->xs, h->w_r8, h->bias, cb, T, d, E, h->k,
@@ -403,22 +417,6 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
     } else {
         constexpr int RT = route::ROUTER_WARPS * 32;
         const bool xf32 = x_dtype == PRICHS_DTYPE_F32, norm = h->norm_w != nullptr;
-        if (h->router_warp && !xf32 && !norm && tail.done == nullptr && h->rt_nsplit == 1 && ntiles_all >= h->sm_count) {
-            const int grid = (ntiles_all + route::ROUTER_WARP_CTA_WARPS - 1) / route::ROUTER_WARP_CTA_WARPS;
-            LAUNCH_K(pdl, route::router_warp_kernel, grid, route::ROUTER_WARP_CTA_WARPS * 32, 0, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
-                     (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts);
-            LAUNCH_CHECK("router");
-            return PRICHS_OK;
-        }
-        if (h->router_tma && !xf32 && !norm && tail.done == nullptr && h->rt_nsplit == 1 && ntiles_all >= h->sm_count) {
-            // large bf16 batch: persistent CTAs, rows staged through shared memory by bulk copies
-            const int grid = std::min(ntiles_all, h->sm_count);
-            const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
-            LAUNCH_K(pdl, route::router_tma_kernel, grid, route::ROUTER_TMA_THREADS, bytes, st, (const bf16*)x_dev, (const bf16*)h->w_rt,
-                     (const float*)h->bias, cb, T, d, E, h->k, logits, sel, gates, tile_counts, h->router_stages, h->status);
-            LAUNCH_CHECK("router");
-            return PRICHS_OK;
-        }
         bf16* xs = (xf32 || norm) ? h->xs : nullptr;  // bf16 (and normalised) copy of the rows for the expert GEMMs
 #define PRICHS_ROUTER_CASE(NS, XF, NM)                                                                                              \
     if (h->rt_nsplit == NS && xf32 == XF && norm == NM)                                                                             \
@@ -440,8 +438,8 @@ int launch_router(prichs_moe* h, const void* x_dev, int x_dtype, const route::Co
 
 // Arguments of the two grouped GEMMs (gate|up + SwiGLU, then down) for T un-permuted tokens and the permuted
 // region that starts `region_tile` 128-row tiles into the permuted buffers.
-void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles, const int* mtile_slot, egemm::Args* a1,
-               egemm::Args* a2) {
+void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles, const int* mtile_slot, const int* mtile_row,
+               egemm::Args* a1, egemm::Args* a2) {
     const bool f32mode = h->mode == PRICHS_MODE_F32;
     memset(a1, 0, sizeof(*a1));
     a1->nk = h->d / egemm::BK;
@@ -452,6 +450,7 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
     a1->a_routed_tile_off = region_tile;
     a1->n_routed_mtiles = n_routed_mtiles;
     a1->mtile_slot = mtile_slot;
+    a1->mtile_row = mtile_row;
     a1->w_rows = 2 * h->f;
     a1->out_split = f32mode;
     a1->out_lo_off = h->f;
@@ -597,7 +596,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     // 2. the shared expert needs no exchange: both of its GEMMs run on the side stream
     {
         egemm::Args s1, s2;
-        gemm_args(h, T, 0, h->ep_zero, h->wave[0].mtile_slot, &s1, &s2);
+        gemm_args(h, T, 0, h->ep_zero, h->wave[0].mtile_slot, nullptr, &s1, &s2);
         CUDA_TRY(cudaStreamWaitEvent(h->side_stream, h->ev_router, 0));
         rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, s1, gemm_grid, h->side_stream);
         if (rc != PRICHS_OK) return rc;
@@ -623,8 +622,8 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         int* tprefix = h->tile_prefix + (size_t)tile0 * route::MAX_E;
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_router, 0));
         // counts of this rank's wave -> all-gather (row `rank` of the matrix, in place) -> the same plan everywhere
-        route::scan_kernel<<<1, 1024, 0, ws>>>(h->tile_counts + (size_t)tile0 * route::MAX_E, tprefix, ntl, wv.meta, wv.mtile_slot, E, h->El,
-                                               h->world, h->rank, h->Rw, 0, SEG_PAD, h->status);
+        route::scan_kernel<<<1, 1024, 0, ws>>>(h->tile_counts + (size_t)tile0 * route::MAX_E, tprefix, ntl, wv.meta, wv.mtile_slot, nullptr, E, h->El,
+                                               h->world, h->rank, h->Rw, 0, SEG_PAD, 0, h->status);
         LAUNCH_CHECK("scan");
         if (tl) cudaEventRecord(wv.tl[0], ws);
         NCCL_TRY(nccl().all_gather(wv.meta->cmat + h->rank * route::MAX_E, wv.meta->cmat, route::MAX_E, NCCL_INT32, wv.comm, ws));
@@ -646,7 +645,7 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
         if (tl) cudaEventRecord(wv.tl[3], ws);
         egemm::Args a1, a2;
-        gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, &a1, &a2);
+        gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, nullptr, &a1, &a2);
         rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, gemm_grid, ws);
         if (rc != PRICHS_OK) return rc;
         if (tl) cudaEventRecord(wv.tl[4], ws);
@@ -715,13 +714,13 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     h->K1 = d * mul; h->K2 = f * mul;
     h->Tcap = round_up(h->Tmax, SEG_PAD);
     h->resid_dtype = -1;
-    {
-        // PRICHS_FUSED_NORM=0 keeps the block entry point's pre-norm as a launch of its own (for comparison)
-        const char* fn = getenv("PRICHS_FUSED_NORM");
-        h->fuse_norm = !(fn && atoi(fn) == 0);
-        const char* fs = getenv("PRICHS_FUSED_SCAN");
-        h->fuse_scan = fs ? (atoi(fs) != 0) : -1;
-    }
+    h->fuse_norm = cfg->separate_prenorm == 0;
+    h->fuse_scan = cfg->scan_placement == 1 ? 1 : (cfg->scan_placement == 2 ? 0 : -1);
+    h->route_kernel = cfg->route_kernel;
+    h->router_ctas_per_sm = cfg->router_ctas_per_sm == 0 ? -1 : std::max(0, cfg->router_ctas_per_sm);
+    h->host_chunk = cfg->host_chunk_tokens > 0 ? std::max(256, cfg->host_chunk_tokens / 16 * 16) : 0;
+    h->rd_stall_tile = -1;
+    h->rd_wait_cycles = 4000000000LL;  // ~2 s, like the GEMM's waits
     h->n_waves = 1;
     if (world > 1) {
         const int want = cfg->ep_waves > 0 ? cfg->ep_waves : h->Tmax / 8192;
@@ -730,10 +729,13 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     // worst case per wave: every token of the wave, from every rank, picks experts of this rank
     // the first wave is the largest
     const long long tw_max = wave_begin(h->Tmax, h->n_waves, 1) + route::TILE_TOKENS;
-    long long recv = world == 1 ? (long long)h->Tmax * k
+    // all experts local: every expert owns a segment of Tcap rows (a token picks an expert at most once), so a row's
+    // place never depends on the totals
+    h->seg_stride = world == 1 ? h->Tcap : 0;
+    long long recv = world == 1 ? (long long)h->El * h->Tcap
                                 : (cfg->ep_max_recv_rows > 0 ? (long long)cfg->ep_max_recv_rows * tw_max / h->Tmax + 1
                                                              : (long long)world * tw_max * k);
-    const long long rw = (recv + (long long)h->El * (SEG_PAD - 1) + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
+    const long long rw = world == 1 ? recv : (recv + (long long)h->El * (SEG_PAD - 1) + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
     const long long rcap = rw * h->n_waves;
     if ((rcap + h->Tcap) * (long long)std::max(h->K1, h->K2) >= (1LL << 40) || rcap > (1LL << 30)) {
         const int tmax = h->Tmax;
@@ -775,6 +777,9 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->tile_counts, ntiles * route::MAX_E));
     A(dalloc(&h->tile_prefix, ntiles * route::MAX_E));
     A(dalloc(&h->mtile_slot, (size_t)h->Rcap / 128 + 1));
+    A(dalloc(&h->mtile_row, (size_t)h->Rcap / 128 + 1));
+    A(dalloc(&h->tile_state, ntiles * route::MAX_E + 4));
+    A(dalloc(&h->rd_ctl, 4));
     A(dalloc(&h->status, 2));  // [0] status word, [1] finished-CTA counter of the router's scan tail
     A(dalloc(&h->meta, 1));
     A(dalloc(&h->ep_zero, 8));
@@ -789,6 +794,9 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     }
     cudaMemset(h->bias, 0, route::MAX_E * sizeof(float));
     cudaMemset(h->status, 0, 2 * sizeof(int));
+    cudaMemset(h->tile_state, 0, (ntiles * route::MAX_E + 4) * sizeof(uint32_t));
+    cudaMemset(h->rd_ctl, 0, 4 * sizeof(int));
+    cudaMemset(h->mtile_row, 0, ((size_t)h->Rcap / 128 + 1) * sizeof(int));
     cudaMemset(h->pos, 0, (size_t)h->Tmax * 2 * sizeof(int));  // stale row maps always stay inside the buffers
     cudaMemset(h->meta, 0, sizeof(route::RouteMeta));
     cudaMemset(h->ep_zero, 0, 8 * sizeof(int));
@@ -820,33 +828,26 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
             rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the CTA-pair expert GEMM", egemm::PAIR_SMEM_BYTES);
     }
     {
-        // The CTA-pair kernel (256 x 256 tiles over two SMs) is the default; PRICHS_GEMM=single selects the
-        // one-CTA kernel (128 x 256 tiles), kept for comparison.
-        const char* sel = getenv("PRICHS_GEMM");
-        h->pair_gemm = !(sel && strcmp(sel, "single") == 0);
-        const char* rs = getenv("PRICHS_EP_RESERVE_SMS");
-        h->ep_reserve_sms = rs ? std::max(0, std::min(64, atoi(rs))) & ~1 : 20;
-        const char* ex = getenv("PRICHS_EP_EXCLUSIVE");
-        h->ep_copy_smem = (ex && atoi(ex) == 0) ? 0 : 8192;
-        const char* pd = getenv("PRICHS_PDL");
-        h->pdl = pd && atoi(pd) != 0;
-        const char* cm = getenv("PRICHS_EP_COMBINE_MODE");
-        h->ep_combine_mode = cm ? atoi(cm) : 1;
-        // Large bf16 batches with bf16-exact router weights can be routed by two alternative kernels, both
-        // bit-identical to the default one (eight warps in lock step per tile): PRICHS_ROUTER=warp (one independent
-        // warp per tile) and PRICHS_ROUTER=staged (rows streamed through a shared-memory ring with bulk copies, one
-        // consumer warp per stage). Measured on B200 all three take 20-21 us for 16384 tokens and 30-35 us for 32768
-        // inside a forward, so neither replaces the default.
-        const char* rk = getenv("PRICHS_ROUTER");
-        h->router_stages = std::min(route::ROUTER_TMA_MAX_STAGES, (227 * 1024 - route::router_tma_weight_bytes(d) - 128) / route::router_tma_stage_bytes(d));
-        const char* rst = getenv("PRICHS_ROUTER_STAGES");  // a shallower ring (2..4), for tests
-        if (rst && atoi(rst) >= 2) h->router_stages = std::min(h->router_stages, atoi(rst));
-        h->router_tma = rk && strcmp(rk, "staged") == 0 && h->mode != PRICHS_MODE_F32 && h->router_stages >= 2;
-        h->router_warp = rk && strcmp(rk, "warp") == 0 && h->mode != PRICHS_MODE_F32;
-        if (h->router_tma && rc == PRICHS_OK) {
-            const int bytes = route::router_tma_smem_bytes(d, h->router_stages);
-            if (cudaFuncSetAttribute(route::router_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
-                rc = fail(PRICHS_ERR_CUDA, "cannot reserve %d bytes of shared memory for the router", bytes);
+        // The CTA-pair kernel (256 x 256 tiles over two SMs) is the default; gemm_kernel = 1 selects the one-CTA
+        // kernel (128 x 256 tiles), kept for comparison.
+        h->pair_gemm = cfg->gemm_kernel != 1;
+        h->ep_reserve_sms = cfg->ep_reserve_sms < 0 ? 0 : (cfg->ep_reserve_sms == 0 ? 20 : std::min(64, cfg->ep_reserve_sms) & ~1);
+        h->ep_copy_smem = cfg->ep_shared_copy_sms ? 0 : 8192;
+        h->pdl = cfg->pdl != 0;
+        h->ep_combine_mode = cfg->ep_combine_mode == 1 ? 0 : (cfg->ep_combine_mode == 2 ? 2 : 1);
+        // single-pass route + place + dispatch kernel: as many ring stages as fit next to the router weights (one
+        // bf16 part when the weights are bf16 values, three when they are fp32 values; known at upload)
+        if (h->mode != PRICHS_MODE_F32 && world == 1) {
+            h->rd_stages[0] = rd_stages_for(d, 1);
+            h->rd_stages[1] = rd_stages_for(d, 3);
+            if (rc == PRICHS_OK && h->rd_stages[0] > 0 &&
+                cudaFuncSetAttribute(route::route_dispatch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     route::rd_smem_bytes(d, 1, h->rd_stages[0])) != cudaSuccess)
+                rc = fail(PRICHS_ERR_CUDA, "cannot reserve shared memory for the single-pass routing kernel");
+            if (rc == PRICHS_OK && h->rd_stages[1] > 0 &&
+                cudaFuncSetAttribute(route::route_dispatch_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     route::rd_smem_bytes(d, 3, h->rd_stages[1])) != cudaSuccess)
+                rc = fail(PRICHS_ERR_CUDA, "cannot reserve shared memory for the single-pass routing kernel");
         }
     }
     for (int i = 0; i < 7 && rc == PRICHS_OK; ++i)
@@ -886,7 +887,7 @@ int prichs_moe_destroy(prichs_moe_t* h) {
         if (wv.mtile_slot) cudaFree(wv.mtile_slot);
         if (wv.token) cudaFree(wv.token);
     }
-    void* ptrs[] = {h->xnorm, h->ep_zero, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
+    void* ptrs[] = {h->mtile_row, h->tile_state, h->rd_ctl, h->xnorm, h->ep_zero, h->w_gu, h->w_dn, h->w_rt, h->w_r8, h->bias, h->xs, h->xp, h->hbuf, h->ybuf, h->logits, h->gates,
                     h->sel, h->pos, h->tile_counts, h->tile_prefix, h->mtile_slot, h->status, h->meta, h->stage_x,
                     h->stage_r, h->stage_y};
     for (void* p : ptrs)
@@ -969,6 +970,7 @@ int prichs_moe_set_bias(prichs_moe_t* h, const float* host_bias, int n) {
     DeviceGuard guard(h->device);
     float tmp[route::MAX_E] = {0};
     memcpy(tmp, host_bias, n * sizeof(float));
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));  // a forward or a bias update may still be using the old values
     CUDA_TRY(cudaMemcpy(h->bias, tmp, sizeof(tmp), cudaMemcpyHostToDevice));
     return PRICHS_OK;
 }
@@ -978,6 +980,7 @@ int prichs_moe_get_bias(prichs_moe_t* h, float* host_bias, int n) {
     if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "router_bias has %d entries, the layer has %d experts", n, h->E);
     DeviceGuard guard(h->device);
     float tmp[route::MAX_E];
+    CUDA_TRY(cudaStreamSynchronize(h->last_stream));  // bias updates are enqueued on the forward's stream
     CUDA_TRY(cudaMemcpy(tmp, h->bias, sizeof(tmp), cudaMemcpyDeviceToHost));
     memcpy(host_bias, tmp, n * sizeof(float));
     return PRICHS_OK;
@@ -1038,12 +1041,42 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
 
     const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     mark();
-    // 1. router
     const bool pdl = h->pdl;
+    // Routing stage. Single pass (one kernel routes, places and dispatches) when the rows are bf16 as they arrive:
+    // from 1024 tokens up by default, always / never with route_kernel = 1 / 2. Otherwise three launches.
+    const int rd_stages = h->rd_stages[h->rt_nsplit == 1 ? 0 : 1];
+    const bool rd_possible = !f32mode && x_dtype == PRICHS_DTYPE_BF16 && !h->norm_w && rd_stages > 0;
+    const bool single_pass = rd_possible && (h->route_kernel == 1 || (h->route_kernel == 0 && !h->small_batch));
+    if (single_pass) {
+        route::RouteDispatchArgs ra;
+        memset(&ra, 0, sizeof(ra));
+        ra.x = reinterpret_cast<const bf16*>(x_dev);
+        ra.wrt = h->w_rt;
+        ra.bias = h->bias;
+        ra.T = T; ra.d = h->d; ra.E = E; ra.top_k = h->k; ra.stages = rd_stages;
+        ra.logits = logits; ra.sel = sel; ra.gates = gates; ra.pos = pos;
+        ra.tile_counts = h->tile_counts; ra.tile_prefix = h->tile_prefix;
+        ra.tile_state = h->tile_state; ra.ctl = h->rd_ctl;
+        ra.xp = h->xp; ra.seg_stride = h->seg_stride; ra.pad_rows = SEG_PAD;
+        ra.meta = h->meta; ra.mtile_slot = h->mtile_slot; ra.mtile_row = h->mtile_row;
+        ra.status = h->status;
+        ra.wait_cycles = h->rd_wait_cycles;
+        ra.stall_tile = h->rd_stall_tile;
+        const int grid = std::min(ntiles, h->sm_count);
+        if (h->rt_nsplit == 1)
+            LAUNCH_K(pdl, route::route_dispatch_kernel<1>, grid, route::RD_THREADS, route::rd_smem_bytes(h->d, 1, rd_stages), st, ra, cb);
+        else
+            LAUNCH_K(pdl, route::route_dispatch_kernel<3>, grid, route::RD_THREADS, route::rd_smem_bytes(h->d, 3, rd_stages), st, ra, cb);
+        LAUNCH_CHECK("route + dispatch");
+        mark();
+        mark();  // (no separate scan and dispatch stages: their time reads as zero)
+        mark();
+    } else {
+    // 1. router
     // 2. prefix sums + placement plan: by the last CTA of the router launch for small batches (decode), where a
     //    launch costs more than the work; as a launch of their own for large ones, where the tail would keep the
     //    whole router grid waiting on one CTA's latency chain for no gain (measured on B200: 2 us of 500 at
-    //    T = 16384) and the fp32-fidelity router. PRICHS_FUSED_SCAN=1 / 0 forces one or the other.
+    //    T = 16384) and the fp32-fidelity router. The config's scan_placement forces one or the other.
     const bool scan_in_router = !f32mode && (h->fuse_scan < 0 ? h->small_batch : h->fuse_scan != 0);
     route::ScanTail tail{};
     if (scan_in_router) {
@@ -1051,33 +1084,35 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         tail.tile_prefix = h->tile_prefix;
         tail.meta = h->meta;
         tail.mtile_slot = h->mtile_slot;
+        tail.mtile_row = h->mtile_row;
         tail.El = h->El;
         tail.cap_rows = h->Rcap;
         tail.pad_rows = SEG_PAD;
+        tail.seg_stride = h->seg_stride;
         tail.status = h->status;
     }
     rc = launch_router(h, x_dev, x_dtype, cb, T, logits, sel, gates, h->tile_counts, st, pdl, tail);
     if (rc != PRICHS_OK) return rc;
     mark();
     if (!scan_in_router) {
-        LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, E, h->El, 1, 0,
-                 h->Rcap, 1, SEG_PAD, h->status);
+        LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, h->mtile_row,
+                 E, h->El, 1, 0, h->Rcap, 1, SEG_PAD, h->seg_stride, h->status);
         LAUNCH_CHECK("scan");
     }
     mark();
     // 3. dispatch
-    route::PeerPtrs xp_peers, y_peers;
-    for (int i = 0; i < route::MAX_RANKS; ++i) {
-        xp_peers.p[i] = h->xp;
-        y_peers.p[i] = h->ybuf;
-    }
+    route::PeerPtrs xp_peers;
+    for (int i = 0; i < route::MAX_RANKS; ++i) xp_peers.p[i] = h->xp;
     LAUNCH_K(pdl, route::dispatch_kernel, (T + 7) / 8, 256, 0, st, a_shared, h->K1, T, (const int*)sel, (const int*)h->tile_prefix,
              (const route::RouteMeta*)h->meta, xp_peers, h->El, pos);
     LAUNCH_CHECK("dispatch");
     mark();
+    }
+    route::PeerPtrs y_peers;
+    for (int i = 0; i < route::MAX_RANKS; ++i) y_peers.p[i] = h->ybuf;
     // 4. gate|up GEMM + SwiGLU for the shared and all routed experts, 5. down GEMM
     egemm::Args a1, a2;
-    gemm_args(h, T, 0, &h->meta->n_routed_mtiles, h->mtile_slot, &a1, &a2);
+    gemm_args(h, T, 0, &h->meta->n_routed_mtiles, h->mtile_slot, h->mtile_row, &a1, &a2);
     rc = launch_expert_gemm(h, 0, tm_x, h->tm_xp, a1, h->sm_count, st, pdl);
     if (rc != PRICHS_OK) return rc;
     mark();
@@ -1169,9 +1204,8 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     // pass; counts are summed over the chunks. Expert-parallel handles run one pass (all ranks in lock step).
     int chunk = T;
     if (h->world == 1 && T >= 4096) {
-        // small chunks keep the un-overlapped first upload and last download short; PRICHS_HOST_CHUNK overrides
-        const char* hc = getenv("PRICHS_HOST_CHUNK");
-        chunk = hc ? std::max(256, atoi(hc) / 16 * 16) : (T >= 8192 ? 1024 : 2048);
+        // small chunks keep the un-overlapped first upload and last download short; the config's host_chunk_tokens overrides
+        chunk = h->host_chunk > 0 ? h->host_chunk : (T >= 8192 ? 1024 : 2048);
         while ((T + chunk - 1) / chunk > MAX_CHUNKS) chunk *= 2;
     }
     const int nchunks = (T + chunk - 1) / chunk;
@@ -1221,7 +1255,13 @@ int prichs_moe_sync_status(prichs_moe_t* h) {
     CUDA_TRY(cudaStreamSynchronize(h->last_stream));
     int s = 0;
     CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (s != 0) CUDA_TRY(cudaMemset(h->status, 0, sizeof(int)));  // reported once, then the handle goes on
+    if (s != 0) {
+        // reported once, then the handle goes on: the scratch state of the kernels that may have given up starts clean
+        CUDA_TRY(cudaMemset(h->status, 0, 2 * sizeof(int)));
+        const size_t ntiles = ((size_t)h->Tmax + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
+        CUDA_TRY(cudaMemset(h->tile_state, 0, (ntiles * route::MAX_E + 4) * sizeof(uint32_t)));
+        CUDA_TRY(cudaMemset(h->rd_ctl, 0, 4 * sizeof(int)));
+    }
     return translate_status(s);
 }
 
@@ -1272,23 +1312,14 @@ int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* expert_token_
     if (!h || !expert_token_counts) return fail(PRICHS_ERR_BAD_ARG, "null handle or counts");
     if (n != h->E) return fail(PRICHS_ERR_BAD_SHAPE, "counts has %d entries, the layer has %d experts", n, h->E);
     if (total_tokens == 0) return PRICHS_OK;  // the reference returns early (moe.rs:233-235)
-    for (int i = 0; i < n; ++i)
-        if (expert_token_counts[i] > 0x7fffffffull) return fail(PRICHS_ERR_BAD_ARG, "expert_token_counts[%d] does not fit 31 bits", i);
     DeviceGuard guard(h->device);
-    // Host-supplied counts: same arithmetic as the device kernel, applied through a scratch RouteMeta.
-    route::RouteMeta* tmp = nullptr;
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&tmp), sizeof(route::RouteMeta)));
-    route::RouteMeta m;
-    memset(&m, 0, sizeof(m));
-    for (int i = 0; i < n; ++i) m.total[i] = (int)expert_token_counts[i];
-    cudaError_t e = cudaMemcpy(tmp, &m, sizeof(m), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) {
-        route::bias_update_kernel<<<1, 32>>>(h->bias, tmp, h->E, h->k, gamma, (unsigned long long)total_tokens);
-        g_launches.fetch_add(1);
-        e = cudaDeviceSynchronize();
-    }
-    cudaFree(tmp);
-    if (e != cudaSuccess) return fail(PRICHS_ERR_CUDA, "bias update failed: %s", cudaGetErrorString(e));
+    // Host-supplied counts travel as kernel arguments: no allocation, no copy, no device-wide synchronisation. The
+    // launch goes to the stream of the handle's last forward, so it is ordered after the router that read the bias
+    // and before the next forward on that stream.
+    route::ExpertCounts hc;
+    for (int i = 0; i < route::MAX_E; ++i) hc.c[i] = i < n ? (unsigned long long)expert_token_counts[i] : 0ull;
+    route::bias_update_kernel<<<1, 32, 0, h->last_stream>>>(h->bias, nullptr, hc, h->E, h->k, gamma, (unsigned long long)total_tokens);
+    LAUNCH_CHECK("bias update");
     return PRICHS_OK;
 }
 
@@ -1297,7 +1328,16 @@ int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, size_t total_
     DeviceGuard guard(h->device);
     unsigned long long tot = total_tokens ? (unsigned long long)total_tokens : (unsigned long long)h->last_T * h->world;
     if (tot == 0) return PRICHS_OK;
-    route::bias_update_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(h->bias, h->meta, h->E, h->k, gamma, tot);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+    if (st != h->last_stream && h->last_T > 0) {
+        // another stream than the forward's: order the update after the forward that wrote the counts and read the bias
+        cudaEvent_t ev;
+        CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        cudaEventRecord(ev, h->last_stream);
+        cudaStreamWaitEvent(st, ev, 0);
+        cudaEventDestroy(ev);
+    }
+    route::bias_update_kernel<<<1, 32, 0, st>>>(h->bias, h->meta, route::ExpertCounts{}, h->E, h->k, gamma, tot);
     LAUNCH_CHECK("bias update");
     return PRICHS_OK;
 }
@@ -1538,7 +1578,6 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
     route::RouteMeta meta;
     CUDA_TRY(cudaMemcpy(&meta, h->meta, sizeof(meta), cudaMemcpyDeviceToHost));
     if (meta.overflow) return fail(PRICHS_ERR_CAPACITY, "the forward pass overflowed its permuted region");
-    const long long routed_rows = 128LL * meta.n_routed_mtiles;
 
     // un-transposed weight copies ([f,d] and [d,2f] per slot, K-major for the input-gradient products)
     if (!b.nat_valid) {
@@ -1568,6 +1607,7 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
     base.routed_base_tiles = h->Tcap / 128;
     base.n_routed_mtiles = &h->meta->n_routed_mtiles;
     base.mtile_slot = h->mtile_slot;
+    base.mtile_row = h->mtile_row;
     base.status = h->status;
 
     // 2. pre-activations again: [gate | up] = x . W_gu (the forward keeps only silu(gate) * up)
@@ -1591,7 +1631,7 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
         if (rc != PRICHS_OK) return rc;
     }
     // 4. SwiGLU backward
-    bwd::swiglu_bwd_kernel<<<4 * h->sm_count, 256, 0, st>>>(b.dh, b.gu, b.dgu, T, f, tcap, &h->meta->n_routed_mtiles);
+    bwd::swiglu_bwd_kernel<<<4 * h->sm_count, 256, 0, st>>>(b.dh, b.gu, b.dgu, T, f, tcap, &h->meta->n_routed_mtiles, h->mtile_row);
     LAUNCH_CHECK("SwiGLU backward");
     // 5. dX = d_gate . W_gate^T + d_up . W_up^T as one product over K = 2f   (model.rs:612-631, 702-722)
     {
@@ -1621,15 +1661,20 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
         LAUNCH_CHECK("router weight gradient");
     }
 
-    // 9. transposed copies: the weight-gradient products contract over rows
+    // 9. transposed copies: the weight-gradient products contract over rows. The shared expert's rows, then every
+    //    expert's segment of the permuted region (its rows rounded up to whole tile pairs)
     rc = bwd_transpose(a_shared, b.xT, T, d, d, R, st);
-    if (rc == PRICHS_OK) rc = bwd_transpose(h->xp, b.xT + tcap, routed_rows, d, h->K1, R, st);
     if (rc == PRICHS_OK) rc = bwd_transpose(h->hbuf, b.hT, T, f, h->K2, R, st);
-    if (rc == PRICHS_OK) rc = bwd_transpose(h->hbuf + (size_t)tcap * h->K2, b.hT + tcap, routed_rows, f, h->K2, R, st);
     if (rc == PRICHS_OK) rc = bwd_transpose(b.dyall, b.dyT, T, d, d, R, st);
-    if (rc == PRICHS_OK) rc = bwd_transpose(b.dyall + (size_t)tcap * d, b.dyT + tcap, routed_rows, d, d, R, st);
     if (rc == PRICHS_OK) rc = bwd_transpose(b.dgu, b.dguT, T, 2 * f, 2 * f, R, st);
-    if (rc == PRICHS_OK) rc = bwd_transpose(b.dgu + (size_t)tcap * 2 * f, b.dguT + tcap, routed_rows, 2 * f, 2 * f, R, st);
+    for (int e = 0; e < h->El && rc == PRICHS_OK; ++e) {
+        const long long n = round_up(meta.counts[e], SEG_PAD), r0 = meta.seg_base[e], k0 = tcap + r0;
+        if (n == 0) continue;
+        rc = bwd_transpose(h->xp + (size_t)r0 * h->K1, b.xT + k0, n, d, h->K1, R, st);
+        if (rc == PRICHS_OK) rc = bwd_transpose(h->hbuf + (size_t)k0 * h->K2, b.hT + k0, n, f, h->K2, R, st);
+        if (rc == PRICHS_OK) rc = bwd_transpose(b.dyall + (size_t)k0 * d, b.dyT + k0, n, d, d, R, st);
+        if (rc == PRICHS_OK) rc = bwd_transpose(b.dgu + (size_t)k0 * 2 * f, b.dguT + k0, n, 2 * f, 2 * f, R, st);
+    }
     if (rc != PRICHS_OK) return rc;
 
     // 10. weight gradients, one expert at a time: its rows are the K window [k0, k0 + n) of the transposed copies
@@ -1707,6 +1752,7 @@ int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void*
         case 13: base = h->bwd.dxall; size = rows_all * h->d * 2; break;
         case 14: base = h->bwd.scal; size = (size_t)h->Tmax * 2 * 4; break;
         case 15: base = h->bwd.dlog; size = (size_t)h->Tmax * route::MAX_E * 4; break;
+        case 16: base = h->mtile_row; size = ((size_t)h->Rcap / 128 + 1) * 4; break;
         default: return fail(PRICHS_ERR_BAD_ARG, "unknown buffer id %d", which);
     }
     if (!base) return fail(PRICHS_ERR_BAD_ARG, "buffer %d does not exist yet (no backward pass has run)", which);
@@ -1714,6 +1760,18 @@ int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_bytes, void*
     CUDA_TRY(cudaStreamSynchronize(h->last_stream));
     CUDA_TRY(cudaMemcpy(host_dst, static_cast<const char*>(base) + offset_bytes, bytes, cudaMemcpyDeviceToHost));
     return PRICHS_OK;
+}
+
+int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    switch (key) {
+        case 0: h->rd_stall_tile = (int)value; return PRICHS_OK;
+        case 1:
+            if (value < 1000) return fail(PRICHS_ERR_BAD_ARG, "wait budget must be at least 1000 cycles");
+            h->rd_wait_cycles = value;
+            return PRICHS_OK;
+        default: return fail(PRICHS_ERR_BAD_ARG, "unknown debug key %d", key);
+    }
 }
 
 int prichs_moe_enable_timing(prichs_moe_t* h, int on) {
@@ -1874,7 +1932,7 @@ extern "C" int prichs_moe_route_static(const void* x_dev, const float* router_de
                                                                                          sel2, gates2, tcount, nullptr, 0.0f, route::ScanTail{});
     LAUNCH_CHECK("router");
     const int cap_rows = (int)((RS_MAX_T * 2 + route::MAX_E * 128) / 128 * 128);
-    route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, E, E, 1, 0, cap_rows, 1, 128, status);
+    route::scan_kernel<<<1, 1024, 0, st>>>(tcount, tprefix, ntiles, meta, slots, nullptr, E, E, 1, 0, cap_rows, 1, 128, 0, status);
     LAUNCH_CHECK("scan");
     route_static_export_kernel<<<(T + 255) / 256, 256, 0, st>>>(logits8, sel2, gates2, meta, T, E, top_k, logits_dev, selected_dev,
                                                                gating_dev, counts_dev);

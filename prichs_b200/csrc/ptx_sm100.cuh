@@ -79,6 +79,14 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                  : "memory");
 }
 
+// Untiled bulk copy shared memory of this CTA -> global (bulk async-group completion). Both addresses 16-byte
+// aligned, size a multiple of 16 bytes. The source must have been written through the async proxy (a bulk load) or
+// made visible to it with fence_proxy_async().
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+                 : "memory");
+}
+
 // 2-D tiled TMA store shared -> global of one box (bulk async-group completion). ONE thread issues it after
 // the writers of the shared-memory box executed fence_proxy_async() and were synchronised with it.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int x, int y, const void* smem_src) {

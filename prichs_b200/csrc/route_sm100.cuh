@@ -53,11 +53,16 @@ struct PeerPtrs {
 //   the contract (the reference's result then depends on its sort's internals)
 //   gates from the RAW logits of the selected experts: exp(L_i - max) / (sum + 1e-9)   (ops.rs:233-245)
 // Writes logits [T,8], sel [T,2] (expert | rank-in-tile << 8, or -1), gates [T,2] and the tile's histogram.
-__device__ __forceinline__ void route_finish(const float (&L)[MAX_E], bool active, uint32_t lower_mask, int row,
-                                             int tile, int lane, const float* __restrict__ bias,
-                                             const ConceptBias& cb, int E, int top_k, float* __restrict__ logits,
-                                             int* __restrict__ sel, float* __restrict__ gates,
-                                             int* __restrict__ tile_counts) {
+// Returns what the lane selected (i2 = -1: one expert only; inactive lanes: i1 = 0, i2 = -1, unused) and, in lane
+// e < 8, the tile's count for expert e.
+struct RouteSel {
+    int i1, i2, r1, r2, my_count;
+};
+__device__ __forceinline__ RouteSel route_finish(const float (&L)[MAX_E], bool active, uint32_t lower_mask, int row,
+                                                 int tile, int lane, const float* __restrict__ bias,
+                                                 const ConceptBias& cb, int E, int top_k, float* __restrict__ logits,
+                                                 int* __restrict__ sel, float* __restrict__ gates,
+                                                 int* __restrict__ tile_counts) {
     int i1 = 0, i2 = -1;
     float l1 = 0.f, l2 = 0.f;
     if (active) {
@@ -121,6 +126,7 @@ __device__ __forceinline__ void route_finish(const float (&L)[MAX_E], bool activ
         *reinterpret_cast<int2*>(sel + (size_t)row * 2) = make_int2(i1 | (r1 << 8), i2 >= 0 ? (i2 | (r2 << 8)) : -1);
         *reinterpret_cast<float2*>(gates + (size_t)row * 2) = make_float2(g1, g2);
     }
+    return RouteSel{i1, i2, r1, r2, my_count};
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -145,9 +151,9 @@ constexpr int ROUTER_KB = 6;
 template <int NT, int SCAN_KEEP>
 __device__ __forceinline__ const int* scan_tiles(const int* tile_counts, int* __restrict__ tile_prefix, int ntiles,
                                                  RouteMeta* meta, int rank);
-__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world,
-                                               int rank, int cap_rows, int pad_rows, int* __restrict__ status,
-                                               const int* local_counts);
+__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int* __restrict__ mtile_row,
+                                               int E, int El, int world, int rank, int cap_rows, int pad_rows,
+                                               int seg_stride, int* __restrict__ status, const int* local_counts);
 
 // Work the last CTA of the router launch does when all experts are local: the prefix sums over the tile
 // histograms and the placement plan, which would otherwise be a one-CTA launch of their own between the router
@@ -157,7 +163,8 @@ struct ScanTail {
     int* tile_prefix;
     RouteMeta* meta;
     int* mtile_slot;
-    int El, cap_rows, pad_rows;
+    int* mtile_row;
+    int El, cap_rows, pad_rows, seg_stride;
     int* status;
 };
 
@@ -369,139 +376,148 @@ router_mma_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ xs, co
         if (s_last) {
             __threadfence();
             const int* totals = scan_tiles<ROUTER_WARPS * 32, 8>(tile_counts, tail.tile_prefix, ntiles, tail.meta, 0);
-            plan_from_cmat(tail.meta, tail.mtile_slot, E, tail.El, 1, 0, tail.cap_rows, tail.pad_rows, tail.status, totals);
+            plan_from_cmat(tail.meta, tail.mtile_slot, tail.mtile_row, E, tail.El, 1, 0, tail.cap_rows, tail.pad_rows, tail.seg_stride, tail.status, totals);
             if (threadIdx.x == 0) *tail.done = 0;
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Router for large bf16 batches with bf16-exact router weights: one WARP per 16-token tile, no shared memory and
-// no barrier. The warp walks the tile's K in 32-element slices with eight slices (8 KB) in flight at all times: a
-// ring of eight register slots, each refilled with the slice eight steps ahead as soon as it has been consumed.
-// Slice i feeds accumulator set i % 8, which therefore sees exactly the slices warp i % 8 of router_mma_kernel
-// sees, in the same order, and the eight sets are added in that kernel's warp order: the logits are bit-identical
-// to router_mma_kernel<1, false, false>. Where that kernel runs a tile on eight warps in lock step (loads, then a
-// barrier, then one warp selects while seven wait), here every warp is independent: with ~7-14 tiles in flight
-// per SM the loads of one tile overlap the selection of another, and the time of the launch is close to the time
-// one warp needs to stream its 48 KB.
-constexpr int ROUTER_WARP_CTA_WARPS = 4;
+// Route, place and dispatch in ONE pass over the tokens (all experts local, bf16 rows). A row is read from
+// global memory once, into shared memory, and leaves it twice -- to the segments of its two experts -- without
+// passing through registers; in between a warp computes the row's logits from the shared-memory copy.
+//
+// One persistent CTA per SM. A producer thread draws 16-token tiles from a global ticket counter and copies each
+// tile's rows with untiled bulk copies into a ring of `stages` buffers (full / empty mbarrier per stage). Consumer
+// warp w owns stage w:
+//   1. logits of the tile's 16 tokens on mma.sync m16n8k16 out of shared memory, arithmetic and summation order of
+//      router_mma_kernel<NSPLIT, false, false> (bit-identical logits); bias, top-2, gates, the tile's per-expert
+//      counts and each token's rank among the tile's earlier tokens (route_finish);
+//   2. the tile's exclusive per-expert prefix over all earlier tiles by decoupled look-back: the warp publishes its
+//      counts as "aggregate" words, reads the state words of the 32 tiles before it (one tile per lane), adds
+//      aggregates back to the nearest "inclusive" word, moves the window further back if there is none, and then
+//      publishes its own inclusive prefix. A state word carries its flag and its value together (2 + 30 bits), so
+//      no fence sits on this path. Tickets are drawn in order and a tile's rows are requested as soon as its ticket
+//      is drawn, so every earlier tile is already being worked on by a running CTA: the walk cannot wait on work
+//      that has not been scheduled.
+//   3. row of assignment (token, expert e) = e * seg_stride + prefix[e] + rank; the rows go from the stage buffer to
+//      the permuted region with bulk copies issued by the lanes that own the tokens; the stage is handed back to
+//      the producer when those copies have read it.
+// The warp that handles the last tile knows the totals and writes the routing summary and the GEMM's tile table.
+// The CTA that leaves last (counter in ctl[1]) returns tile_state and the ticket counter to zero, so a launch
+// leaves the scratch state as it found it and the kernel can be replayed from a CUDA graph.
+// Every wait (mbarriers, look-back) is bounded by `wait_cycles`; one that gives up raises the CTA's abort flag,
+// every role leaves its loop, in-flight copies are waited for, and the status word reports -5.
+constexpr int RD_MAX_STAGES = 4;
+constexpr int RD_THREADS = (RD_MAX_STAGES + 1) * 32;
+constexpr int RD_ROW_PAD = 64;  // bytes: the two rows a quarter-warp reads fall on disjoint banks
+constexpr uint32_t RD_AGG = 1u << 30, RD_INCL = 2u << 30, RD_VAL = (1u << 30) - 1u;
 
-__global__ void __launch_bounds__(ROUTER_WARP_CTA_WARPS * 32)
-router_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wrt, const float* __restrict__ bias,
-                   const ConceptBias cb, int T, int d, int E, int top_k, float* __restrict__ logits, int* __restrict__ sel,
-                   float* __restrict__ gates, int* __restrict__ tile_counts) {
-    ptx::grid_dep_launch();
-    ptx::grid_dep_wait();
-    const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-    const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
-    const int tile = blockIdx.x * ROUTER_WARP_CTA_WARPS + (threadIdx.x >> 5);
-    if (tile >= ntiles) return;
-    const int r0 = tile * TILE_TOKENS + g, r1 = r0 + 8;
-    const __nv_bfloat16* x0 = x + (size_t)min(r0, T - 1) * d + 8 * q;
-    const __nv_bfloat16* x1 = x + (size_t)min(r1, T - 1) * d + 8 * q;
-    const __nv_bfloat16* wl = wrt + (size_t)g * d + 8 * q;
+__host__ __device__ inline int rd_stage_bytes(int d) { return TILE_TOKENS * (2 * d + RD_ROW_PAD); }
+__host__ __device__ inline int rd_weight_bytes(int d, int nsplit) { return nsplit * MAX_E * (2 * d + RD_ROW_PAD); }
+__host__ __device__ inline int rd_smem_bytes(int d, int nsplit, int stages) {
+    return stages * rd_stage_bytes(d) + rd_weight_bytes(d, nsplit) + 2 * RD_MAX_STAGES * 8 + RD_MAX_STAGES * 4 + 16;
+}
 
-    constexpr int RING = ROUTER_WARPS;  // slices in flight = accumulator sets = warps of the lock-step kernel
-    float acc[RING][2][4];
+struct RouteDispatchArgs {
+    const __nv_bfloat16* x;    // [T, d] token rows
+    const __nv_bfloat16* wrt;  // [NSPLIT][8][d] transposed router weights
+    const float* bias;
+    int T, d, E, top_k, stages;
+    float* logits;
+    int* sel;
+    float* gates;
+    int* pos;
+    int* tile_counts;
+    int* tile_prefix;
+    uint32_t* tile_state;  // [ceil(T/16)][8] look-back words, all zero between launches
+    int* ctl;              // [0] next ticket, [1] CTAs that have left; both zero between launches
+    __nv_bfloat16* xp;     // permuted region, expert e's segment at row e * seg_stride
+    int seg_stride, pad_rows;
+    RouteMeta* meta;
+    int* mtile_slot;
+    int* mtile_row;
+    int* status;
+    long long wait_cycles;
+    int stall_tile;  // test knob: this tile never publishes its counts, so its successors' look-back runs out (-1: none)
+};
+
+__device__ __forceinline__ uint4 ld_relaxed_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_4(void* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Routing summary and GEMM tile table for fixed-stride segments, by one warp; lane e < 8 passes expert e's total.
+__device__ __forceinline__ void plan_fixed_stride_warp(RouteMeta* meta, int* __restrict__ mtile_slot, int* __restrict__ mtile_row,
+                                                       int E, int seg_stride, int pad_rows, int total, int lane) {
+    const uint32_t full = 0xffffffffu;
+    if (lane >= E) total = 0;
+    const int tiles = (total + pad_rows - 1) / pad_rows * (pad_rows / 128);
+    int inc = tiles;
 #pragma unroll
-    for (int w = 0; w < RING; ++w)
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[w][hh][i] = 0.f;
-    uint4 xa[RING], xb[RING];
-#pragma unroll
-    for (int w = 0; w < RING; ++w) {  // d is a multiple of 256: the first eight slices always exist
-        xa[w] = ptx::ld_stream_16(x0 + 32 * w);
-        xb[w] = ptx::ld_stream_16(x1 + 32 * w);
+    for (int o = 1; o < MAX_E; o <<= 1) {
+        const int n = __shfl_up_sync(full, inc, o);
+        if (lane >= o) inc += n;
     }
-    for (int kc = 0; kc < d; kc += RING * 32) {
+    const int tile0 = inc - tiles;
+    const int ntot = __shfl_sync(full, inc, MAX_E - 1);
+    const int recv = __reduce_add_sync(full, lane < MAX_E ? total : 0);
+    if (lane < MAX_E) {
+        meta->counts[lane] = total;
+        meta->total[lane] = total;
+        meta->src_off[lane] = 0;
+        meta->seg_base[lane] = lane < E ? lane * seg_stride : 0;
+        meta->cmat[lane] = total;
+    }
+    if (lane == 0) {
+        meta->n_routed_mtiles = ntot;
+        meta->recv_rows = recv;
+        meta->overflow = 0;
+    }
+    int t0s[MAX_E], tots[MAX_E];
 #pragma unroll
-        for (int w = 0; w < RING; ++w) {
-            const int kk = kc + 32 * w;
-            const uint4 a0 = xa[w], a1 = xb[w];
-            if (kk + RING * 32 < d) {  // refill the slot with the slice eight steps ahead
-                xa[w] = ptx::ld_stream_16(x0 + kk + RING * 32);
-                xb[w] = ptx::ld_stream_16(x1 + kk + RING * 32);
+    for (int e = 0; e < MAX_E; ++e) {
+        t0s[e] = __shfl_sync(full, tile0, e);
+        tots[e] = __shfl_sync(full, total, e);
+    }
+    for (int i = lane; i < ntot; i += 32) {
+        int le = 0, t0 = 0, tot = tots[0];
+#pragma unroll
+        for (int e = 1; e < MAX_E; ++e) {
+            if (e < E && i >= t0s[e]) {
+                le = e;
+                t0 = t0s[e];
+                tot = tots[e];
             }
-            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wl + kk));
-            ptx::mma_m16n8k16_bf16(acc[w][0], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-            ptx::mma_m16n8k16_bf16(acc[w][1], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
         }
+        const int j = i - t0;
+        mtile_slot[i] = (j * 128 >= tot) ? -1 - le : le;
+        mtile_row[i] = le * (seg_stride / 128) + j;
     }
-    // c[0..1]: row g, experts 2q, 2q+1; c[2..3]: row g+8; sets added in the order the lock-step kernel adds its warps
-    float c[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float v = 0.f;
-        v += acc[0][0][i] + acc[0][1][i];
-        c[i] = v;
-    }
-#pragma unroll
-    for (int w = 1; w < RING; ++w)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float v = 0.f;
-            v += acc[w][0][i] + acc[w][1][i];
-            c[i] += v;
-        }
-    float L[MAX_E];
-    const int qbase = lane & ~3;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
-        const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
-        const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
-        const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
-        L[2 * j] = (q == 0) ? t0 : t2;
-        L[2 * j + 1] = (q == 0) ? t1 : t3;
-    }
-    const int row = (q == 0) ? r0 : r1;
-    const bool active = (q < 2) && (row < T);
-    const uint32_t below = (1u << (4 * g)) - 1u;
-    const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
-    route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
 }
 
-// ---------------------------------------------------------------------------------------------------
-// Alternative router for large bf16 batches with bf16-exact router weights (opt-in): the arithmetic of
-// router_mma_kernel<1, false, false> in the same order (bit-identical logits), with the rows streamed through
-// shared memory. One persistent CTA per SM; a producer thread copies the 16-token tiles (16 contiguous rows) with
-// untiled bulk copies, one per row, into a ring of `stages` buffers, each with a full and an empty mbarrier, so
-// the ring's 100-200 KB per SM are in flight whatever the consumers do. Consumer warp w owns stage w: it waits
-// for its tile, walks all of K out of shared memory (router weights are staged there too; rows of both are padded
-// by 64 bytes so that the two rows a quarter-warp touches fall on disjoint banks) into eight accumulator sets --
-// slice i feeds set i % 8, the slices warp i % 8 of the lock-step kernel sees, added in that kernel's warp order --
-// hands the stage back and selects. No CTA-wide barrier inside the loop: the warps are independent.
-// Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag, every role leaves its loop, the
-// producer lets its copies land, and the status word reports it.
-constexpr int ROUTER_TMA_MAX_STAGES = 4;
-constexpr int ROUTER_TMA_THREADS = (ROUTER_TMA_MAX_STAGES + 1) * 32;
-constexpr int ROUTER_TMA_ROW_PAD = 64;
-constexpr long long ROUTER_WAIT_CYCLES = 4000000000LL;
-
-__host__ __device__ inline int router_tma_stage_bytes(int d) { return TILE_TOKENS * (2 * d + ROUTER_TMA_ROW_PAD); }
-__host__ __device__ inline int router_tma_weight_bytes(int d) { return MAX_E * (2 * d + ROUTER_TMA_ROW_PAD); }
-__host__ __device__ inline int router_tma_smem_bytes(int d, int stages) {
-    return stages * router_tma_stage_bytes(d) + router_tma_weight_bytes(d) + 2 * ROUTER_TMA_MAX_STAGES * 8 + 16;
-}
-
-__global__ void __launch_bounds__(ROUTER_TMA_THREADS, 1)
-router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wrt, const float* __restrict__ bias,
-                  const ConceptBias cb, int T, int d, int E, int top_k, float* __restrict__ logits, int* __restrict__ sel,
-                  float* __restrict__ gates, int* __restrict__ tile_counts, int stages, int* __restrict__ status) {
+template <int NSPLIT>
+__global__ void __launch_bounds__(RD_THREADS, 1)
+route_dispatch_kernel(const __grid_constant__ RouteDispatchArgs a, const ConceptBias cb) {
     extern __shared__ __align__(128) uint8_t rsm[];
-    const int rowb = 2 * d + ROUTER_TMA_ROW_PAD;
+    const int d = a.d, stages = a.stages, T = a.T;
+    const int rowb = 2 * d + RD_ROW_PAD;
     const int stage_bytes = TILE_TOKENS * rowb;
-    uint8_t* wsm = rsm + (size_t)stages * stage_bytes;  // router weights, [8][rowb]
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(wsm + MAX_E * rowb);
-    uint64_t* empty_bar = full_bar + ROUTER_TMA_MAX_STAGES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + ROUTER_TMA_MAX_STAGES);
+    uint8_t* wsm = rsm + (size_t)stages * stage_bytes;  // router weights, [NSPLIT][8][rowb]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(wsm + NSPLIT * MAX_E * rowb);
+    uint64_t* empty_bar = full_bar + RD_MAX_STAGES;
+    volatile int* tile_of_stage = reinterpret_cast<volatile int*>(empty_bar + RD_MAX_STAGES);
+    volatile int* abort_flag = tile_of_stage + RD_MAX_STAGES;
+    __shared__ int s_last;
 
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full = 0xffffffffu;
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
@@ -510,41 +526,52 @@ router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
-    // the transposed router weights [8][d] into padded shared-memory rows, 16 bytes per thread and step
-    for (int i = threadIdx.x; i < MAX_E * (d / 8); i += ROUTER_TMA_THREADS) {
-        const int e = i / (d / 8), c = i - e * (d / 8);
-        *reinterpret_cast<uint4*>(wsm + (size_t)e * rowb + 16 * c) = __ldg(reinterpret_cast<const uint4*>(wrt + (size_t)e * d) + c);
+    // the transposed router weights into padded shared-memory rows, 16 bytes per thread and step
+    for (int i = threadIdx.x; i < NSPLIT * MAX_E * (d / 8); i += RD_THREADS) {
+        const int r = i / (d / 8), c = i - r * (d / 8);
+        *reinterpret_cast<uint4*>(wsm + (size_t)r * rowb + 16 * c) = __ldg(reinterpret_cast<const uint4*>(a.wrt + (size_t)r * d) + c);
     }
     __syncthreads();
     const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
-    const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
-    if (warp == ROUTER_TMA_MAX_STAGES) {
+    if (warp == RD_MAX_STAGES) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
-            int issued = 0;
-            bool ok = true;
-            for (int it = 0; it < my_tiles; ++it) {
-                const int s = it % stages;
-                const uint32_t ph = (uint32_t)((it / stages) & 1);
-                if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, ROUTER_WAIT_CYCLES)) {
+            int loads = 0, stops = 0;
+            bool ok = true, more = true;
+            for (int n = 0; ok; ++n) {
+                const int s = n % stages;
+                const uint32_t ph = (uint32_t)((n / stages) & 1);
+                if (!ptx::mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.wait_cycles)) {
                     ok = false;
                     break;
                 }
-                const int tile = blockIdx.x + it * gridDim.x;
-                const int rows = min(TILE_TOKENS, T - tile * TILE_TOKENS);
-                uint8_t* dst = rsm + (size_t)s * stage_bytes;
-                ptx::mbar_expect_tx(&full_bar[s], (uint32_t)(rows * 2 * d));
-                for (int r = 0; r < rows; ++r)
-                    ptx::bulk_load_1d(dst + (size_t)r * rowb, x + ((size_t)tile * TILE_TOKENS + r) * d, (uint32_t)(2 * d), &full_bar[s]);
-                ++issued;
+                int tile = -1;
+                if (more) {
+                    tile = atomicAdd(a.ctl, 1);
+                    if (tile >= ntiles) {
+                        tile = -1;
+                        more = false;
+                    }
+                }
+                tile_of_stage[s] = tile;
+                if (tile >= 0) {
+                    const int rows = min(TILE_TOKENS, T - tile * TILE_TOKENS);
+                    uint8_t* dst = rsm + (size_t)s * stage_bytes;
+                    ptx::mbar_expect_tx(&full_bar[s], (uint32_t)(rows * 2 * d));
+                    for (int r = 0; r < rows; ++r)
+                        ptx::bulk_load_1d(dst + (size_t)r * rowb, a.x + ((size_t)tile * TILE_TOKENS + r) * d, (uint32_t)(2 * d), &full_bar[s]);
+                    ++loads;
+                } else {
+                    ptx::mbar_arrive(&full_bar[s]);  // tells the stage's consumer that no tile follows
+                    if (++stops == stages) break;
+                }
             }
             if (!ok) {
                 // leaving early: the copies already in flight must land before this CTA's shared memory goes away
-                for (int i = max(0, issued - stages); i < issued; ++i) {
+                for (int i = max(0, loads - stages); i < loads; ++i) {
                     const long long t0 = clock64();
-                    while (!ptx::mbar_try_wait(&full_bar[i % stages], (uint32_t)((i / stages) & 1)) &&
-                           clock64() - t0 < ROUTER_WAIT_CYCLES / 16) {
+                    while (!ptx::mbar_try_wait(&full_bar[i % stages], (uint32_t)((i / stages) & 1)) && clock64() - t0 < a.wait_cycles) {
                     }
                 }
             }
@@ -552,71 +579,177 @@ router_tma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     } else if (warp < stages) {
         // ---------------------------------------------------------------- consumer warp of stage `warp`
         const int g = lane >> 2, q = lane & 3;
-        const uint8_t* r0p = rsm + (size_t)warp * stage_bytes + (size_t)g * rowb + 16 * q;
+        uint8_t* stage = rsm + (size_t)warp * stage_bytes;
+        const uint8_t* r0p = stage + (size_t)g * rowb + 16 * q;
         const uint8_t* r1p = r0p + 8 * (size_t)rowb;
         const uint8_t* wp = wsm + (size_t)g * rowb + 16 * q;
-        for (int it = warp, n = 0; it < my_tiles; it += stages, ++n) {
-            const int tile = blockIdx.x + it * gridDim.x;
-            if (!ptx::mbar_wait_bounded(&full_bar[warp], (uint32_t)(n & 1), abort_flag, ROUTER_WAIT_CYCLES)) break;
-            float acc[ROUTER_WARPS][2][4];
+        for (int n = 0;; ++n) {
+            // the vote keeps the warp converged for the warp-wide operations below
+            if (!__all_sync(full, ptx::mbar_wait_bounded(&full_bar[warp], (uint32_t)(n & 1), abort_flag, a.wait_cycles))) break;
+            const int tile = tile_of_stage[warp];
+            if (tile < 0) break;
+            // ---- 1. logits: NSPLIT passes over K (small parts first), eight accumulator sets per pass, one per warp
+            //         of the lock-step kernel, added in that kernel's order
+            float cw[ROUTER_WARPS][4];
 #pragma unroll
             for (int w = 0; w < ROUTER_WARPS; ++w)
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh)
+                for (int i = 0; i < 4; ++i) cw[w][i] = 0.f;
+#pragma unroll 1
+            for (int s = NSPLIT - 1; s >= 0; --s) {
+                float acc[ROUTER_WARPS][2][4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[w][hh][i] = 0.f;
-            for (int kc = 0; kc < d; kc += ROUTER_WARPS * 32) {
+                for (int w = 0; w < ROUTER_WARPS; ++w)
 #pragma unroll
-                for (int w = 0; w < ROUTER_WARPS; ++w) {
-                    const int kb = 2 * (kc + 32 * w);
-                    const uint4 a0 = *reinterpret_cast<const uint4*>(r0p + kb);
-                    const uint4 a1 = *reinterpret_cast<const uint4*>(r1p + kb);
-                    const uint4 wv = *reinterpret_cast<const uint4*>(wp + kb);
-                    ptx::mma_m16n8k16_bf16(acc[w][0], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-                    ptx::mma_m16n8k16_bf16(acc[w][1], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[w][hh][i] = 0.f;
+                const uint8_t* wps = wp + (size_t)s * MAX_E * rowb;
+                for (int kc = 0; kc < d; kc += ROUTER_WARPS * 32) {
+#pragma unroll
+                    for (int w = 0; w < ROUTER_WARPS; ++w) {
+                        const int kb = 2 * (kc + 32 * w);
+                        const uint4 a0 = *reinterpret_cast<const uint4*>(r0p + kb);
+                        const uint4 a1 = *reinterpret_cast<const uint4*>(r1p + kb);
+                        const uint4 wv = *reinterpret_cast<const uint4*>(wps + kb);
+                        ptx::mma_m16n8k16_bf16(acc[w][0], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+                        ptx::mma_m16n8k16_bf16(acc[w][1], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                    }
                 }
+#pragma unroll
+                for (int w = 0; w < ROUTER_WARPS; ++w)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cw[w][i] += acc[w][0][i] + acc[w][1][i];
             }
-            // the tile has been read: hand the stage back to the producer
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty_bar[warp]);
-
-            // sets added in the order the lock-step kernel adds its warps
             float c[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float v = 0.f;
-                v += acc[0][0][i] + acc[0][1][i];
-                c[i] = v;
-            }
+            for (int i = 0; i < 4; ++i) c[i] = cw[0][i];
 #pragma unroll
             for (int w = 1; w < ROUTER_WARPS; ++w)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float v = 0.f;
-                    v += acc[w][0][i] + acc[w][1][i];
-                    c[i] += v;
-                }
+                for (int i = 0; i < 4; ++i) c[i] += cw[w][i];
             float L[MAX_E];
             const int qbase = lane & ~3;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float t0 = __shfl_sync(0xffffffffu, c[0], qbase + j);
-                const float t1 = __shfl_sync(0xffffffffu, c[1], qbase + j);
-                const float t2 = __shfl_sync(0xffffffffu, c[2], qbase + j);
-                const float t3 = __shfl_sync(0xffffffffu, c[3], qbase + j);
+                const float t0 = __shfl_sync(full, c[0], qbase + j);
+                const float t1 = __shfl_sync(full, c[1], qbase + j);
+                const float t2 = __shfl_sync(full, c[2], qbase + j);
+                const float t3 = __shfl_sync(full, c[3], qbase + j);
                 L[2 * j] = (q == 0) ? t0 : t2;
                 L[2 * j + 1] = (q == 0) ? t1 : t3;
             }
-            const int r0 = tile * TILE_TOKENS + g;
-            const int row = (q == 0) ? r0 : r0 + 8;
+            const int lrow = (q == 0) ? g : g + 8;  // this lane's token inside the tile (lanes q < 2)
+            const int row = tile * TILE_TOKENS + lrow;
             const bool active = (q < 2) && (row < T);
             const uint32_t below = (1u << (4 * g)) - 1u;
             const uint32_t lower_mask = (q == 0) ? (below & 0x11111111u) : (0x11111111u | (below & 0x22222222u));
-            route_finish(L, active, lower_mask, row, tile, lane, bias, cb, E, top_k, logits, sel, gates, tile_counts);
+            const RouteSel rs = route_finish(L, active, lower_mask, row, tile, lane, a.bias, cb, a.E, a.top_k, a.logits, a.sel, a.gates,
+                                             a.tile_counts);
+
+            // ---- 2. exclusive prefix of this tile's counts over all earlier tiles (decoupled look-back)
+            uint32_t* my_state = a.tile_state + (size_t)tile * MAX_E;
+            const bool publish = tile != a.stall_tile;
+            int run[MAX_E];
+#pragma unroll
+            for (int e = 0; e < MAX_E; ++e) run[e] = 0;
+            bool ok = true;
+            if (tile > 0) {
+                if (publish && lane < MAX_E) st_relaxed_4(my_state + lane, RD_AGG | (uint32_t)rs.my_count);
+                uint32_t open = 0xffu;  // experts whose walk has not yet met an inclusive prefix (warp-uniform)
+                int base = tile - 1;
+                const long long t_start = clock64();
+                while (open) {
+                    const int p = base - lane;
+                    uint4 w0 = make_uint4(RD_INCL, RD_INCL, RD_INCL, RD_INCL), w1 = w0;  // before tile 0: prefix 0
+                    if (p >= 0) {
+                        w0 = ld_relaxed_16(a.tile_state + (size_t)p * MAX_E);
+                        w1 = ld_relaxed_16(a.tile_state + (size_t)p * MAX_E + 4);
+                    }
+                    const uint32_t w[MAX_E] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    uint32_t incl_m[MAX_E], need_m[MAX_E];
+                    bool usable = true;
+#pragma unroll
+                    for (int e = 0; e < MAX_E; ++e) {
+                        const uint32_t flag = w[e] >> 30;
+                        incl_m[e] = __ballot_sync(full, flag == 2u);
+                        const uint32_t unset = __ballot_sync(full, flag == 0u);
+                        // lanes up to and including the nearest inclusive word (all 32 when the window has none)
+                        need_m[e] = incl_m[e] ? ((2u << (__ffs(incl_m[e]) - 1)) - 1u) : full;
+                        if (((open >> e) & 1u) && (unset & need_m[e])) usable = false;
+                    }
+                    if (!usable) {
+                        // some earlier tile has not published yet: look at the same window again
+                        const bool give_up = __shfl_sync(full, (int)(clock64() - t_start > a.wait_cycles || *abort_flag != 0), 0) != 0;
+                        if (give_up) {
+                            ok = false;
+                            break;
+                        }
+                        continue;
+                    }
+#pragma unroll
+                    for (int e = 0; e < MAX_E; ++e) {
+                        if ((open >> e) & 1u) {
+                            const int v = ((need_m[e] >> lane) & 1u) ? (int)(w[e] & RD_VAL) : 0;
+                            run[e] += __reduce_add_sync(full, v);
+                            if (incl_m[e]) open &= ~(1u << e);
+                        }
+                    }
+                    base -= 32;
+                }
+            }
+            if (!ok) {
+                if (lane == 0) *abort_flag = 1;
+                break;
+            }
+            int mine = 0;  // lane e < 8: exclusive prefix of expert e
+#pragma unroll
+            for (int e = 0; e < MAX_E; ++e) mine = (lane == e) ? run[e] : mine;
+            if (lane < MAX_E) {
+                if (publish) st_relaxed_4(my_state + lane, RD_INCL | (uint32_t)(mine + rs.my_count));
+                a.tile_prefix[(size_t)tile * MAX_E + lane] = mine;
+            }
+            if (tile == ntiles - 1)
+                plan_fixed_stride_warp(a.meta, a.mtile_slot, a.mtile_row, a.E, a.seg_stride, a.pad_rows, mine + rs.my_count, lane);
+
+            // ---- 3. rows to their segments, straight out of the stage buffer
+            if (active) {
+                int e1 = 0, e2 = 0;
+#pragma unroll
+                for (int e = 0; e < MAX_E; ++e) {
+                    e1 = (rs.i1 == e) ? run[e] : e1;
+                    e2 = (rs.i2 == e) ? run[e] : e2;
+                }
+                const int p1 = rs.i1 * a.seg_stride + e1 + rs.r1;
+                const int p2 = rs.i2 >= 0 ? rs.i2 * a.seg_stride + e2 + rs.r2 : -1;
+                *reinterpret_cast<int2*>(a.pos + (size_t)row * 2) = make_int2(p1, p2);
+                const uint8_t* src = stage + (size_t)lrow * rowb;
+                ptx::bulk_store_1d(a.xp + (size_t)p1 * d, src, (uint32_t)(2 * d));
+                if (p2 >= 0) ptx::bulk_store_1d(a.xp + (size_t)p2 * d, src, (uint32_t)(2 * d));
+                ptx::bulk_commit();
+                ptx::bulk_wait_read<0>();
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty_bar[warp]);
         }
+        ptx::bulk_wait_all();  // this lane's copies have been written before the CTA leaves
     }
     __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicExch(status, -5);
+    if (threadIdx.x == 0) {
+        const int aborted = *abort_flag;
+        if (aborted) atomicExch(a.status, -5);
+        // Every ticket of this CTA has been drawn and every look-back of its warps has ended (barrier above). The CTA
+        // that leaves last therefore sees no reader or writer of the scratch state any more and clears it.
+        s_last = (atomicAdd(a.ctl + 1, 1) == (int)gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        for (int i = threadIdx.x; i < ntiles * MAX_E / 4; i += RD_THREADS) reinterpret_cast<uint4*>(a.tile_state)[i] = make_uint4(0, 0, 0, 0);
+        if (threadIdx.x == 0) {
+            a.ctl[0] = 0;
+            a.ctl[1] = 0;
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -687,14 +820,22 @@ router_f32_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xs, c
 // ---------------------------------------------------------------------------------------------------
 // Placement plan from the counts matrix (one CTA). For every expert e, owned by rank e / El:
 //   total[e] = sum_s cmat[s][e],  src_off[e] = sum_{s < rank} cmat[s][e],
-//   seg_base[e] = sum of the padded totals (to pad_rows, a multiple of 128) of the owner's lower experts.
-// For the local experts it also fills the m-tile -> weight-slot table the grouped GEMM walks.
+//   seg_base[e] = row, in the owner's permuted region, where expert e's segment starts:
+//     seg_stride == 0 (expert parallel): the padded totals (to pad_rows, a multiple of 128) of the owner's lower
+//                     experts, so the region is dense;
+//     seg_stride > 0  (all experts local): le * seg_stride -- every expert has a segment of fixed capacity, so a
+//                     row's place depends only on the rows before it, never on the totals (this is what lets one
+//                     pass over the tokens route and place them).
+// For the local experts it also fills the table the grouped GEMM walks: entry i is the i-th 128-row tile that
+// holds rows, mtile_row[i] its tile index inside the region (null = dense region, tile i is entry i) and
+// mtile_slot[i] its weight slot. A segment contributes whole pad_rows blocks; a 128-row tile of such a block that
+// holds only padding rows is marked (-1 - slot).
 // `local_counts` (single rank only): the totals in shared memory, straight from the scan, so that this plan
 // reads nothing back from global memory; null = take them from meta->cmat.
-__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El,
-                                               int world, int rank, int cap_rows, int pad_rows, int* __restrict__ status,
-                                               const int* local_counts) {
-    __shared__ int s_total[MAX_E], s_base[MAX_E + 1], s_over;
+__device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict__ mtile_slot, int* __restrict__ mtile_row,
+                                               int E, int El, int world, int rank, int cap_rows, int pad_rows,
+                                               int seg_stride, int* __restrict__ status, const int* local_counts) {
+    __shared__ int s_total[MAX_E], s_base[MAX_E + 1], s_tile0[MAX_E + 1], s_over;
     const int tid = threadIdx.x;
     if (tid < MAX_E) {
         int tot = 0, off = 0;
@@ -715,39 +856,47 @@ __device__ __forceinline__ void plan_from_cmat(RouteMeta* meta, int* __restrict_
     }
     __syncthreads();
     if (tid == 0) {
-        int recv = 0, local_rows = 0, over = 0;
+        int recv = 0, over = 0;
         for (int o = 0; o < world; ++o) {
-            int base = 0;
+            int base = 0, tiles = 0;
             for (int le = 0; le < El; ++le) {
                 const int e = o * El + le;
+                const int padded = (s_total[e] + pad_rows - 1) / pad_rows * pad_rows;
+                if (seg_stride > 0) {
+                    base = le * seg_stride;
+                    if (padded > seg_stride) over = 1;
+                }
                 meta->seg_base[e] = base;
                 if (o == rank) {
                     s_base[le] = base;
+                    s_tile0[le] = tiles;
                     recv += s_total[e];
                 }
-                base += (s_total[e] + pad_rows - 1) / pad_rows * pad_rows;
+                base += padded;
+                tiles += padded / 128;
             }
             // every rank evaluates every owner's region, so that all of them skip the exchange together
             if (base > cap_rows) over = 1;
             if (o == rank) {
                 s_base[El] = base;
-                local_rows = base;
+                s_tile0[El] = tiles;
             }
         }
         s_over = over;
         meta->overflow = over;
         meta->recv_rows = recv;
-        meta->n_routed_mtiles = over ? 0 : local_rows / 128;
+        meta->n_routed_mtiles = over ? 0 : s_tile0[El];
         if (over) atomicExch(status, -2);
     }
     __syncthreads();
-    const int ntiles = s_over ? 0 : s_base[El] / 128;
+    const int ntiles = s_over ? 0 : s_tile0[El];
     for (int i = tid; i < ntiles; i += blockDim.x) {
         int le = 0;
-        while (le + 1 < El && i * 128 >= s_base[le + 1]) ++le;
-        // tiles that hold only padding rows are marked (-1 - slot): the GEMM kernels skip them
-        const bool padding_only = i * 128 >= s_base[le] + s_total[rank * El + le];
+        while (le + 1 < El && i >= s_tile0[le + 1]) ++le;
+        const int j = i - s_tile0[le];  // tile inside the segment
+        const bool padding_only = j * 128 >= s_total[rank * El + le];
         mtile_slot[i] = padding_only ? -1 - le : le;
+        if (mtile_row != nullptr) mtile_row[i] = s_base[le] / 128 + j;
     }
 }
 
@@ -851,19 +1000,20 @@ __device__ __forceinline__ const int* scan_tiles(const int* tile_counts, int* __
 // in the same launch.
 __global__ void __launch_bounds__(1024)
 scan_kernel(const int* tile_counts, int* __restrict__ tile_prefix, int ntiles, RouteMeta* meta,
-            int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows, int fuse_plan,
-            int pad_rows, int* __restrict__ status) {
+            int* __restrict__ mtile_slot, int* __restrict__ mtile_row, int E, int El, int world, int rank, int cap_rows,
+            int fuse_plan, int pad_rows, int seg_stride, int* __restrict__ status) {
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
     const int* totals = scan_tiles<1024, 2>(tile_counts, tile_prefix, ntiles, meta, rank);
-    if (fuse_plan) plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status, world == 1 ? totals : nullptr);
+    if (fuse_plan)
+        plan_from_cmat(meta, mtile_slot, mtile_row, E, El, world, rank, cap_rows, pad_rows, seg_stride, status, world == 1 ? totals : nullptr);
 }
 
 // Placement plan as its own launch (expert-parallel mode, after the counts of all ranks were gathered).
 __global__ void __launch_bounds__(256)
 plan_kernel(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int world, int rank, int cap_rows,
             int pad_rows, int* __restrict__ status) {
-    plan_from_cmat(meta, mtile_slot, E, El, world, rank, cap_rows, pad_rows, status, nullptr);
+    plan_from_cmat(meta, mtile_slot, nullptr, E, El, world, rank, cap_rows, pad_rows, 0, status, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -1070,12 +1220,18 @@ rmsnorm_rows_kernel(const void* __restrict__ x, const float* __restrict__ weight
 // ---------------------------------------------------------------------------------------------------
 // b_i += gamma * (top_k / E - count_i / total_tokens), each operation rounded on its own like the
 // reference's f32 arithmetic (moe.rs:237-244). count_i is the total over all ranks.
-__global__ void bias_update_kernel(float* __restrict__ bias, const RouteMeta* __restrict__ meta, int E, int top_k,
-                                   float gamma, unsigned long long total_tokens) {
+// The counts come from the routing summary of the last forward (`meta`) or, when it is null, from the kernel
+// arguments (`host_counts`, the reference's call shape with host-side counts).
+struct ExpertCounts {
+    unsigned long long c[MAX_E];
+};
+__global__ void bias_update_kernel(float* __restrict__ bias, const RouteMeta* __restrict__ meta, const ExpertCounts host_counts,
+                                   int E, int top_k, float gamma, unsigned long long total_tokens) {
     const int i = threadIdx.x;
     if (i >= E || total_tokens == 0ull) return;
+    const unsigned long long count = meta != nullptr ? (unsigned long long)meta->total[i] : host_counts.c[i];
     const float target_load = __fdiv_rn((float)top_k, (float)E);
-    const float actual_load = __fdiv_rn((float)(unsigned long long)meta->total[i], (float)total_tokens);
+    const float actual_load = __fdiv_rn((float)count, (float)total_tokens);
     const float diff = __fsub_rn(target_load, actual_load);
     bias[i] = __fadd_rn(bias[i], __fmul_rn(gamma, diff));
 }

@@ -66,7 +66,7 @@ class MoEStash:
 class MoELayer:
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int, top_k: int, *, seed=None,
                  mode: str = "bf16", max_tokens: int = 0, device: int = -1, ep_world: int = 1, ep_rank: int = 0,
-                 ep_max_recv_rows: int = 0, ep_waves: int = 0, init: bool = True):
+                 ep_max_recv_rows: int = 0, ep_waves: int = 0, init: bool = True, **tuning):
         rng = np.random.default_rng(seed)
         self.hidden_dim, self.intermediate_dim = int(hidden_dim), int(intermediate_dim)
         self.top_k = int(top_k)
@@ -84,6 +84,11 @@ class MoELayer:
         self.mode = {"bf16": _capi.MODE_BF16, "f32": _capi.MODE_F32}[mode]
         self._device, self._ep_world, self._ep_rank, self._ep_max_recv = device, ep_world, ep_rank, ep_max_recv_rows
         self._ep_waves = int(ep_waves)
+        # tuning fields of prichs_moe_config_t (route_kernel, gemm_kernel, pdl, ...); absent = 0 = the default
+        unknown = set(tuning) - set(_capi.TUNING_FIELDS)
+        if unknown:
+            raise TypeError(f"unknown MoELayer option(s): {sorted(unknown)}")
+        self._tuning = {k: int(v) for k, v in tuning.items()}
         self._h = C.c_void_p()
         self._max_tokens = 0
         self._want_max_tokens = int(max_tokens)
@@ -148,6 +153,8 @@ class MoELayer:
             cap = max(T, self._want_max_tokens, 1)
             cfg = _capi.Config(self.hidden_dim, self.intermediate_dim, self._num_experts, self.top_k, cap, self.mode,
                                self._device, self._ep_world, self._ep_rank, self._ep_max_recv, self._ep_waves)
+            for name, value in self._tuning.items():
+                setattr(cfg, name, value)
             h = C.c_void_p()
             _check(L.prichs_moe_create(C.byref(cfg), C.byref(h)))
             self._h, self._max_tokens, self._weights_dirty = h, cap, True
@@ -356,6 +363,11 @@ class MoELayer:
     def token_capacity(self) -> int:
         """max_tokens of the device handle (0 before the first forward)."""
         return self._max_tokens
+
+    def debug_set(self, key: int, value: int):
+        """Test knobs of the single-pass routing kernel (prichs_moe_debug_set)."""
+        self._ensure(1)
+        _check(_capi.lib().prichs_moe_debug_set(self._h, int(key), int(value)))
 
     def sync_status(self):
         if self._h:

@@ -108,18 +108,16 @@ def golden_small_inputs():
 
 def np_backward_decomposed(ws, x, R, sel, gates, counts, pad=256):
     """fp32 numpy model of the steps prichs_moe_backward performs, in its row space: shared rows [0,T), permuted row
-    Tcap + pos; [gate | up] in blocks of 256 columns (128 gate then 128 up of the same hidden units). Returns the
+    Tcap + pos with pos = expert * Tcap + rank in the expert's bin; [gate | up] in blocks of 256 columns (128 gate then 128 up of the same hidden units). Returns the
     intermediates (gu, hall, yall, dyall, scal, dh, dgu, dxall, dlog), the row map (Tcap, seg_base, pos, live rows) and
     the results (dx, grads in the order of `ws`)."""
     T, d = x.shape
     E = ws[0].shape[1]
     f = ws[1].shape[1]
     k = sel.shape[1]
-    seg_base = np.zeros(E, np.int64)
-    for e in range(1, E):
-        seg_base[e] = seg_base[e - 1] + (counts[e - 1] + pad - 1) // pad * pad
     Tcap = (T + pad - 1) // pad * pad
-    Rtot = Tcap + int(seg_base[-1] + (counts[-1] + pad - 1) // pad * pad)
+    seg_base = np.arange(E, dtype=np.int64) * Tcap  # fixed-capacity segments (the handle is created for T tokens)
+    Rtot = Tcap + E * Tcap
     pos = np.full((T, k), -1, np.int64)
     fill = np.zeros(E, np.int64)
     row_expert = np.full(Rtot, -1, np.int64)

@@ -50,9 +50,9 @@ def _to_host(t):
 
 
 def _gpu_forward(torch, ws, bias, k, x, mode="bf16", x_kind="bf16", y_kind=None, resid=None, cb=None, host=False,
-                 layer=None):
+                 layer=None, **tuning):
     from prichs_b200 import MoELayer
-    m = layer or MoELayer.from_weights(ws, k, mode=mode)
+    m = layer or MoELayer.from_weights(ws, k, mode=mode, **tuning)
     m.router_bias = bias
     if host:
         y = m.forward_with_memory(np.ascontiguousarray(x, np.float32), cb, residual=resid)
@@ -132,35 +132,41 @@ def test_ragged_token_counts(torch_cuda, oracle, T):
     _check_outputs(oracle, ws, bias, k, x, y, agree, TOL_BF16)
 
 
-def test_dispatch_layout_and_intermediates(torch_cuda, oracle):
-    """Stage by stage: permutation rows are exact copies in ascending token order inside 256-aligned segments;
-    H and Y of the shared expert match the oracle's intermediates."""
+@pytest.mark.parametrize("route_kernel", [1, 2])
+def test_dispatch_layout_and_intermediates(torch_cuda, oracle, route_kernel):
+    """Stage by stage, for the single-pass routing kernel (1) and the three-launch path (2): every expert owns a
+    segment of Tcap rows; permutation rows are exact copies in ascending token order inside it; the GEMM's tile table
+    lists the tiles that hold rows; H and Y of the shared expert match the oracle's intermediates."""
     from prichs_b200 import synth
     d, f, E, k, T = 256, 128, 8, 2, 200
     ws, x, bias = _synth_case(5, T, d, f, E, bias_range=(-0.1, 0.1), std=0.05)
-    m, y, st = _gpu_forward(torch_cuda, ws, bias, k, x)
+    m, y, st = _gpu_forward(torch_cuda, ws, bias, k, x, route_kernel=route_kernel)
     sel = st.selected_experts.reshape(T, k)
     counts = st.expert_token_counts
+    Tcap = (m.token_capacity + 255) // 256 * 256
     meta = m.debug_buffer(5, 4 * 36).view(np.int32)
     assert np.array_equal(meta[0:8], counts)
     seg_base = meta[8:16]
-    pad = (counts + 255) // 256 * 256  # segments are padded to one CTA-pair tile
-    assert np.array_equal(seg_base, np.concatenate([[0], np.cumsum(pad)[:-1]]))
+    pad = (counts + 255) // 256 * 256  # a segment's rows are rounded up to whole CTA-pair tiles
+    assert np.array_equal(seg_base, np.arange(E) * Tcap)
     assert meta[32] == pad.sum() // 128 and meta[34] == 0
     pos = m.debug_buffer(4, T * 2 * 4).view(np.int32).reshape(T, 2)
-    rcap_rows = int(pad.sum())
+    rcap_rows = E * Tcap
     xp = synth.from_bf16_bits(m.debug_buffer(1, rcap_rows * d * 2).view(np.uint16)).reshape(rcap_rows, d)
     for e in range(E):
         tok, slot = np.nonzero(sel == e)
         rows = pos[tok, slot]
         assert np.array_equal(rows, seg_base[e] + np.arange(len(tok))), f"expert {e}: rows not in token order"
         assert np.array_equal(xp[rows], x[tok]), f"expert {e}: permuted rows are not exact copies"
-    slots = m.debug_buffer(8, 4 * (rcap_rows // 128)).view(np.int32)
+    ntl = int(pad.sum() // 128)
+    slots = m.debug_buffer(8, 4 * ntl).view(np.int32)
+    trows = m.debug_buffer(16, 4 * ntl).view(np.int32)
     # tiles that hold only padding rows are marked -1 - expert
     exp_slots = np.concatenate([np.where(np.arange(pad[e] // 128) * 128 < counts[e], e, -1 - e) for e in range(E)]).astype(np.int32)
+    exp_rows = np.concatenate([e * Tcap // 128 + np.arange(pad[e] // 128) for e in range(E)]).astype(np.int32)
     assert np.array_equal(slots, exp_slots)
+    assert np.array_equal(trows, exp_rows)
     # shared expert intermediates
-    Tcap = (m.token_capacity + 255) // 256 * 256
     H = synth.from_bf16_bits(m.debug_buffer(2, T * f * 2).view(np.uint16)).reshape(T, f)
     Hexp = oracle.swiglu(oracle.matmul_2d(x, ws[1]), oracle.matmul_2d(x, ws[2]))
     assert_close(H, Hexp, 1e-2, "shared H")
@@ -309,10 +315,10 @@ def test_block_sublayer_prenorm_moe_residual(torch_cuda, oracle, mode, x_kind):
 
 
 @pytest.mark.parametrize("x_kind,d,T", [("bf16", 512, 300), ("f32", 512, 300), ("bf16", 1536, 77), ("f32", 1536, 1030)])
-def test_prenorm_folded_into_router_equals_separate_norm_kernel(torch_cuda, monkeypatch, x_kind, d, T):
+def test_prenorm_folded_into_router_equals_separate_norm_kernel(torch_cuda, x_kind, d, T):
     """In bf16 mode the block entry point folds the RMSNorm into the router kernel's read of the rows. The result
-    (logits, routing, output) must be bit-identical to running the norm as a kernel of its own, which the
-    environment switch PRICHS_FUSED_NORM=0 (read when the handle is created) selects."""
+    (logits, routing, output) must be bit-identical to running the norm as a kernel of its own, which the config
+    field separate_prenorm = 1 selects."""
     import torch
     from prichs_b200 import MoELayer, synth
     f, E, k, eps = 256, 8, 2, 1e-5
@@ -322,9 +328,8 @@ def test_prenorm_folded_into_router_equals_separate_norm_kernel(torch_cuda, monk
         x_res = synth.round_bf16(x_res)
     w = (1.0 + 0.1 * synth.normal(73, 0, (d,))).astype(np.float32)
     outs = []
-    for fused in ("1", "0"):
-        monkeypatch.setenv("PRICHS_FUSED_NORM", fused)
-        m = MoELayer.from_weights(ws, k, mode="bf16")
+    for separate in (0, 1):
+        m = MoELayer.from_weights(ws, k, mode="bf16", separate_prenorm=separate)
         m.router_bias = synth.router_bias(71, E, -0.1, 0.1)
         y = _to_host(m.block_forward(_to_dev(torch, x_res, x_kind), torch.from_numpy(w), eps))
         m.sync_status()
@@ -335,19 +340,18 @@ def test_prenorm_folded_into_router_equals_separate_norm_kernel(torch_cuda, monk
 
 
 @pytest.mark.parametrize("T", [1, 37, 5000])
-def test_scan_at_router_tail_equals_separate_scan_launch(torch_cuda, monkeypatch, T):
+def test_scan_at_router_tail_equals_separate_scan_launch(torch_cuda, T):
     """With all experts local the last CTA of the router launch computes the prefix sums and the placement plan.
-    PRICHS_FUSED_SCAN=0 (read when the handle is created) keeps them as a launch of their own; counts, row map,
-    placement metadata and output must be identical."""
+    scan_placement = 2 keeps them as a launch of their own; counts, row map, placement metadata and output must be
+    identical (route_kernel = 2: the three-launch path, also for the large batch)."""
     import torch
     from prichs_b200 import MoELayer, synth
     d, f, E, k = 512, 256, 8, 2
     ws = synth.layer_weights(81, d, f, E, std=0.03, bf16=True)
     x = synth.round_bf16(synth.normal(82, 0, (T, d)))
     outs = []
-    for fused in ("1", "0"):
-        monkeypatch.setenv("PRICHS_FUSED_SCAN", fused)
-        m = MoELayer.from_weights(ws, k, mode="bf16")
+    for placement in (1, 2):
+        m = MoELayer.from_weights(ws, k, mode="bf16", scan_placement=placement, route_kernel=2)
         m.router_bias = synth.router_bias(81, E, -0.1, 0.1)
         for _ in range(2):  # twice: the finished-CTA counter must be back at zero after a forward
             y = _to_host(m.forward(_to_dev(torch, x, "bf16")))
@@ -359,14 +363,15 @@ def test_scan_at_router_tail_equals_separate_scan_launch(torch_cuda, monkeypatch
         assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("d,T,exact_router,stages", [(512, 5003, True, None), (1536, 4096, False, None), (1024, 7001, True, "2")])
-def test_alternative_router_kernels_equal_the_lock_step_kernel(torch_cuda, monkeypatch, d, T, exact_router, stages):
-    """Large bf16 batches can be routed by three kernels (PRICHS_ROUTER, read when the handle is created): `legacy`,
-    eight warps in lock step per 16-token tile (the default); `warp`, one independent warp per tile; `staged`, rows
-    streamed through a shared-memory ring with bulk copies, one consumer warp per stage. Same
-    arithmetic in the same order: logits, selection, gates, counts, tile histograms and the layer output must be
-    bit-identical. Covers a ragged last tile, a 2-stage ring and both router-weight forms (bf16-exact: 1 part,
-    fp32: 3 parts, where `warp` and `staged` fall back to the lock-step kernel)."""
+@pytest.mark.parametrize("d,T,exact_router", [(512, 5003, True), (1536, 4096, False), (1024, 7001, True), (1536, 16384, True),
+                                              (2048, 1500, True), (256, 16, True), (256, 1, True)])
+def test_single_pass_routing_kernel_equals_three_launches(torch_cuda, d, T, exact_router):
+    """route_kernel = 1 routes, places and dispatches in one pass over the tokens (tickets, rows staged in shared
+    memory, decoupled look-back for the per-expert prefix); route_kernel = 2 runs router, scan and dispatch as three
+    launches. Same arithmetic in the same order: logits, selection, gates, counts, tile histograms, prefix sums, row
+    map, placement summary, tile table, the permuted rows and the layer output must be bit-identical. Covers a ragged
+    last tile, rings of 4, 3 and 2 stages, a single tile, and both router-weight forms (bf16 values: one part, fp32
+    values: three parts). Each path runs twice: the scratch state must be clean again after a forward."""
     import torch
     from prichs_b200 import MoELayer, synth
     f, E, k = 256, 8, 2
@@ -374,22 +379,62 @@ def test_alternative_router_kernels_equal_the_lock_step_kernel(torch_cuda, monke
     if not exact_router:
         ws[0] = synth.normal(86, 0, (d, E), 0.0, 0.03).astype(np.float32)
     x = synth.round_bf16(synth.normal(87, 0, (T, d)))
-    if stages:
-        monkeypatch.setenv("PRICHS_ROUTER_STAGES", stages)
+    ntl = (T + 15) // 16
     outs = []
-    for kind in ("legacy", "warp", "staged"):
-        monkeypatch.setenv("PRICHS_ROUTER", kind)
-        m = MoELayer.from_weights(ws, k, mode="bf16")
+    for kind in (2, 1):
+        m = MoELayer.from_weights(ws, k, mode="bf16", route_kernel=kind)
         m.router_bias = synth.router_bias(85, E, -0.1, 0.1)
         for _ in range(2):
             y = _to_host(m.forward(_to_dev(torch, x, "bf16")))
-        m.sync_status()
+            m.sync_status()
         st = m.last_stash()
+        Tcap = (m.token_capacity + 255) // 256 * 256
+        n_mt = int(m.debug_buffer(5, 4 * 36).view(np.int32)[32])
+        pos = m.debug_buffer(4, T * 2 * 4).view(np.int32).reshape(T, 2).copy()
+        rows = np.unique(pos[pos >= 0])
+        xp = np.stack([m.debug_buffer(1, d * 2, offset=int(r) * d * 2) for r in rows[:: max(1, len(rows) // 64)]])
         outs.append((y, st.router_logits.copy(), st.selected_experts.copy(), st.gating_weights.copy(),
-                     st.expert_token_counts.copy(), m.debug_buffer(6, ((T + 15) // 16) * 8 * 4).copy()))
-    for other in outs[1:]:
-        for a, b in zip(outs[0], other):
-            assert np.array_equal(a, b)
+                     st.expert_token_counts.copy(), m.debug_buffer(6, ntl * 8 * 4).copy(), m.debug_buffer(7, ntl * 8 * 4).copy(),
+                     pos, m.debug_buffer(5, 4 * 36).copy(), m.debug_buffer(8, 4 * n_mt).copy(), m.debug_buffer(16, 4 * n_mt).copy(), xp))
+    names = ["out", "logits", "selected", "gates", "counts", "tile histograms", "tile prefix", "row map", "summary",
+             "tile slots", "tile rows", "permuted rows"]
+    for name, a, b in zip(names, outs[0], outs[1]):
+        assert np.array_equal(a, b), name
+
+
+def test_single_pass_routing_kernel_against_oracle(torch_cuda, oracle):
+    """The single-pass kernel on its own against the oracle at a size where it is the default (T >= 1024)."""
+    d, f, E, k, T = 512, 384, 8, 2, 3000
+    ws, x, bias = _synth_case(91, T, d, f, E, bias_range=(-0.1, 0.1), std=0.03)
+    m, y, st = _gpu_forward(torch_cuda, ws, bias, k, x)
+    agree = _check_routing(oracle, ws, bias, k, x, st)
+    _check_outputs(oracle, ws, bias, k, x, y, agree, TOL_BF16)
+
+
+def test_look_back_wait_runs_out_and_reports_timeout(torch_cuda):
+    """A tile that never publishes its counts (test knob) makes the look-back of the tiles after it run out of its
+    budget: the kernel gives up in an orderly way, the status word reports PRICHS_ERR_TIMEOUT, and the handle works
+    again afterwards. Nothing faults or hangs: every wait in the kernel is bounded (here to about a millisecond)."""
+    import torch
+    from prichs_b200 import MoELayer, PrichsError, synth, _capi
+    d, f, E, k, T = 256, 128, 8, 2, 200
+    ws = synth.layer_weights(95, d, f, E, std=0.05, bf16=True)
+    x = synth.round_bf16(synth.normal(96, 0, (T, d)))
+    m = MoELayer.from_weights(ws, k, mode="bf16", route_kernel=1)
+    xd = _to_dev(torch, x, "bf16")
+    good = _to_host(m.forward(xd))
+    m.sync_status()
+    m.debug_set(1, 2_000_000)  # ~1 ms of clock cycles per wait
+    m.debug_set(0, 3)          # tile 3 keeps its counts to itself
+    m.forward(xd)
+    with pytest.raises(PrichsError) as err:
+        m.sync_status()
+    assert err.value.code == _capi.ERR_TIMEOUT
+    m.debug_set(0, -1)
+    m.debug_set(1, 4_000_000_000)
+    again = _to_host(m.forward(xd))
+    m.sync_status()
+    assert np.array_equal(good, again)
 
 
 def test_rmsnorm_reference_fixture_values(torch_cuda, oracle):
