@@ -127,6 +127,36 @@ def cpu_baseline(ws, bias, x_f32, target_seconds=12.0, max_tokens=None):
             "sample": f"first {n} tokens of the batch, one full layer forward (routing + shared + routed experts + combine), {dt:.2f} s"}
 
 
+def parity_check(layer, ws, bias, x_host, x_dev, n_sample, seed):
+    """This rank's forward of one timed batch against the CPU oracle, outside every timed region: top-2 indices, gates
+    and per-expert counts bit-exact on ALL tokens when the oracle's top-k is fed the GPU's own fp32 logits (ties go to
+    the lower index), logits within 1e-4, and the layer output of a seeded sample of tokens within the bf16 tolerance
+    2e-2 (|a - b| <= tol * (|b| + rms(b))). Tokens whose own-logit routing differs from the GPU's (near-ties of two
+    selection logits) are left out of the output comparison and counted."""
+    from oracle import oracle as O
+    T = x_host.shape[0]
+    y = layer.forward(x_dev).float().cpu().numpy()
+    layer.sync_status()
+    st = layer.last_stash()
+    given = O.route(None, ws[0], bias, K, logits=st.router_logits)
+    own = O.route(x_host, ws[0], bias, K)
+    sel = st.selected_experts.reshape(T, K)
+    routing_ok = bool(np.array_equal(sel, given["selected"]) and np.array_equal(st.expert_token_counts, given["counts"])
+                      and np.allclose(st.gating_weights.reshape(T, K), given["gating"], rtol=2e-6, atol=1e-7)
+                      and int(st.expert_token_counts.sum()) == T * K)
+    logit_err = float(np.abs(st.router_logits - own["logits"]).max())
+    agree = np.all(sel == own["selected"], axis=1)
+    rng = np.random.default_rng(seed)
+    mask = np.zeros(T, bool)
+    mask[rng.choice(T, size=min(n_sample, T), replace=False)] = True
+    mask &= agree
+    ref = O.moe_forward_train(ws, bias, K, x_host, token_mask=mask)["out"]
+    rms = float(np.sqrt(np.mean(ref[mask].astype(np.float64) ** 2)))
+    rel = np.abs(y[mask] - ref[mask]) / (np.abs(ref[mask]) + rms)
+    return {"routing_bit_exact": routing_ok, "logits_max_abs_err": logit_err, "max_rel": float(rel.max()),
+            "tokens_checked": int(mask.sum()), "tokens_routed": T, "near_tie_tokens_skipped": int((~agree).sum())}
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU path (C++ restatement; no Rust toolchain on this image) on the
     host cores, all threads, each step a bounded sample of the workload."""
@@ -295,6 +325,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of this run's own result (profiling)")
     ap.add_argument("--ep-waves", type=int, default=0, help="expert-parallel token waves (0 = library default)")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override T (profiling of a small case only; the line is then not the baseline's config)")
@@ -306,7 +337,7 @@ def main():
     ap.add_argument("--route-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="single GPU: 0 = library default, 1 = single-pass routing kernel, 2 = router / scan / dispatch launches")
     ap.add_argument("--gemm-kernel", type=int, default=0, choices=[0, 1], help="0 = CTA-pair kernel, 1 = one-CTA kernel")
-    ap.add_argument("--pdl", type=int, default=0, choices=[0, 1], help="programmatic dependent launch between the kernels")
+    ap.add_argument("--pdl", type=int, default=0, choices=[0, 1, 2], help="programmatic dependent launch: 0/1 = on (default), 2 = off")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -502,6 +533,19 @@ def main():
         "roofline_sum": roofline_sum(T, rows, ms_step, peaks, world),
         "clocks": clocks.summary(),
     }
+    # ---- parity of this run's own result against the CPU oracle (every rank; outside the timed regions) -------------
+    if not args.no_parity:
+        par = parity_check(layer, ws, bias, xs_host[0], xs[0], 4096 if rank == 0 else 512, 1234 + rank)
+        if world > 1:
+            t = torch.tensor([0.0 if par["routing_bit_exact"] else 1.0, par["max_rel"], par["logits_max_abs_err"]], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            n = torch.tensor([par["tokens_checked"], par["tokens_routed"], par["near_tie_tokens_skipped"]], device=dev, dtype=torch.int64)
+            dist.all_reduce(n)
+            par = {"routing_bit_exact": float(t[0]) == 0.0, "logits_max_abs_err": float(t[2]), "max_rel": float(t[1]),
+                   "tokens_checked": int(n[0]), "tokens_routed": int(n[1]), "near_tie_tokens_skipped": int(n[2]), "ranks": world}
+        par["tolerance"] = 2e-2
+        par["ok"] = bool(par["routing_bit_exact"] and par["max_rel"] <= 2e-2 and par["logits_max_abs_err"] <= 1e-3)
+        line["parity"] = par
     if world > 1 and args.config == 4:
         # one aux-loss-free bias step from the global counts of the last forward: b_i += gamma (k/E - count_i/total);
         # gamma = 1e-3 on load fractions equals a count-form step of gamma / (T * world) per token of deviation
@@ -524,6 +568,8 @@ def main():
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if "parity" in line and not line["parity"]["ok"]:
+        raise SystemExit("parity check against the CPU oracle failed: " + json.dumps(line["parity"]))
 
 
 if __name__ == "__main__":

@@ -74,7 +74,8 @@ typedef struct prichs_moe_config {
                              launch of their own; 1 = always at the tail; 2 = always their own launch          */
     int separate_prenorm; /* block entry point: 1 = the RMSNorm runs as its own launch (0: folded into the router)  */
     int gemm_kernel;      /* 0 = CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles), 1 = one-CTA kernel          */
-    int pdl;              /* 1 = programmatic dependent launch between the kernels of a single-GPU forward          */
+    int pdl;              /* programmatic dependent launch between the kernels of a single-GPU forward (a kernel's
+                             set-up overlaps the tail of its predecessor): 0 / 1 = on, 2 = off                     */
     int host_chunk_tokens;/* host-buffer entry point: tokens per pipelined chunk (0 = choose from T)                */
     int router_ctas_per_sm; /* router grid cap in CTAs per SM (0 = default; -1 = one CTA per 16-token tile)         */
     int ep_reserve_sms;   /* expert parallel: SMs the GEMM launches leave to the exchange kernels (0 = default 20,
@@ -123,6 +124,52 @@ PRICHS_API int prichs_moe_get_bias(prichs_moe_t* h, float* host_bias, int n);
 PRICHS_API int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* resid_dev,
                        const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T,
                        void* stream);
+
+/* MoELayer::forward_train (moe.rs:93-211): the same forward, which also keeps what the backward pass needs. The
+ * reference copies gate / up / act / out of every expert into host vectors on every call, also from forward()
+ * (moe.rs:108-111,172-175,186-208,219); here the stash is this separate entry point and stays on the device:
+ * act (H) and out (Y) are the forward's own buffers, x is the permuted-row buffer, and the [gate | up]
+ * pre-activations -- which the plain forward never writes to memory -- are stored by the first GEMM's epilogue (bf16).
+ * prichs_moe_backward after this call skips its recomputation of them; prichs_moe_get_stash and
+ * prichs_moe_get_expert_assignments hand the pieces out in the reference's shapes. All experts local, bf16 mode;
+ * the stash buffer (rows x 2f bf16) is allocated by the first call. */
+PRICHS_API int prichs_moe_forward_train(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* resid_dev,
+                                        const float* concept_bias, int n_concept, void* y_dev, int y_dtype, int T,
+                                        void* stream);
+
+/* One stash vector of the last forward as host fp32, in the reference's shape (MoEStash / ExpertForwardStash,
+ * moe.rs:32-53). slot 0 = shared expert (n = T rows), slot 1 + e = routed expert e (n = its assignment count, rows in
+ * ascending token order). which: 0 x [n,d], 1 gate [n,f], 2 up [n,f], 3 act [n,f], 4 out [n,d]. n_floats must equal
+ * the field's size. gate and up exist after prichs_moe_forward_train only. Waits for the forward. */
+PRICHS_API int prichs_moe_get_stash(prichs_moe_t* h, int slot, int which, float* host_dst, size_t n_floats);
+
+/* ExpertForwardStash::token_indices / weights of routed expert e for the last forward (the reference's
+ * expert_assignments[e], moe.rs:121,140): token indices ascending and their gate weights. *n_tokens receives the
+ * count; the arrays (may be null to ask for the count only) hold `capacity` entries. */
+PRICHS_API int prichs_moe_get_expert_assignments(prichs_moe_t* h, int expert, int32_t* token_indices_host, float* weights_host,
+                                                 size_t capacity, size_t* n_tokens);
+
+/* ---- the engine's call shape ---------------------------------------------------------------------
+ * Replacements for GpuModelEngine::gpu_moe_forward_shared / gpu_moe_forward_expert / gpu_moe_finalize_forward
+ * (crates/prichs-cuda/src/engine.rs:1917-2239) and for forward_gemm(router) + the host top-k loop between them, to
+ * be called in the order of crates/prichs-model/src/model.rs:1327-1408 (training) or :1124-1182 (forward_gpu_only):
+ *   1. prichs_engine_moe_forward_shared  takes normed2 [seq_len,d] (host fp32 slice as in the reference, or a device
+ *      pointer with on_device = 1) and enqueues the WHOLE layer as a training forward: router and top-2 on the device,
+ *      shared and routed experts as grouped GEMMs, combine. Optional outputs: the shared expert's stash vectors.
+ *   2. prichs_engine_moe_routing         router_logits [seq_len,E], selected_experts [seq_len,k] (usize), gating
+ *      weights [seq_len,k]: what the reference computes with an Sgemm round trip and top_k_gating_unbiased on the host.
+ *   3. prichs_engine_moe_forward_expert  per expert, ascending: computes nothing (the grouped forward already ran the
+ *      expert); returns its token indices and weights and, where asked, its stash rows x, gate, up, act, out.
+ *   4. prichs_engine_moe_finalize_forward downloads the layer output [seq_len,d] (no residual) and waits.
+ * With on_device = 1 and null stash pointers nothing but the final output crosses PCIe. */
+PRICHS_API int prichs_engine_moe_forward_shared(prichs_moe_t* h, const void* normed2, int on_device, int dtype, size_t seq_len,
+                                                float* shared_gate, float* shared_up, float* shared_act, float* shared_out);
+PRICHS_API int prichs_engine_moe_routing(prichs_moe_t* h, float* router_logits, size_t* selected_experts, float* gating_weights,
+                                         size_t seq_len);
+PRICHS_API int prichs_engine_moe_forward_expert(prichs_moe_t* h, int expert, int32_t* token_indices, float* weights, size_t capacity,
+                                                size_t* n_tokens, float* exp_x, float* exp_gate, float* exp_up, float* exp_act,
+                                                float* exp_out);
+PRICHS_API int prichs_engine_moe_finalize_forward(prichs_moe_t* h, float* total_out, size_t n_floats);
 
 /* The MoE sub-layer of the reference's block in one call (crates/prichs-model/src/block.rs:64-67):
  *   y = x_res + MoELayer::forward_with_memory(rms_norm(x_res, norm_weight, eps), concept_bias)
@@ -285,7 +332,8 @@ PRICHS_API int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value);
  *
  * Every intermediate (transposed router weights, per-tile histograms, prefix sums, packed selections) lives in
  * ONE fixed 1 MiB array that is part of the library image on each GPU that loads it and stays there until the
- * process exits. The call performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ * process exits. The call performs no cudaMalloc/cudaFree and calls no allocating library routine (the very
+ * first kernel launch of a process may still make the CUDA runtime load the library's device code).
  *   x_dev        [T,d] bf16, device          router_dev   [d,E] fp32, device (the reference's layout)
  *   bias_dev     [E] fp32 device, or null for a zero bias
  *   outputs (device, caller-owned): logits_dev [T,E] fp32, selected_dev [T,top_k] int32,

@@ -5,6 +5,6 @@ This package is the thin host side above it: `MoELayer` mirrors the reference's
 crates/prichs-model/src/moe.rs API, `synth` makes the seeded synthetic tensors the benchmark and tests use.
 There is no CPU fallback: without the built library or without a CUDA device the layer raises.
 """
-from .moe import Expert, MoELayer, MoEStash, PrichsError  # noqa: F401
+from .moe import Expert, ExpertForwardStash, MoELayer, MoEStash, PrichsError  # noqa: F401
 
-__all__ = ["Expert", "MoELayer", "MoEStash", "PrichsError"]
+__all__ = ["Expert", "ExpertForwardStash", "MoELayer", "MoEStash", "PrichsError"]

@@ -60,6 +60,17 @@ SYMBOLS = {
     "prichs_moe_get_stage_ms": (C.c_int, [C.c_void_p, _fp]),
     "prichs_moe_get_ep_timeline": (C.c_int, [C.c_void_p, _fp, C.c_int]),
     "prichs_moe_debug_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "prichs_moe_forward_train": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, _fp, C.c_int, C.c_void_p, C.c_int,
+                                           C.c_int, C.c_void_p]),
+    "prichs_moe_get_stash": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]),
+    "prichs_moe_get_expert_assignments": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t,
+                                                    C.POINTER(C.c_size_t)]),
+    "prichs_engine_moe_forward_shared": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p]),
+    "prichs_engine_moe_routing": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "prichs_engine_moe_forward_expert": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t),
+                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "prichs_engine_moe_finalize_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "prichs_moe_debug_set": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong]),
     "prichs_moe_route_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -219,6 +219,8 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive_cluster(acc ? te_leader1 : te_leader0);
                     }
+                    if (args.stash_gu != nullptr)
+                        stash_gate_up(args.stash_gu + (size_t)(row0 + lane) * args.stash_ld + nt * 256 + c, g, u);
                     const int sub = (c >> 5) & 1;                      // which half of the 64-column box
                     const int buf = args.out_split ? 0 : (c >> 6) & 1; // split mode: box 0 = hi, box 1 = lo
                     if (sub == 0) {

@@ -78,7 +78,28 @@ struct Args {
     int out_lo_off;
     int out_f32;               // plain only: the output tensor map is fp32 (32-column boxes) instead of bf16
     int* status;               // device status word; set to -5 on a bounded-wait timeout
+    __nv_bfloat16* stash_gu;   // SwiGLU only, training forward: when non-null the pre-activations are also written,
+                               // as bf16 rows [., stash_ld] in the column order of B (128 gate | 128 up per block)
+    int stash_ld;
 };
+
+// Training forward: the 32 gate and 32 up pre-activations one epilogue lane holds for its output row go to the stash
+// as two 64-byte runs (full 32-byte sectors, so plain vector stores lose nothing against a staged TMA store).
+__device__ __forceinline__ void stash_gate_up(__nv_bfloat16* row_ptr, const uint32_t (&g)[32], const uint32_t (&u)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t pg[4], pu[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(g[8 * j + 2 * i]), __uint_as_float(g[8 * j + 2 * i + 1]));
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(u[8 * j + 2 * i]), __uint_as_float(u[8 * j + 2 * i + 1]));
+            pg[i] = *reinterpret_cast<uint32_t*>(&a);
+            pu[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        reinterpret_cast<uint4*>(row_ptr)[j] = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+        reinterpret_cast<uint4*>(row_ptr + 128)[j] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+    }
+}
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
     // silu(g) * u with silu(g) = g / (1 + exp(-g))   (crates/prichs-core/src/ops.rs:137-140,142-159)
@@ -272,6 +293,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
                     }
+                    if (args.stash_gu != nullptr)
+                        stash_gate_up(args.stash_gu + (size_t)(row0 + lane) * args.stash_ld + nt * 256 + c, g, u);
                     const int sub = (c >> 5) & 1;                      // which half of the 64-column box
                     const int buf = args.out_split ? 0 : (c >> 6) & 1; // split mode: box 0 = hi, box 1 = lo
                     if (sub == 0) {

@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 #include <vector>
 
@@ -349,6 +350,8 @@ struct prichs_moe {
 
     // backward pass (allocated by the first prichs_moe_backward): recomputed pre-activations, gradient buffers in
     // the forward's row space, transposed copies for the weight-gradient products, un-transposed weight copies
+    bool want_stash;  // the forward being enqueued keeps the [gate | up] pre-activations (training forward)
+    bool gu_valid;    // bwd.gu holds the pre-activations of the last forward
     struct Bwd {
         bool ready, nat_valid;
         bf16 *gu, *dyall, *dh, *dgu, *dxall, *xT, *hT, *dyT, *dguT, *w_dn_nat, *w_gu_nat;
@@ -457,6 +460,10 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
     a1->out_f32 = 0;
     a1->status = h->status;
     *a2 = *a1;
+    if (h->want_stash) {
+        a1->stash_gu = h->bwd.gu;
+        a1->stash_ld = 2 * h->f;
+    }
     a2->nk = h->f / egemm::BK;
     a2->n_ntiles = h->d / egemm::BN;
     a2->a_routed_tile_off = h->Tcap / 128 + region_tile;
@@ -833,7 +840,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->pair_gemm = cfg->gemm_kernel != 1;
         h->ep_reserve_sms = cfg->ep_reserve_sms < 0 ? 0 : (cfg->ep_reserve_sms == 0 ? 20 : std::min(64, cfg->ep_reserve_sms) & ~1);
         h->ep_copy_smem = cfg->ep_shared_copy_sms ? 0 : 8192;
-        h->pdl = cfg->pdl != 0;
+        h->pdl = cfg->pdl != 2;
         h->ep_combine_mode = cfg->ep_combine_mode == 1 ? 0 : (cfg->ep_combine_mode == 2 ? 2 : 1);
         // single-pass route + place + dispatch kernel: as many ring stages as fit next to the router weights (one
         // bf16 part when the weights are bf16 values, three when they are fp32 values; known at upload)
@@ -1004,6 +1011,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     h->last_chunked = false;
     h->last_was_block = false;
     h->last_a_shared = nullptr;
+    h->gu_valid = false;
     if (T == 0) {
         if (h->world > 1) return fail(PRICHS_ERR_BAD_SHAPE, "in expert-parallel mode every rank must pass at least one token");
         return PRICHS_OK;
@@ -1124,7 +1132,35 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     if (rc != PRICHS_OK) return rc;
     mark();
     h->ev_valid = timing;
+    h->gu_valid = h->want_stash;
     return PRICHS_OK;
+}
+
+// Allocates the buffer of the [gate | up] pre-activations (rows of the forward's row space, 2f bf16 columns in the
+// column order of the first GEMM's B operand).
+static int stash_alloc(prichs_moe* h) {
+    if (h->bwd.gu) return PRICHS_OK;
+    const size_t R = (size_t)h->Tcap + h->Rcap;
+    int rc = dalloc(&h->bwd.gu, R * 2 * h->f);
+    if (rc != PRICHS_OK) return rc;
+    CUDA_TRY(cudaMemset(h->bwd.gu, 0, R * 2 * h->f * sizeof(bf16)));
+    return PRICHS_OK;
+}
+
+int prichs_moe_forward_train(prichs_moe_t* h, const void* x_dev, int x_dtype, const void* resid_dev, const float* concept_bias,
+                             int n_concept, void* y_dev, int y_dtype, int T, void* stream) {
+    if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
+    if (h->world > 1 || h->mode != PRICHS_MODE_BF16)
+        return fail(PRICHS_ERR_BAD_ARG, "the training forward (activation stash) runs with all experts local in the bf16 mode");
+    {
+        DeviceGuard guard(h->device);
+        int rc = stash_alloc(h);
+        if (rc != PRICHS_OK) return rc;
+    }
+    h->want_stash = true;
+    const int rc = prichs_moe_forward(h, x_dev, x_dtype, resid_dev, concept_bias, n_concept, y_dev, y_dtype, T, stream);
+    h->want_stash = false;
+    return rc;
 }
 
 int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype, const float* norm_weight_dev, float eps,
@@ -1170,6 +1206,33 @@ int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype
     return rc;
 }
 
+}  // extern "C"
+
+namespace {
+constexpr int HOST_MAX_CHUNKS = 64;
+// Staging buffers, streams and events of the entry points that take host buffers; every resource is created only
+// if it is still missing, so a call that failed half way can be repeated.
+int host_path_setup(prichs_moe* h) {
+    if (h->host_ready) return PRICHS_OK;
+    const size_t n = (size_t)h->Tmax * h->d;
+    int rc = PRICHS_OK;
+    if (!h->stage_x) rc = dalloc(&h->stage_x, n);
+    if (rc == PRICHS_OK && !h->stage_y) rc = dalloc(&h->stage_y, n);
+    if (rc == PRICHS_OK && !h->counts_acc) rc = dalloc(&h->counts_acc, route::MAX_E);
+    if (rc != PRICHS_OK) return rc;
+    if (!h->own_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
+    if (!h->in_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+    if (!h->out_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+    if (!h->chunk_ev) h->chunk_ev = new cudaEvent_t[2 * HOST_MAX_CHUNKS]();
+    for (int i = 0; i < 2 * HOST_MAX_CHUNKS; ++i)
+        if (!h->chunk_ev[i]) CUDA_TRY(cudaEventCreateWithFlags(&h->chunk_ev[i], cudaEventDisableTiming));
+    h->host_ready = true;
+    return PRICHS_OK;
+}
+}  // namespace
+
+extern "C" {
+
 int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host, const float* concept_bias,
                             int n_concept, float* y_host, int T) {
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
@@ -1179,21 +1242,10 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     if (!x_host || !y_host) return fail(PRICHS_ERR_BAD_ARG, "null host buffer");
     DeviceGuard guard(h->device);
     const size_t n = (size_t)h->Tmax * h->d;
-    constexpr int MAX_CHUNKS = 64;
-    if (!h->host_ready) {
-        // every resource is created only if it is still missing, so a call that failed half way can be repeated
-        int rc = PRICHS_OK;
-        if (!h->stage_x) rc = dalloc(&h->stage_x, n);
-        if (rc == PRICHS_OK && !h->stage_y) rc = dalloc(&h->stage_y, n);
-        if (rc == PRICHS_OK && !h->counts_acc) rc = dalloc(&h->counts_acc, route::MAX_E);
-        if (rc != PRICHS_OK) return rc;
-        if (!h->own_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
-        if (!h->in_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
-        if (!h->out_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
-        if (!h->chunk_ev) h->chunk_ev = new cudaEvent_t[2 * MAX_CHUNKS]();
-        for (int i = 0; i < 2 * MAX_CHUNKS; ++i)
-            if (!h->chunk_ev[i]) CUDA_TRY(cudaEventCreateWithFlags(&h->chunk_ev[i], cudaEventDisableTiming));
-        h->host_ready = true;
+    constexpr int MAX_CHUNKS = HOST_MAX_CHUNKS;
+    {
+        const int rc0 = host_path_setup(h);
+        if (rc0 != PRICHS_OK) return rc0;
     }
     if (resid_host && !h->stage_r) {
         int rc = dalloc(&h->stage_r, n);
@@ -1422,7 +1474,7 @@ int bwd_alloc(prichs_moe* h) {
     const size_t R = (size_t)h->Tcap + h->Rcap, d = h->d, f = h->f;
     int rc = PRICHS_OK;
     auto A = [&](int r) { if (rc == PRICHS_OK) rc = r; };
-    if (!b.gu) A(dalloc(&b.gu, R * 2 * f));
+    if (!b.gu) A(stash_alloc(h));
     if (!b.dyall) A(dalloc(&b.dyall, R * d));
     if (!b.dh) A(dalloc(&b.dh, R * f));
     if (!b.dgu) A(dalloc(&b.dgu, R * 2 * f));
@@ -1444,7 +1496,6 @@ int bwd_alloc(prichs_moe* h) {
     if (rc != PRICHS_OK) return rc;
     // rows that no kernel of a backward pass writes (padding of the permuted region) must stay finite
     CUDA_TRY(cudaMemset(b.dyall, 0, R * d * sizeof(bf16)));
-    CUDA_TRY(cudaMemset(b.gu, 0, R * 2 * f * sizeof(bf16)));
     CUDA_TRY(cudaMemset(b.dh, 0, R * f * sizeof(bf16)));
     CUDA_TRY(cudaMemset(b.dgu, 0, R * 2 * f * sizeof(bf16)));
     CUDA_TRY(cudaMemset(b.dxall, 0, R * d * sizeof(bf16)));
@@ -1610,8 +1661,9 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
     base.mtile_row = h->mtile_row;
     base.status = h->status;
 
-    // 2. pre-activations again: [gate | up] = x . W_gu (the forward keeps only silu(gate) * up)
-    {
+    // 2. pre-activations: kept by a training forward; after a plain forward (which keeps only silu(gate) * up) they
+    //    are computed again, [gate | up] = x . W_gu
+    if (!h->gu_valid) {
         egemm::Args a = base;
         a.nk = d / egemm::BK;
         a.n_ntiles = 2 * f / egemm::BN;
@@ -1870,20 +1922,23 @@ __global__ void route_static_export_kernel(const float* __restrict__ logits8, co
     }
 }
 
-// Device address of the scratch array on the current device, resolved once per device.
+// Device address of the scratch array on the current device, resolved once per device (std::call_once: two host
+// threads that make the first call on a device at the same time both get the finished address).
 int route_scratch_base(unsigned char** out) {
     constexpr int MAX_DEV = 64;
     static unsigned char* base[MAX_DEV] = {nullptr};
-    static std::atomic<int> ready[MAX_DEV];
+    static cudaError_t err[MAX_DEV];
+    static std::once_flag once[MAX_DEV];
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEV) return fail(PRICHS_ERR_BAD_ARG, "device ordinal %d is out of range", dev);
-    if (!ready[dev].load(std::memory_order_acquire)) {
+    std::call_once(once[dev], [dev] {
         unsigned char* p = nullptr;
-        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch));
+        err[dev] = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_scratch);
         base[dev] = p;
-        ready[dev].store(1, std::memory_order_release);
-    }
+    });
+    if (err[dev] != cudaSuccess || base[dev] == nullptr)
+        return fail(PRICHS_ERR_CUDA, "cudaGetSymbolAddress of the routing scratch failed: %s", cudaGetErrorString(err[dev]));
     *out = base[dev];
     return PRICHS_OK;
 }
@@ -1939,3 +1994,5 @@ extern "C" int prichs_moe_route_static(const void* x_dev, const float* router_de
     LAUNCH_CHECK("export");
     return PRICHS_OK;
 }
+
+#include "engine_compat.cuh"

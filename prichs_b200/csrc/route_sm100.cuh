@@ -515,7 +515,6 @@ route_dispatch_kernel(const __grid_constant__ RouteDispatchArgs a, const Concept
     __shared__ int s_last;
 
     ptx::grid_dep_launch();
-    ptx::grid_dep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full = 0xffffffffu;
     if (threadIdx.x == 0) {
@@ -526,13 +525,22 @@ route_dispatch_kernel(const __grid_constant__ RouteDispatchArgs a, const Concept
         *abort_flag = 0;
         ptx::fence_barrier_init();
     }
-    // the transposed router weights into padded shared-memory rows, 16 bytes per thread and step
-    for (int i = threadIdx.x; i < NSPLIT * MAX_E * (d / 8); i += RD_THREADS) {
-        const int r = i / (d / 8), c = i - r * (d / 8);
-        *reinterpret_cast<uint4*>(wsm + (size_t)r * rowb + 16 * c) = __ldg(reinterpret_cast<const uint4*>(a.wrt + (size_t)r * d) + c);
-    }
-    __syncthreads();
+    __syncthreads();  // barriers are initialised: the producer starts its copies at once
     const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
+    // Everything above, and the staging of the router weights below (they only change at upload, which synchronises
+    // the device), is independent of the previous kernel of the stream; under programmatic dependent launch it runs
+    // while that kernel drains. Tokens, bias and the scratch state are touched after the wait only.
+    if (warp == RD_MAX_STAGES) ptx::grid_dep_wait();
+    if (warp < RD_MAX_STAGES) {
+        // the consumer warps stage the transposed router weights in padded shared-memory rows (16 bytes per thread and
+        // step) while the first tiles are on their way, and meet at a barrier of their own
+        for (int i = threadIdx.x; i < NSPLIT * MAX_E * (d / 8); i += RD_MAX_STAGES * 32) {
+            const int r = i / (d / 8), c = i - r * (d / 8);
+            *reinterpret_cast<uint4*>(wsm + (size_t)r * rowb + 16 * c) = __ldg(reinterpret_cast<const uint4*>(a.wrt + (size_t)r * d) + c);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(RD_MAX_STAGES * 32) : "memory");
+        ptx::grid_dep_wait();
+    }
 
     if (warp == RD_MAX_STAGES) {
         // ---------------------------------------------------------------- producer

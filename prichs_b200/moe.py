@@ -54,13 +54,51 @@ class Expert:
 
 
 @dataclass
+class ExpertForwardStash:
+    """One routed expert's part of the stash (moe.rs:32-42), host fp32 arrays in the reference's shapes."""
+    expert_idx: int
+    token_indices: np.ndarray  # [n] ascending
+    weights: np.ndarray        # [n] gate weights
+    x: np.ndarray              # [n, d]
+    gate: np.ndarray           # [n, f]
+    up: np.ndarray             # [n, f]
+    act: np.ndarray            # [n, f]
+    out: np.ndarray            # [n, d]
+
+
+@dataclass
 class MoEStash:
-    """Routing part of the reference's MoEStash (moe.rs:44-53). The activation stashes that only the backward
-    pass reads (shared_gate/up/act/out, routed_stashes) are not produced by this forward-only library."""
+    """The reference's MoEStash (moe.rs:44-53). The routing fields are always filled. The activation fields
+    (shared_gate / shared_up / shared_act / shared_out, routed_stashes) stay on the device after `forward_train` and
+    are downloaded when first read; they are valid until the next forward on the layer."""
     router_logits: np.ndarray          # [T, E] fp32
     selected_experts: np.ndarray       # [T*k] int64, slot order = descending selection logit
     gating_weights: np.ndarray         # [T*k] fp32
     expert_token_counts: np.ndarray = field(default_factory=lambda: np.zeros(0, np.int64))  # [E]
+    _layer: object = field(default=None, repr=False, compare=False)
+
+    def _shared(self, which):
+        if self._layer is None:
+            raise PrichsError(_capi.ERR_BAD_ARG, "this stash carries no activations: use forward_train on device tensors")
+        return self._layer.stash_field(0, which)
+
+    shared_gate = property(lambda self: self._shared(1))
+    shared_up = property(lambda self: self._shared(2))
+    shared_act = property(lambda self: self._shared(3))
+    shared_out = property(lambda self: self._shared(4))
+
+    @property
+    def routed_stashes(self) -> List[ExpertForwardStash]:
+        """Experts that received tokens, ascending (the reference skips empty experts, moe.rs:151-153)."""
+        if self._layer is None:
+            raise PrichsError(_capi.ERR_BAD_ARG, "this stash carries no activations: use forward_train on device tensors")
+        out = []
+        for e in range(len(self.expert_token_counts)):
+            if self.expert_token_counts[e] == 0:
+                continue
+            idx, w = self._layer.expert_assignments(e)
+            out.append(ExpertForwardStash(e, idx, w, *[self._layer.stash_field(1 + e, i) for i in range(5)]))
+        return out
 
 
 class MoELayer:
@@ -193,7 +231,7 @@ class MoELayer:
         return cb.ctypes.data_as(C.POINTER(C.c_float)), cb.size, cb  # cb kept alive by the caller's tuple
 
     def forward_with_memory(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, residual=None, out=None,
-                            stream=None):
+                            stream=None, _train=False):
         """y = MoE(x) (+ residual when given: the caller's add of block.rs:67, fused)."""
         cbt = self._cb(starkdb_concept_bias)
         cb_ptr, cb_n = cbt[0], cbt[1]
@@ -236,7 +274,8 @@ class MoELayer:
             residual = residual.contiguous()
             rp = residual.data_ptr()
         st = stream if stream is not None else torch.cuda.current_stream(x.device).cuda_stream
-        _check(L.prichs_moe_forward(self._h, x.data_ptr(), dt, rp, cb_ptr, cb_n, y.data_ptr(), ydt, T, st))
+        fwd = L.prichs_moe_forward_train if _train else L.prichs_moe_forward
+        _check(fwd(self._h, x.data_ptr(), dt, rp, cb_ptr, cb_n, y.data_ptr(), ydt, T, st))
         self._T_last = T
         return y
 
@@ -329,8 +368,34 @@ class MoELayer:
         return dx
 
     def forward_train(self, x, starkdb_concept_bias: Optional[Sequence[float]] = None, **kw):
-        out = self.forward_with_memory(x, starkdb_concept_bias, **kw)
-        return out, self.last_stash()
+        """MoELayer::forward_train (moe.rs:93-211): (out, MoEStash). For CUDA tensors in bf16 mode with all experts local
+        the forward keeps the backward pass's activations on the device (prichs_moe_forward_train); the stash's
+        activation fields download them on demand. Otherwise only the routing fields are available."""
+        import_ok = not isinstance(x, np.ndarray) and self.mode == _capi.MODE_BF16 and self._ep_world == 1
+        out = self.forward_with_memory(x, starkdb_concept_bias, _train=import_ok, **kw)
+        st = self.last_stash()
+        if import_ok:
+            st._layer = self
+        return out, st
+
+    def stash_field(self, slot: int, which: int) -> np.ndarray:
+        """One stash vector of the last forward (prichs_moe_get_stash): slot 0 shared / 1 + e routed expert e;
+        which 0 x, 1 gate, 2 up, 3 act, 4 out."""
+        n = self._T_last if slot == 0 else int(self.last_counts()[slot - 1])
+        width = self.hidden_dim if which in (0, 4) else self.intermediate_dim
+        out = np.empty((n, width), np.float32)
+        _check(_capi.lib().prichs_moe_get_stash(self._h, slot, which, out.ctypes.data, out.size))
+        return out
+
+    def expert_assignments(self, expert: int):
+        """(token_indices, weights) of routed expert `expert` for the last forward, tokens ascending."""
+        n = C.c_size_t(0)
+        cap = int(self.last_counts()[expert])
+        idx = np.empty(cap, np.int32)
+        w = np.empty(cap, np.float32)
+        _check(_capi.lib().prichs_moe_get_expert_assignments(self._h, expert, idx.ctypes.data, w.ctypes.data, cap, C.byref(n)))
+        assert n.value == cap
+        return idx.astype(np.int64), w
 
     def last_stash(self) -> MoEStash:
         """Routing results of the last forward (waits for its stream)."""

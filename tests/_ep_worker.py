@@ -28,13 +28,22 @@ def main():
              (512, 384, 8, 2, 3000, (-0.1, 0.1), 3, False), (1536, 1280, 8, 2, 4096, None, 4, False),
              (512, 384, 8, 2, 2500, None, 2, True),
              (512, 384, 8, 2, 40, (-0.1, 0.1), 4, False),       # fewer tokens than waves x 16: some waves are empty
-             (512, 384, 8, 2, 700, (-0.1, 0.1), 2, "f32")]      # fp32-fidelity mode across ranks
+             (512, 384, 8, 2, 700, (-0.1, 0.1), 2, "f32"),      # fp32-fidelity mode across ranks
+             # the multi-GPU configurations of the baseline at their real size: T = 32768 tokens per GPU, production
+             # dimensions, default waves; uniform routing and the Zipf(1.2)-skewed router. Routing is checked on every
+             # token, outputs on a seeded sample of 1024 tokens per rank.
+             (1536, 1280, 8, 2, 32768, None, 0, "big"), (1536, 1280, 8, 2, 32768, None, 0, "zipf")]
     for d, f, E, k, T, brange, waves, skew in cases:
         f32 = skew == "f32"
+        big = skew in ("big", "zipf")
+        zipf = skew == "zipf"
         skew = skew is True
         Tr = T + 37 * rank  # ragged: every rank brings a different number of tokens
-        ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=not f32)
+        ws = synth.layer_weights(3, d, f, E, std=0.02 if big else 0.03, bf16=not f32)
         bias = synth.router_bias(3, E, *brange) if brange else np.zeros(E, np.float32)
+        if zipf:
+            import bench
+            ws[0], _, zshare, ztarget = bench.zipf_router(ws[0], 4)
         if skew:
             ws[0] = synth.round_bf16(np.abs(ws[0]) * np.array([6, 4, 3, 2, 1.5, 1, 1, 1], np.float32)[None, :] *
                                      np.sign(synth.normal(5, 1, ws[0].shape)))
@@ -74,16 +83,22 @@ def main():
         assert meta[33] == hp["recv_rows"] and meta[34] == 0
         assert np.array_equal(meta[36:36 + 8 * world].reshape(world, 8), cmat)
         # outputs against the oracle of the whole layer on this rank's tokens
-        ref = O.moe_forward_train(ws, bias, k, x)
+        mask = None
+        if big:
+            mask = np.zeros(Tr, bool)
+            mask[np.random.default_rng(77 + rank).choice(Tr, size=1024, replace=False)] = True
+        ref = O.moe_forward_train(ws, bias, k, x, token_mask=mask)
         ok = np.all(ref["selected"] == sel, axis=1)
         assert (~ok).sum() <= max(2, Tr // 200)
+        if mask is not None:
+            ok &= mask
         rep_ = assert_close(y[ok], ref["out"][ok], 1e-3 if f32 else 2e-2, f"EP output rank {rank}")
         # bias update from the global counts: identical on every rank, equal to the oracle's
         total_tokens = sum(T + 37 * r for r in range(world))
         m.update_bias_from_last(1e-3, total_tokens=total_tokens)  # ragged ranks: the global total is given
         exp = O.update_aux_free_bias(bias, cmat.sum(axis=0), total_tokens, 1e-3, k)
         assert np.array_equal(m.router_bias, exp)
-        if skew:
+        if skew or zipf:
             share = cmat.sum(axis=0) / cmat.sum()
             assert share.max() > 1.5 / E, f"routing is not skewed: {share}"
         print(f"EP_OK rank={rank} d={d} T={Tr} waves={waves} max_rel={rep_['max_rel']:.3e} recv_rows={hp['recv_rows']}", flush=True)

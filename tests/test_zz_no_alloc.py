@@ -7,8 +7,8 @@ library keeps the router stage's scratch in a fixed 1 MiB device array of its ow
 
 The test calls the entry point through the C-ABI twice in a row (a larger batch first, then a smaller one with
 different data and a bias, so that leftovers of the first call would show) and compares logits, selected
-experts, gates and counts with what prichs_moe_forward reports for the same inputs. Both paths run the same
-kernels, so the comparison is exact. This file sorts last on purpose: a run that stops at the first failure has
+experts, gates and counts with what prichs_moe_forward reports for the same inputs (both paths run the same
+router kernel, so that comparison is exact) and with the CPU oracle (which shares no code with them). This file sorts last on purpose: a run that stops at the first failure has
 then already run every other test.
 """
 import ctypes as C
@@ -56,7 +56,7 @@ def _route_handle(torch, ws, bias, k, x):
     return out
 
 
-def test_route_static_matches_handle_path_twice_in_a_row(capi):
+def test_route_static_matches_handle_path_twice_in_a_row(capi, oracle):
     import torch
     from prichs_b200 import synth
     assert torch.cuda.is_available()
@@ -74,6 +74,15 @@ def test_route_static_matches_handle_path_twice_in_a_row(capi):
         assert np.array_equal(gat, gat_h), "gates differ from the handle path"
         assert np.array_equal(cnt, cnt_h.astype(np.int32)), "counts differ from the handle path"
         assert int(cnt.sum()) == T * k
+        # ... and against the CPU oracle, which shares no code with either GPU path: selection, gates and counts are
+        # bit-exact when its top-k is fed the GPU's own logits, and the logits agree with its own to 1e-4
+        b = bias if bias is not None else np.zeros(E, np.float32)
+        given = oracle.route(None, ws[0], b, k, logits=lo)
+        assert np.array_equal(sel, given["selected"]), "selected experts differ from the oracle on the GPU's logits"
+        assert np.array_equal(cnt, given["counts"].astype(np.int32)), "counts differ from the oracle"
+        np.testing.assert_allclose(gat, given["gating"], rtol=2e-6, atol=1e-7)
+        own = oracle.route(x, ws[0], b, k)
+        assert np.abs(lo - own["logits"]).max() <= 1e-4
 
 
 def test_route_static_rejects_sizes_beyond_its_scratch(capi):
