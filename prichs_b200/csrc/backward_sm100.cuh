@@ -351,9 +351,11 @@ dgamma_reduce_kernel(const float* __restrict__ part, float* __restrict__ d_gamma
 
 // dst[c, r] = src[r, c] for r < rows, c < cols (bf16). src row pitch src_pitch, dst row pitch dst_pitch (elements).
 // 64 x 64 tiles through shared memory (padded against bank conflicts); grid = (ceil(cols/64), ceil(rows/64)).
+// src_nkt > 0: the source is stored tile by tile (256 x 64 blocks, src_nkt blocks per 256 rows; see egemm::Args::b_nkt)
+// instead of row-major with src_pitch.
 __global__ void __launch_bounds__(256)
 transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int cols,
-                      long long src_pitch, long long dst_pitch) {
+                      long long src_pitch, long long dst_pitch, int src_nkt) {
     __shared__ __nv_bfloat16 tile[64][66];
     const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
     const long long r0 = (long long)blockIdx.y * 64;
@@ -361,7 +363,8 @@ transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __re
     for (int i = ty; i < 64; i += 4) {
         const long long r = r0 + i;
         const int c = c0 + tx;
-        tile[i][tx] = (r < rows && c < cols) ? src[(size_t)r * src_pitch + c] : __float2bfloat16(0.f);
+        const size_t at = src_nkt > 0 ? ((((size_t)(r >> 8) * src_nkt + (c >> 6)) << 8) + (r & 255)) * 64 + (c & 63) : (size_t)r * src_pitch + c;
+        tile[i][tx] = (r < rows && c < cols) ? src[at] : __float2bfloat16(0.f);
     }
     __syncthreads();
     for (int i = ty; i < 64; i += 4) {

@@ -105,6 +105,7 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
                 const int a_row = (is_shared ? 2 * mp : args.a_routed_tile_off + rt) * BM + (int)cta_rank * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[2 * rp];
                 const int b_row = slot * args.w_rows + nt * BN + (int)cta_rank * 128;
+                const int b_blk0 = (slot * (args.w_rows / BN) + nt) * args.b_nkt;  // first box of this n-tile (tiled B)
                 for (int pass = 0; ok && pass < npass; ++pass) {
                     const int a_col0 = (pass == 1) ? k_elems : 0;
                     const int b_col0 = (pass == 2) ? k_elems : 0;
@@ -118,7 +119,10 @@ expert_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const _
                         const uint32_t full_leader = ptx::mapa_u32(ptx::smem_u32(&full_bar[stage]), 0);
                         if (leader) ptx::mbar_expect_tx(&full_bar[stage], 2 * PAIR_STAGE_BYTES);
                         ptx::tma_load_2d_pair(sa, tm_a, a_col0 + kb * BK, a_row, full_leader);
-                        ptx::tma_load_2d_pair(sb, &tm_b, b_col0 + kb * BK, b_row, full_leader);
+                        if (args.b_nkt > 0)  // this CTA's 128 rows of the contiguous 256 x 64 box
+                            ptx::tma_load_2d_pair(sb, &tm_b, 0, (b_blk0 + b_col0 / BK + kb) * BN + (int)cta_rank * 128, full_leader);
+                        else
+                            ptx::tma_load_2d_pair(sb, &tm_b, b_col0 + kb * BK, b_row, full_leader);
                         if (++stage == PAIR_STAGES) {
                             stage = 0;
                             phase ^= 1;

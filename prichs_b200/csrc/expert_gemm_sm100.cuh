@@ -74,6 +74,11 @@ struct Args {
     const int* mtile_row;      // device: permuted m-tile -> its 128-row tile index inside the permuted region; null when
                                // the region is dense (tile i sits at tile index i)
     int w_rows;                // B rows per weight slot
+    int b_nkt;                 // 0: B is row-major [slot * w_rows + n, K]. > 0: B is stored tile by tile -- the 256 x 64
+                               // block (n-tile, k-block) of a slot is one contiguous 32 KB box, b_nkt k-blocks per
+                               // n-tile -- and its tensor map is the [all blocks x 256, 64] matrix of those boxes. A
+                               // CTA then streams its weights from DRAM in 32 KB runs instead of 128-byte pieces
+                               // 2 K bytes apart, which is what a small batch (weights read once) is bound by
     int out_split;             // SwiGLU only: also write the bf16 residual (lo) at column offset `out_lo_off`
     int out_lo_off;
     int out_f32;               // plain only: the output tensor map is fp32 (32-column boxes) instead of bf16
@@ -179,6 +184,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                 const int a_row = (is_shared ? mt : args.a_routed_tile_off + rt) * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[mt - args.shared_mtiles];
                 const int b_row = slot * args.w_rows + nt * BN;
+                const int b_blk0 = (slot * (args.w_rows / BN) + nt) * args.b_nkt;  // first box of this n-tile (tiled B)
                 for (int pass = 0; ok && pass < npass; ++pass) {
                     // pass 0: hi.hi, pass 1: lo.hi, pass 2: hi.lo
                     const int a_col0 = (pass == 1) ? k_elems : 0;
@@ -192,7 +198,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         uint8_t* sb = sa + A_BYTES;
                         ptx::mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
                         ptx::tma_load_2d(sa, tm_a, a_col0 + kb * BK, a_row, &full_bar[stage]);
-                        ptx::tma_load_2d(sb, &tm_b, b_col0 + kb * BK, b_row, &full_bar[stage]);
+                        if (args.b_nkt > 0)
+                            ptx::tma_load_2d(sb, &tm_b, 0, (b_blk0 + b_col0 / BK + kb) * BN, &full_bar[stage]);
+                        else
+                            ptx::tma_load_2d(sb, &tm_b, b_col0 + kb * BK, b_row, &full_bar[stage]);
                         ++issued;
                         if (++stage == STAGES) {
                             stage = 0;

@@ -119,7 +119,14 @@ int make_tmap(CUtensorMap* tm, const void* base, size_t rows, size_t cols, int b
 }
 
 // ---- weight repacking (once, at upload) -------------------------------------------------------------
-// gate/up [d,f] fp32 (x.W layout) -> rows of the stacked K-major B operand of the first GEMM:
+// Both GEMM weights are stored tile by tile: element (n, k) of a slot's K-major [rows, kw] matrix sits at
+//   (((n / 256) * (kw / 64) + k / 64) * 256 + n % 256) * 64 + k % 64,
+// i.e. every 256 x 64 block the GEMM loads per pipeline stage is one contiguous 32 KB run (egemm::Args::b_nkt).
+__device__ __forceinline__ size_t tiled_at(int n, int k, int kw) {
+    return ((((size_t)(n >> 8) * (kw >> 6) + (k >> 6)) << 8) + (n & 255)) * 64 + (k & 63);
+}
+
+// gate/up [d,f] fp32 (x.W layout) -> the stacked K-major B operand of the first GEMM:
 // row n of a slot, n = blk*256 + r, holds hidden unit blk*128 + (r % 128) of gate (r < 128) or up (r >= 128).
 // kw = d (bf16 mode) or 2d ([hi | lo], fp32-fidelity mode).
 __global__ void repack_gate_up_kernel(const float* __restrict__ wg, const float* __restrict__ wu,
@@ -132,8 +139,8 @@ __global__ void repack_gate_up_kernel(const float* __restrict__ wg, const float*
         const int col = blk * 128 + (r & 127);
         const float v = (r < 128 ? wg : wu)[(size_t)k * f + col];
         const bf16 hi = __float2bfloat16_rn(v);
-        dst[(size_t)n * kw + k] = hi;
-        if (split) dst[(size_t)n * kw + d + k] = __float2bfloat16_rn(v - __bfloat162float(hi));
+        dst[tiled_at(n, k, kw)] = hi;
+        if (split) dst[tiled_at(n, d + k, kw)] = __float2bfloat16_rn(v - __bfloat162float(hi));
     }
 }
 
@@ -145,8 +152,8 @@ __global__ void repack_down_kernel(const float* __restrict__ wd, bf16* __restric
         const int n = (int)(i / f), k = (int)(i % f);
         const float v = wd[(size_t)k * d + n];
         const bf16 hi = __float2bfloat16_rn(v);
-        dst[(size_t)n * kw + k] = hi;
-        if (split) dst[(size_t)n * kw + f + k] = __float2bfloat16_rn(v - __bfloat162float(hi));
+        dst[tiled_at(n, k, kw)] = hi;
+        if (split) dst[tiled_at(n, f + k, kw)] = __float2bfloat16_rn(v - __bfloat162float(hi));
     }
 }
 
@@ -455,6 +462,7 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
     a1->mtile_slot = mtile_slot;
     a1->mtile_row = mtile_row;
     a1->w_rows = 2 * h->f;
+    a1->b_nkt = h->K1 / egemm::BK;
     a1->out_split = f32mode;
     a1->out_lo_off = h->f;
     a1->out_f32 = 0;
@@ -468,6 +476,7 @@ void gemm_args(prichs_moe* h, int T, int region_tile, const int* n_routed_mtiles
     a2->n_ntiles = h->d / egemm::BN;
     a2->a_routed_tile_off = h->Tcap / 128 + region_tile;
     a2->w_rows = h->d;
+    a2->b_nkt = h->K2 / egemm::BK;
     a2->out_split = 0;
     a2->out_f32 = f32mode;
 }
@@ -819,11 +828,12 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     cudaMemset(h->hbuf, 0, rows_all * h->K2 * sizeof(bf16));
 
     A(make_tmap(&h->tm_xp, h->xp, h->Rcap, h->K1, egemm::BM));
-    A(make_tmap(&h->tm_wgu, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, egemm::BN));
+    // weights: the matrix of 256 x 64 boxes (see repack_gate_up_kernel)
+    A(make_tmap(&h->tm_wgu, h->w_gu, (size_t)h->n_slots * 2 * f * (h->K1 / 64), 64, egemm::BN));
     A(make_tmap(&h->tm_h, h->hbuf, rows_all, h->K2, egemm::BM));
-    A(make_tmap(&h->tm_wdn, h->w_dn, (size_t)h->n_slots * d, h->K2, egemm::BN));
-    A(make_tmap(&h->tm_wgu_half, h->w_gu, (size_t)h->n_slots * 2 * f, h->K1, 128));
-    A(make_tmap(&h->tm_wdn_half, h->w_dn, (size_t)h->n_slots * d, h->K2, 128));
+    A(make_tmap(&h->tm_wdn, h->w_dn, (size_t)h->n_slots * d * (h->K2 / 64), 64, egemm::BN));
+    A(make_tmap(&h->tm_wgu_half, h->w_gu, (size_t)h->n_slots * 2 * f * (h->K1 / 64), 64, 128));
+    A(make_tmap(&h->tm_wdn_half, h->w_dn, (size_t)h->n_slots * d * (h->K2 / 64), 64, 128));
     A(make_tmap(&h->tm_h_out, h->hbuf, rows_all, h->K2, 32));
     A(make_tmap(&h->tm_y_out, h->ybuf, rows_all, d, 32, h->mode == PRICHS_MODE_F32));
     if (rc == PRICHS_OK) {
@@ -1512,10 +1522,11 @@ int bwd_alloc(prichs_moe* h) {
     return rc;
 }
 
-int bwd_transpose(const bf16* src, bf16* dst, long long rows, int cols, long long src_pitch, long long dst_pitch, cudaStream_t st) {
+int bwd_transpose(const bf16* src, bf16* dst, long long rows, int cols, long long src_pitch, long long dst_pitch, cudaStream_t st,
+                  int src_nkt = 0) {
     if (rows <= 0) return PRICHS_OK;
     const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
-    bwd::transpose_bf16_kernel<<<grid, 256, 0, st>>>(src, dst, rows, cols, src_pitch, dst_pitch);
+    bwd::transpose_bf16_kernel<<<grid, 256, 0, st>>>(src, dst, rows, cols, src_pitch, dst_pitch, src_nkt);
     LAUNCH_CHECK("transpose");
     return PRICHS_OK;
 }
@@ -1633,9 +1644,9 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
     // un-transposed weight copies ([f,d] and [d,2f] per slot, K-major for the input-gradient products)
     if (!b.nat_valid) {
         for (int s = 0; s < h->n_slots; ++s) {
-            rc = bwd_transpose(h->w_dn + (size_t)s * d * h->K2, b.w_dn_nat + (size_t)s * f * d, d, f, h->K2, d, st);
+            rc = bwd_transpose(h->w_dn + (size_t)s * d * h->K2, b.w_dn_nat + (size_t)s * f * d, d, f, h->K2, d, st, h->K2 / 64);
             if (rc != PRICHS_OK) return rc;
-            rc = bwd_transpose(h->w_gu + (size_t)s * 2 * f * h->K1, b.w_gu_nat + (size_t)s * d * 2 * f, 2 * f, d, h->K1, 2 * f, st);
+            rc = bwd_transpose(h->w_gu + (size_t)s * 2 * f * h->K1, b.w_gu_nat + (size_t)s * d * 2 * f, 2 * f, d, h->K1, 2 * f, st, h->K1 / 64);
             if (rc != PRICHS_OK) return rc;
         }
         b.nat_valid = true;
@@ -1669,6 +1680,7 @@ int backward_impl(prichs_moe* h, const bf16* a_shared, const void* dy_dev, int d
         a.n_ntiles = 2 * f / egemm::BN;
         a.a_routed_tile_off = 0;
         a.w_rows = 2 * f;
+        a.b_nkt = d / egemm::BK;  // the forward's weights are stored tile by tile
         rc = bwd_gemm(h, tm_x, h->tm_xp, h->tm_wgu, b.tm_gu_out, a, st, "pre-activation GEMM");
         if (rc != PRICHS_OK) return rc;
     }
