@@ -334,6 +334,10 @@ def main():
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
     ap.add_argument("--streams", type=int, default=8, help="decode config: streams the independent layers are spread over")
+    ap.add_argument("--no-same-t", action="store_true", help="several GPUs: skip rank 0's one-GPU run at the same T")
+    ap.add_argument("--ep-nccl-barriers", type=int, default=0, choices=[0, 1], help="1 = NCCL all-gathers as barriers instead of readiness flags")
+    ap.add_argument("--ep-dispatch-kernel", type=int, default=0, choices=[0, 1], help="0 = bulk-copy dispatch, 1 = warp-per-token dispatch")
+    ap.add_argument("--ep-reserve-sms", type=int, default=0, help="SMs the expert-parallel GEMM launches leave free (0 = default, -1 = none)")
     ap.add_argument("--route-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="single GPU: 0 = library default, 1 = single-pass routing kernel, 2 = router / scan / dispatch launches")
     ap.add_argument("--gemm-kernel", type=int, default=0, choices=[0, 1], help="0 = CTA-pair kernel, 1 = one-CTA kernel")
@@ -378,7 +382,33 @@ def main():
         if skew:
             ws[0], zipf_sigma, zipf_share, zipf_target = zipf_router(ws[0], seed)
         bias = np.zeros(E, np.float32)
-        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves)
+        same_T = None
+        if rank == 0 and not args.no_same_t:
+            # like-for-like baseline of the scaling figure: the same T tokens on ONE GPU with all eight experts local
+            # (the driver's own efficiency divides by the config-1 value, measured at T = 16384)
+            solo = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank)
+            solo.router_bias = bias
+            xsolo = [torch.from_numpy(synth.to_bf16_bits(synth.tokens(seed * 1000 + 7919 * i, T, D, bf16=True)).view(np.int16)).view(torch.bfloat16).to(dev)
+                     for i in range(2)]
+            ysolo = torch.empty_like(xsolo[0])
+            for i in range(5):
+                solo.forward(xsolo[i % 2], out=ysolo)
+            torch.cuda.synchronize(dev)
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for i in range(30):
+                solo.forward(xsolo[i % 2], out=ysolo)
+            s1.record()
+            torch.cuda.synchronize(dev)
+            solo.sync_status()
+            ms1 = s0.elapsed_time(s1) / 30
+            same_T = {"tokens": T, "ms_per_step": ms1, "tokens_per_s": T / (ms1 * 1e-3), "steps": 30}
+            solo.close()
+            del solo, xsolo, ysolo
+            torch.cuda.empty_cache()
+        layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves,
+                                      ep_nccl_barriers=args.ep_nccl_barriers, ep_reserve_sms=args.ep_reserve_sms,
+                                      ep_dispatch_kernel=args.ep_dispatch_kernel)
         for e in range(E):  # only the experts this rank owns are uploaded
             if e // (E // world) != rank:
                 layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
@@ -533,6 +563,9 @@ def main():
         "roofline_sum": roofline_sum(T, rows, ms_step, peaks, world),
         "clocks": clocks.summary(),
     }
+    if world > 1 and rank == 0 and same_T is not None:
+        same_T["efficiency_vs_same_T"] = value / (n_gpus * same_T["tokens_per_s"])
+        line["single_gpu_same_T"] = same_T
     # ---- parity of this run's own result against the CPU oracle (every rank; outside the timed regions) -------------
     if not args.no_parity:
         par = parity_check(layer, ws, bias, xs_host[0], xs[0], 4096 if rank == 0 else 512, 1234 + rank)

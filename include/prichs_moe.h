@@ -83,6 +83,10 @@ typedef struct prichs_moe_config {
     int ep_shared_copy_sms; /* expert parallel: 1 = dispatch / combine may share SMs with GEMM CTAs                 */
     int ep_combine_mode;  /* expert parallel: which combine launches keep off the GEMM SMs: 0 = all but the last
                              wave's (default), 1 = all, 2 = none                                                   */
+    int ep_dispatch_kernel; /* expert parallel: 0 = rows travel as bulk copies through shared memory on the reserved SMs,
+                             1 = one warp per token with 16-byte loads and stores                                  */
+    int ep_nccl_barriers; /* expert parallel: 1 = "rows landed" / "outputs ready" are NCCL all-gathers used as barriers
+                             (0: readiness flags the ranks write into each other's memory over NVLink)           */
 } prichs_moe_config_t;
 
 /* ---- lifetime ------------------------------------------------------------------------------------ */
@@ -260,8 +264,11 @@ PRICHS_API int prichs_moe_update_bias_from_last(prichs_moe_t* h, float gamma, si
  * dispatch kernel writes each permuted row straight into the owner's receive buffer over NVLink (peer-mapped
  * memory) and the combine kernel reads expert outputs straight from the owners' buffers, so no separate
  * all-to-all copy exists. NCCL carries only the control plane: one 32-byte all-gather of the per-rank expert
- * counts (placement plan + global counts for the bias update) and two token-sized all-gathers used as
- * barriers (rows landed / outputs ready), all on the forward's stream.
+ * counts per wave (placement plan + global counts for the bias update). "Rows landed" and "outputs ready" are
+ * readiness flags: each rank stores the forward's sequence number into a slot of every peer's flag array after the
+ * producing kernel, and a bounded wait on the local slots precedes the consuming kernel (a wait that runs out is
+ * reported as PRICHS_ERR_TIMEOUT by prichs_moe_sync_status; nothing hangs). ep_nccl_barriers = 1 uses two
+ * token-sized NCCL all-gathers as barriers instead.
  * Set-up, with any host channel (MPI, torch.distributed, a file) moving the bytes:
  *   1. rank 0: prichs_moe_ep_unique_id(id) and broadcast the PRICHS_EP_ID_BYTES bytes;
  *   2. every rank: prichs_moe_ep_export(h, blob) and all-gather the 128-byte blobs in rank order;
@@ -319,7 +326,9 @@ PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_b
 /* Test knobs of the single-pass routing kernel (no counterpart in the reference). key 0: index of a 16-token tile
  * that does not publish its counts in the following forwards, so that the look-back of the tiles after it runs out
  * and the forward reports PRICHS_ERR_TIMEOUT through prichs_moe_sync_status (-1 = none, the default). key 1: budget
- * of that kernel's bounded waits in clock cycles (default 4e9, about two seconds). */
+ * of that kernel's bounded waits, and of the expert-parallel readiness waits, in clock cycles (default 4e9, about two
+ * seconds). key 2: 1 + kind * 4 + wave of a readiness signal this rank does not send in the following expert-parallel
+ * forwards (kind 0 rows landed, 1 outputs ready; 0 = none), so that the other ranks' bounded wait for it runs out. */
 PRICHS_API int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value);
 
 /* ---- routing without any allocation ---------------------------------------------------------------

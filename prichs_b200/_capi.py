@@ -22,10 +22,10 @@ class Config(C.Structure):
                                        # tuning (0 = default): see prichs_moe_config_t
                                        "route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl",
                                        "host_chunk_tokens", "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms",
-                                       "ep_combine_mode")]
+                                       "ep_combine_mode", "ep_dispatch_kernel", "ep_nccl_barriers")]
 
 TUNING_FIELDS = ("route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl", "host_chunk_tokens",
-                 "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms", "ep_combine_mode")
+                 "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms", "ep_combine_mode", "ep_dispatch_kernel", "ep_nccl_barriers")
 
 
 # name -> (restype, argtypes); the full export list of include/prichs_moe.h

@@ -322,6 +322,7 @@ struct prichs_moe {
     long long rd_wait_cycles;  // budget of the single-pass kernel's bounded waits
     int rd_stall_tile;    // test knob (prichs_moe_debug_set): the tile that never publishes its counts, -1 none
     void* ybuf;
+    size_t y_bytes;  // bytes of the expert outputs inside the allocation (the flags follow)
     float *logits, *gates;
     int *sel, *pos, *tile_counts, *tile_prefix, *mtile_slot, *status;
     route::RouteMeta* meta;
@@ -343,6 +344,13 @@ struct prichs_moe {
     int ep_combine_mode; // which combine launches keep off the GEMM SMs: 0 all, 1 all but the last wave's, 2 none
     int ep_copy_smem;    // dynamic shared memory requested by dispatch/combine in expert-parallel mode: more than a
                          // GEMM CTA leaves free, so these kernels only run on the reserved SMs (0 = share SMs)
+    int* ep_flags;             // readiness flags written by the peers (tail of the expert-output allocation)
+    void* flag_peer[route::MAX_RANKS];  // the same array of every rank
+    int ep_seq;                // sequence number of the expert-parallel forward being enqueued
+    int ep_skip_signal;        // test knob: 1 + kind * 4 + wave of a signal this rank does not send (0: none)
+    int ep_barrier_mode;       // 0: readiness flags over NVLink; 1: NCCL all-gathers as barriers
+    bool ep_bulk_dispatch;     // expert-parallel dispatch with bulk copies through shared memory
+    int db_stages;             // ... depth of its ring
     int* ep_zero;              // a device int that stays zero (the "no permuted tiles" count of the shared launches)
     cudaStream_t side_stream;  // shared-expert GEMMs of the expert-parallel mode
     cudaEvent_t ev_router, ev_shared;
@@ -532,18 +540,22 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
 
 namespace {
 
-// Adds the per-expert counts of the chunk that just ran to `acc` (first chunk: overwrite).
+// Adds the per-expert counts of the chunk that just ran to `acc` (first chunk: overwrite): acc[0..8) this rank's
+// counts, acc[8..16) the totals over all ranks.
 __global__ void host_chunk_accumulate_kernel(const route::RouteMeta* __restrict__ meta, int* __restrict__ acc, int first) {
     const int e = threadIdx.x;
-    if (e < route::MAX_E) acc[e] = (first ? 0 : acc[e]) + meta->counts[e];
+    if (e < route::MAX_E) {
+        acc[e] = (first ? 0 : acc[e]) + meta->counts[e];
+        acc[route::MAX_E + e] = (first ? 0 : acc[route::MAX_E + e]) + meta->total[e];
+    }
 }
 // After the last chunk: the call's totals become the handle's "last forward" counts.
-__global__ void host_chunk_finish_kernel(route::RouteMeta* __restrict__ meta, const int* __restrict__ acc) {
+__global__ void host_chunk_finish_kernel(route::RouteMeta* __restrict__ meta, const int* __restrict__ acc, int rank) {
     const int e = threadIdx.x;
     if (e < route::MAX_E) {
         meta->counts[e] = acc[e];
-        meta->total[e] = acc[e];
-        meta->cmat[e] = acc[e];
+        meta->total[e] = acc[route::MAX_E + e];
+        meta->cmat[rank * route::MAX_E + e] = acc[e];
     }
 }
 
@@ -583,6 +595,23 @@ __global__ void ep_totals_kernel(const WaveMetas wm, int n_waves, route::RouteMe
     }
 }
 
+// Readiness flags (route::ep_signal_kernel / ep_wait_kernel) of wave `w`: `signal` tells every rank that this rank's
+// part of `kind` is done (enqueued after the kernel that produced it), `wait` holds the stream until every rank has
+// said so. Sequence number = the forward's.
+int ep_signal_and_wait(prichs_moe* h, int kind, int w, cudaStream_t ws, bool signal, bool wait) {
+    if (signal && h->ep_skip_signal != 1 + kind * 4 + w) {
+        route::PeerPtrs fl;
+        for (int i = 0; i < route::MAX_RANKS; ++i) fl.p[i] = h->flag_peer[i];
+        route::ep_signal_kernel<<<1, 32, 0, ws>>>(fl, kind, w, h->rank, h->world, h->ep_seq);
+        LAUNCH_CHECK("readiness signal");
+    }
+    if (wait) {
+        route::ep_wait_kernel<<<1, 32, 0, ws>>>(h->ep_flags, kind, w, h->world, h->ep_seq, h->rd_wait_cycles, h->status);
+        LAUNCH_CHECK("readiness wait");
+    }
+    return PRICHS_OK;
+}
+
 // Expert-parallel forward. Buffer-reuse hazards between consecutive forwards are closed by stream order plus
 // the collectives: a peer writes this rank's receive region of wave w only after the counts all-gather of
 // its next forward's wave w, which this rank joins after every wave of the current forward has been joined
@@ -597,13 +626,20 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
     int rc = make_tmap(&tm_x, a_shared, (size_t)T, (size_t)h->K1, egemm::BM);
     if (rc != PRICHS_OK) return rc;
     h->ev_valid = false;
+    h->ep_seq += 1;
     // A few SMs stay free of the persistent GEMM CTAs so that the small kernels of the other streams (scans,
     // plans, NCCL) are never queued behind a whole GEMM.
     const int gemm_grid = std::max(2, h->sm_count - h->ep_reserve_sms);
     const size_t xsz = (h->resid_dtype >= 0 ? h->resid_dtype : x_dtype) == PRICHS_DTYPE_F32 ? 4 : 2, osz = y_dtype == PRICHS_DTYPE_F32 ? 4 : 2, ysz = f32mode ? 4 : 2;
 
     // 1. router over the whole batch
-    rc = launch_router(h, x_dev, x_dtype, cb, T, h->logits, h->sel, h->gates, h->tile_counts, st);
+    // routing results of this call start at token `tok_base` of the stash arrays (non-zero only while the host-buffer
+    // entry point feeds a batch through in chunks)
+    float* const logits0 = h->logits + (size_t)h->tok_base * route::MAX_E;
+    int* const sel0 = h->sel + (size_t)h->tok_base * 2;
+    float* const gates0 = h->gates + (size_t)h->tok_base * 2;
+    int* const pos0 = h->pos + (size_t)h->tok_base * 2;
+    rc = launch_router(h, x_dev, x_dtype, cb, T, logits0, sel0, gates0, h->tile_counts, st);
     if (rc != PRICHS_OK) return rc;
     CUDA_TRY(cudaEventRecord(h->ev_router, st));
     const bool tl = h->timing;
@@ -632,9 +668,9 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         const int t0 = wave_begin(T, W, w), tn = wave_begin(T, W, w + 1) - t0;
         const int tile0 = t0 / route::TILE_TOKENS, ntl = (tn + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
         const int region_tile = w * (h->Rw / 128);
-        int* sel = h->sel + (size_t)t0 * 2;
-        float* gates = h->gates + (size_t)t0 * 2;
-        int* pos = h->pos + (size_t)t0 * 2;
+        int* sel = sel0 + (size_t)t0 * 2;
+        float* gates = gates0 + (size_t)t0 * 2;
+        int* pos = pos0 + (size_t)t0 * 2;
         int* tprefix = h->tile_prefix + (size_t)tile0 * route::MAX_E;
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_router, 0));
         // counts of this rank's wave -> all-gather (row `rank` of the matrix, in place) -> the same plan everywhere
@@ -652,13 +688,24 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
             xp_peers.p[i] = static_cast<bf16*>(h->xp_peer[i]) + (size_t)w * h->Rw * h->K1;
             y_peers.p[i] = h->y_peer[i];
         }
-        if (tn > 0) {
+        if (tn > 0 && h->ep_bulk_dispatch) {
+            // bulk copies through shared memory on the SMs the GEMMs leave free (its ring does not fit beside a GEMM CTA)
+            const int grid = std::max(1, std::min((tn + route::TILE_TOKENS - 1) / route::TILE_TOKENS, std::max(2, h->ep_reserve_sms)));
+            route::dispatch_bulk_kernel<<<grid, route::DB_THREADS, route::db_smem_bytes(h->K1 * 2, h->db_stages), ws>>>(
+                a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos, h->db_stages, h->rd_wait_cycles, h->status);
+            LAUNCH_CHECK("dispatch");
+        } else if (tn > 0) {
             route::dispatch_kernel<<<std::min((tn + 7) / 8, 2 * h->sm_count), 256, h->ep_copy_smem, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
             LAUNCH_CHECK("dispatch");
         }
         if (tl) cudaEventRecord(wv.tl[2], ws);
-        // barrier: every rank's rows of this wave have landed before an expert GEMM reads them
-        NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
+        // every rank's rows of this wave have landed before an expert GEMM reads them
+        if (h->ep_barrier_mode == 1) {
+            NCCL_TRY(nccl().all_gather(wv.token + h->rank, wv.token, 1, NCCL_INT32, wv.comm, ws));
+        } else {
+            rc = ep_signal_and_wait(h, 0, w, ws, true, true);
+            if (rc != PRICHS_OK) return rc;
+        }
         if (tl) cudaEventRecord(wv.tl[3], ws);
         egemm::Args a1, a2;
         gemm_args(h, 0, region_tile, &wv.meta->n_routed_mtiles, wv.mtile_slot, nullptr, &a1, &a2);
@@ -668,9 +715,19 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
         rc = launch_expert_gemm(h, 1, h->tm_h, h->tm_h, a2, gemm_grid, ws);
         if (rc != PRICHS_OK) return rc;
         if (tl) cudaEventRecord(wv.tl[5], ws);
+        // every owner's outputs of this wave are complete before the combine gathers them over NVLink: the peers learn
+        // of this rank's outputs as soon as its down projection ends, without waiting for its shared expert
+        if (h->ep_barrier_mode != 1) {
+            rc = ep_signal_and_wait(h, 1, w, ws, true, false);
+            if (rc != PRICHS_OK) return rc;
+        }
         CUDA_TRY(cudaStreamWaitEvent(ws, h->ev_shared, 0));  // the shared expert's rows are complete
-        // barrier: every owner's outputs of this wave are complete before the combine gathers them over NVLink
-        NCCL_TRY(nccl().all_gather(wv.token + route::MAX_RANKS + h->rank, wv.token + route::MAX_RANKS, 1, NCCL_INT32, wv.comm, ws));
+        if (h->ep_barrier_mode == 1) {
+            NCCL_TRY(nccl().all_gather(wv.token + route::MAX_RANKS + h->rank, wv.token + route::MAX_RANKS, 1, NCCL_INT32, wv.comm, ws));
+        } else {
+            rc = ep_signal_and_wait(h, 1, w, ws, false, true);
+            if (rc != PRICHS_OK) return rc;
+        }
         if (tl) cudaEventRecord(wv.tl[6], ws);
         if (tn > 0) {
             const char* resid_w = resid_dev ? static_cast<const char*>(resid_dev) + (size_t)t0 * h->d * xsz : nullptr;
@@ -782,9 +839,16 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     A(dalloc(&h->hbuf, rows_all * h->K2));
     {
         void* p = nullptr;
-        if (rc == PRICHS_OK && cudaMalloc(&p, rows_all * d * (h->mode == PRICHS_MODE_F32 ? 4 : 2)) != cudaSuccess)
+        // (+ the readiness flags of the expert-parallel exchange at its tail, so that one IPC handle maps both)
+        const size_t ybytes = rows_all * d * (h->mode == PRICHS_MODE_F32 ? 4 : 2);
+        if (rc == PRICHS_OK && cudaMalloc(&p, ybytes + 1024) != cudaSuccess)
             rc = fail(PRICHS_ERR_CUDA, "cudaMalloc of the expert-output buffer failed");
         h->ybuf = p;
+        h->y_bytes = ybytes;
+        if (p) {
+            h->ep_flags = reinterpret_cast<int*>(static_cast<char*>(p) + ybytes);
+            cudaMemset(h->ep_flags, 0, 1024);
+        }
     }
     A(dalloc(&h->logits, (size_t)h->Tmax * route::MAX_E));
     A(dalloc(&h->gates, (size_t)h->Tmax * 2));
@@ -823,6 +887,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     for (int i = 0; i < route::MAX_RANKS; ++i) {
         h->xp_peer[i] = h->xp;
         h->y_peer[i] = h->ybuf;
+        h->flag_peer[i] = h->ep_flags;
     }
     cudaMemset(h->xp, 0, (size_t)h->Rcap * h->K1 * sizeof(bf16));
     cudaMemset(h->hbuf, 0, rows_all * h->K2 * sizeof(bf16));
@@ -852,6 +917,13 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->ep_copy_smem = cfg->ep_shared_copy_sms ? 0 : 8192;
         h->pdl = cfg->pdl != 2;
         h->ep_combine_mode = cfg->ep_combine_mode == 1 ? 0 : (cfg->ep_combine_mode == 2 ? 2 : 1);
+        h->ep_barrier_mode = cfg->ep_nccl_barriers ? 1 : 0;
+        h->db_stages = std::min(route::DB_MAX_STAGES, (200 * 1024) / (route::TILE_TOKENS * h->K1 * 2));
+        h->ep_bulk_dispatch = world > 1 && cfg->ep_dispatch_kernel != 1 && h->db_stages >= 2 && h->ep_reserve_sms >= 2;
+        if (h->ep_bulk_dispatch && rc == PRICHS_OK &&
+            cudaFuncSetAttribute(route::dispatch_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 route::db_smem_bytes(h->K1 * 2, h->db_stages)) != cudaSuccess)
+            rc = fail(PRICHS_ERR_CUDA, "cannot reserve shared memory for the bulk dispatch kernel");
         // single-pass route + place + dispatch kernel: as many ring stages as fit next to the router weights (one
         // bf16 part when the weights are bf16 values, three when they are fp32 values; known at upload)
         if (h->mode != PRICHS_MODE_F32 && world == 1) {
@@ -1228,7 +1300,7 @@ int host_path_setup(prichs_moe* h) {
     int rc = PRICHS_OK;
     if (!h->stage_x) rc = dalloc(&h->stage_x, n);
     if (rc == PRICHS_OK && !h->stage_y) rc = dalloc(&h->stage_y, n);
-    if (rc == PRICHS_OK && !h->counts_acc) rc = dalloc(&h->counts_acc, route::MAX_E);
+    if (rc == PRICHS_OK && !h->counts_acc) rc = dalloc(&h->counts_acc, 2 * route::MAX_E);
     if (rc != PRICHS_OK) return rc;
     if (!h->own_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking));
     if (!h->in_stream) CUDA_TRY(cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
@@ -1264,18 +1336,30 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     // Tokens are independent, so a large batch is fed through in chunks: the upload of chunk i+1 and the
     // download of chunk i-1 overlap the kernels of chunk i (three streams). Results are bit-identical to one
     // pass; counts are summed over the chunks. Expert-parallel handles run one pass (all ranks in lock step).
-    int chunk = T;
+    // Chunk boundaries. All experts local: chunks of 1024 (2048) tokens. Expert parallel: every forward is a collective,
+    // so all ranks must run the SAME number of chunks; that number depends only on max_tokens (equal on all ranks by
+    // contract) and every rank cuts its own T into that many pieces.
+    int nchunks = 1, chunk = T;
     if (h->world == 1 && T >= 4096) {
         // small chunks keep the un-overlapped first upload and last download short; the config's host_chunk_tokens overrides
         chunk = h->host_chunk > 0 ? h->host_chunk : (T >= 8192 ? 1024 : 2048);
         while ((T + chunk - 1) / chunk > MAX_CHUNKS) chunk *= 2;
+        nchunks = (T + chunk - 1) / chunk;
+    } else if (h->world > 1) {
+        nchunks = std::max(1, std::min(8, h->Tmax / (h->host_chunk > 0 ? h->host_chunk : 8192)));
+        if (nchunks > 1 && T < 16 * nchunks)
+            return fail(PRICHS_ERR_BAD_SHAPE, "in expert-parallel mode the host-buffer entry point cuts every rank's batch into %d chunks: pass at least %d tokens", nchunks, 16 * nchunks);
     }
-    const int nchunks = (T + chunk - 1) / chunk;
+    auto bound = [&](int c) -> int {
+        if (c >= nchunks) return T;
+        if (h->world == 1) return std::min(T, c * chunk);
+        return (int)((long long)T * c / nchunks / 16 * 16);
+    };
     cudaStream_t st = h->own_stream;
     const size_t row = (size_t)h->d;
     int rc = PRICHS_OK;
     for (int c = 0; c < nchunks && rc == PRICHS_OK; ++c) {
-        const int t0 = c * chunk, tc = std::min(chunk, T - t0);
+        const int t0 = bound(c), tc = bound(c + 1) - t0;
         const size_t off = (size_t)t0 * row, bytes = (size_t)tc * row * sizeof(float);
         cudaEvent_t ev_in = h->chunk_ev[2 * c], ev_done = h->chunk_ev[2 * c + 1];
         CUDA_TRY(cudaMemcpyAsync(h->stage_x + off, x_host + off, bytes, cudaMemcpyHostToDevice, h->in_stream));
@@ -1296,7 +1380,7 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
         CUDA_TRY(cudaMemcpyAsync(y_host + off, h->stage_y + off, bytes, cudaMemcpyDeviceToHost, h->out_stream));
     }
     if (rc == PRICHS_OK && nchunks > 1) {
-        host_chunk_finish_kernel<<<1, 32, 0, st>>>(h->meta, h->counts_acc);
+        host_chunk_finish_kernel<<<1, 32, 0, st>>>(h->meta, h->counts_acc, h->rank);
         LAUNCH_CHECK("count totals");
     }
     h->last_T = T;
@@ -1439,6 +1523,7 @@ int prichs_moe_ep_init(prichs_moe_t* h, const void* id128, const void* all_blobs
         CUDA_TRY(cudaIpcOpenMemHandle(&py, hs[1], cudaIpcMemLazyEnablePeerAccess));
         h->xp_peer[r] = pxp;
         h->y_peer[r] = py;
+        h->flag_peer[r] = static_cast<char*>(py) + h->y_bytes;  // every rank has the same sizes
     }
     static_assert(MAX_WAVES * 128 <= PRICHS_EP_ID_BYTES, "one 128-byte communicator id per wave");
     // Stream priorities order the work of a forward when several kernels compete for SMs: the shared expert
@@ -1834,6 +1919,7 @@ int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value) {
             if (value < 1000) return fail(PRICHS_ERR_BAD_ARG, "wait budget must be at least 1000 cycles");
             h->rd_wait_cycles = value;
             return PRICHS_OK;
+        case 2: h->ep_skip_signal = (int)value; return PRICHS_OK;
         default: return fail(PRICHS_ERR_BAD_ARG, "unknown debug key %d", key);
     }
 }

@@ -1068,6 +1068,145 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, cons
 }
 
 // ---------------------------------------------------------------------------------------------------
+// Dispatch for the expert-parallel exchange, on a handful of SMs: the same placement as dispatch_kernel, but a row
+// travels global memory -> shared memory -> owner's receive region as bulk copies (one load, one or two stores of
+// the whole row), so a CTA keeps its whole ring of tile buffers in flight with three instructions per token instead
+// of one 16-byte load and two stores per lane and step. Stores over NVLink are posted: a few such CTAs saturate the
+// link, and the SMs the grouped GEMMs must leave free for the exchange shrink accordingly.
+// One producer thread per CTA copies 16-token tiles (tile = blockIdx.x, + gridDim.x, ...) into a ring of `stages`
+// buffers; consumer warp w owns stage w: lanes 0..15 look up their token's rows, record them in `pos`, and issue the
+// stores; the stage goes back to the producer when the stores have read it. Waits are bounded (status -5).
+constexpr int DB_MAX_STAGES = 4;
+constexpr int DB_THREADS = (DB_MAX_STAGES + 1) * 32;
+__host__ __device__ inline int db_smem_bytes(int row_bytes, int stages) { return stages * TILE_TOKENS * row_bytes + 2 * DB_MAX_STAGES * 8 + 16; }
+
+__global__ void __launch_bounds__(DB_THREADS, 1)
+dispatch_bulk_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, const int* __restrict__ sel,
+                     const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
+                     int* __restrict__ pos, int stages, long long wait_cycles, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    const int row_bytes = row_elems * 2;
+    const int stage_bytes = TILE_TOKENS * row_bytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(dsm + (size_t)stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + DB_MAX_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + DB_MAX_STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    const int ntiles = (T + TILE_TOKENS - 1) / TILE_TOKENS;
+    const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const bool skip = meta->overflow != 0;  // the plan did not fit: every rank skips the exchange
+    if (warp == DB_MAX_STAGES) {
+        if (lane == 0 && !skip) {
+            int issued = 0;
+            bool ok = true;
+            for (int it = 0; it < my_tiles; ++it) {
+                const int s = it % stages;
+                if (!ptx::mbar_wait_bounded(&empty_bar[s], (uint32_t)(((it / stages) & 1) ^ 1), abort_flag, wait_cycles)) {
+                    ok = false;
+                    break;
+                }
+                const int tile = blockIdx.x + it * gridDim.x;
+                const int rows = min(TILE_TOKENS, T - tile * TILE_TOKENS);
+                ptx::mbar_expect_tx(&full_bar[s], (uint32_t)(rows * row_bytes));
+                ptx::bulk_load_1d(dsm + (size_t)s * stage_bytes, xs + (size_t)tile * TILE_TOKENS * row_elems, (uint32_t)(rows * row_bytes), &full_bar[s]);
+                ++issued;
+            }
+            if (!ok) {
+                for (int i = max(0, issued - stages); i < issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!ptx::mbar_try_wait(&full_bar[i % stages], (uint32_t)((i / stages) & 1)) && clock64() - t0 < wait_cycles) {
+                    }
+                }
+            }
+        }
+    } else if (warp < stages && !skip) {
+        const uint8_t* stage = dsm + (size_t)warp * stage_bytes;
+        for (int it = warp, n = 0; it < my_tiles; it += stages, ++n) {
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int t = tile * TILE_TOKENS + lane;
+            // the routing look-ups do not need the rows: they overlap the copy
+            int row0 = -1, row1 = -1, own0 = 0, own1 = 0;
+            if (lane < TILE_TOKENS && t < T) {
+                const int2 s2 = *reinterpret_cast<const int2*>(sel + (size_t)t * 2);
+                if (s2.x >= 0) {
+                    const int e = s2.x & 0xff;
+                    row0 = meta->seg_base[e] + meta->src_off[e] + tile_prefix[(size_t)tile * MAX_E + e] + (s2.x >> 8);
+                    own0 = e / El;
+                }
+                if (s2.y >= 0) {
+                    const int e = s2.y & 0xff;
+                    row1 = meta->seg_base[e] + meta->src_off[e] + tile_prefix[(size_t)tile * MAX_E + e] + (s2.y >> 8);
+                    own1 = e / El;
+                }
+                *reinterpret_cast<int2*>(pos + (size_t)t * 2) = make_int2(row0, row1);
+            }
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&full_bar[warp], (uint32_t)(n & 1), abort_flag, wait_cycles))) break;
+            if (row0 >= 0 || row1 >= 0) {
+                const uint8_t* src = stage + (size_t)lane * row_bytes;
+                if (row0 >= 0) ptx::bulk_store_1d(reinterpret_cast<__nv_bfloat16*>(dst.p[own0]) + (size_t)row0 * row_elems, src, (uint32_t)row_bytes);
+                if (row1 >= 0) ptx::bulk_store_1d(reinterpret_cast<__nv_bfloat16*>(dst.p[own1]) + (size_t)row1 * row_elems, src, (uint32_t)row_bytes);
+                ptx::bulk_commit();
+                ptx::bulk_wait_read<0>();
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty_bar[warp]);
+        }
+        ptx::bulk_wait_all();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(status, -5);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Readiness flags of the expert-parallel exchange. Every rank owns a small array of ints, flags[kind][wave][source],
+// that its peers write over NVLink: after the kernel that produced something a peer will read (kind 0: this rank's
+// rows of a wave have been stored into the peers' receive regions; kind 1: this rank's expert outputs of a wave are
+// complete) a one-warp kernel stores the forward's sequence number into slot [kind][wave][this rank] of EVERY
+// rank's array, with release semantics at system scope; stream order puts it after the producing kernel. Before the
+// kernel that consumes the data a one-warp kernel polls the local slots of all sources until they carry at least
+// that sequence number (acquire at system scope). Sequence numbers only grow, so nothing is ever reset.
+// The wait is bounded: after `budget_cycles` it records -5 in the status word and returns; the stream goes on, the
+// forward's result is then undefined and prichs_moe_sync_status reports PRICHS_ERR_TIMEOUT.
+constexpr int EP_FLAG_INTS = 2 * 4 * MAX_RANKS;  // [kind][wave][source]
+__host__ __device__ inline int ep_flag_index(int kind, int wave, int source) { return (kind * 4 + wave) * MAX_RANKS + source; }
+
+__global__ void ep_signal_kernel(const __grid_constant__ PeerPtrs flag_arrays, int kind, int wave, int rank, int world, int seq) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        int* dst = reinterpret_cast<int*>(flag_arrays.p[r]) + ep_flag_index(kind, wave, rank);
+        __threadfence_system();
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(seq) : "memory");
+    }
+}
+
+__global__ void ep_wait_kernel(const int* __restrict__ flags, int kind, int wave, int world, int seq, long long budget_cycles,
+                               int* __restrict__ status) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        const int* src = flags + ep_flag_index(kind, wave, r);
+        const long long t0 = clock64();
+        for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            if (v - seq >= 0) break;  // wrap-safe comparison of sequence numbers
+            if (clock64() - t0 > budget_cycles) {
+                atomicExch(status, -5);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
 // Combine: one warp per token, gather-based (no atomics; the reference's GPU path uses atomicAdd,
 // crates/prichs-cuda/src/kernels.cu:906-924). Follows the CPU order: out = shared row; then the selected
 // experts in ascending expert index, out += gate * row (multiply and add rounded separately, moe.rs:178-184);

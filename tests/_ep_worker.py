@@ -101,6 +101,17 @@ def main():
         if skew or zipf:
             share = cmat.sum(axis=0) / cmat.sum()
             assert share.max() > 1.5 / E, f"routing is not skewed: {share}"
+        if big and not zipf:
+            # the host-buffer entry point feeds an expert-parallel batch through in chunks (every rank the same number
+            # of chunks, each a collective forward): same result, same counts, and the stash covers the whole batch
+            counts_dev = st.expert_token_counts.copy()
+            yh = m.forward(x.astype(np.float32))
+            m.sync_status()
+            assert_close(yh[ok], ref["out"][ok], 2e-2, f"EP output through host buffers, rank {rank}")
+            assert np.abs(yh - y).max() <= 1e-2 * (np.abs(y).max() + 1.0)
+            st2 = m.last_stash()
+            assert np.array_equal(st2.expert_token_counts, counts_dev)
+            assert np.array_equal(st2.selected_experts, st.selected_experts)
         print(f"EP_OK rank={rank} d={d} T={Tr} waves={waves} max_rel={rep_['max_rel']:.3e} recv_rows={hp['recv_rows']}", flush=True)
         dist.barrier()
         m.close()
@@ -129,6 +140,42 @@ def main():
     dist.barrier()
     m.close()
     dist.barrier()
+    # readiness flags: rank 0 withholds its "rows landed" signal of wave 0 (test knob); every rank's bounded wait for it
+    # runs out after about a millisecond, the forward ends in an orderly way and reports PRICHS_ERR_TIMEOUT; with the
+    # knob cleared the same handles work again. Nothing faults or hangs. The NCCL-barrier variant must give the same
+    # output as the flag variant.
+    ws = synth.layer_weights(3, d, f, E, std=0.03, bf16=True)
+    outs = []
+    for nccl_barriers in (0, 1):
+        m = MoELayer.from_weights(ws, k, ep_world=world, ep_rank=rank, device=local, ep_waves=2, ep_nccl_barriers=nccl_barriers,
+                                  ep_dispatch_kernel=nccl_barriers)  # second pass: also the warp-per-token dispatch kernel
+        for e in range(E):
+            if e // El != rank:
+                m.experts[e].gate_proj = m.experts[e].up_proj = m.experts[e].down_proj = None
+        ep.connect(m, dist, max_tokens=T)
+        outs.append(m.forward(xd).float().cpu().numpy())
+        m.sync_status()
+        if nccl_barriers == 0:
+            m.debug_set(1, 2_000_000)
+            if rank == 0:
+                m.debug_set(2, 1 + 0 * 4 + 0)
+            m.forward(xd)
+            try:
+                m.sync_status()
+                raise AssertionError("the missing readiness signal was not reported")
+            except PrichsError as e:
+                assert e.code == -5, e
+            m.debug_set(2, 0)
+            m.debug_set(1, 4_000_000_000)
+            dist.barrier()
+            again = m.forward(xd).float().cpu().numpy()
+            m.sync_status()
+            assert np.array_equal(again, outs[0])
+            print(f"EP_OK rank={rank} readiness wait ran out and was reported", flush=True)
+        dist.barrier()
+        m.close()
+        dist.barrier()
+    assert np.array_equal(outs[0], outs[1]), "flag and NCCL-barrier variants differ"
     dist.destroy_process_group()
 
 
