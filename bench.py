@@ -157,6 +157,73 @@ def parity_check(layer, ws, bias, x_host, x_dev, n_sample, seed):
             "tokens_checked": int(mask.sum()), "tokens_routed": T, "near_tie_tokens_skipped": int((~agree).sum())}
 
 
+def skew_measure(args, dist, dev, rank, world, local_rank, steps=20):
+    """Config 4 as an object of the multi-GPU line: the shapes of config 3 with W_r scaled so that expert selection
+    follows Zipf(1.2) (seed 4), timed like the headline (barrier, CUDA events, max over ranks), checked against the
+    oracle like the headline, then one aux-loss-free bias step from the global counts (gamma = 1e-3 on load
+    fractions, i.e. gamma / (T * world) per token of deviation in count form)."""
+    import torch
+    from prichs_b200 import MoELayer, ep, synth
+    seed, T = 4, (args.tokens or 32768)
+    ws = synth.layer_weights(seed, D, F, E, bf16=True)
+    ws[0], sigma, share, target = zipf_router(ws[0], seed)
+    bias = np.zeros(E, np.float32)
+    layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves,
+                                  ep_nccl_barriers=args.ep_nccl_barriers, ep_reserve_sms=args.ep_reserve_sms,
+                                  ep_dispatch_kernel=args.ep_dispatch_kernel)
+    for e in range(E):
+        if e // (E // world) != rank:
+            layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
+    ep.connect(layer, dist, max_tokens=T)
+    layer.router_bias = bias
+    xh = [synth.tokens(seed * 1000 + rank + 7919 * i, T, D, bf16=True) for i in range(2)]
+    xs = [torch.from_numpy(synth.to_bf16_bits(x).view(np.int16)).view(torch.bfloat16).to(dev) for x in xh]
+    y = torch.empty_like(xs[0])
+    for i in range(5):
+        layer.forward(xs[i % 2], out=y)
+    torch.cuda.synchronize(dev)
+    layer.sync_status()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        layer.forward(xs[i % 2], out=y)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    par = parity_check(layer, ws, bias, xh[0], xs[0], 4096 if rank == 0 else 512, 4321 + rank)
+    tt = torch.tensor([0.0 if par["routing_bit_exact"] else 1.0, par["max_rel"], par["logits_max_abs_err"]], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    nn = torch.tensor([par["tokens_checked"], par["tokens_routed"]], device=dev, dtype=torch.int64)
+    dist.all_reduce(nn)
+    gcounts = torch.tensor(layer.last_counts(), device=dev)
+    dist.all_reduce(gcounts)
+    import ctypes as C
+    from prichs_b200 import _capi
+    rr = C.c_int64()
+    _capi.lib().prichs_moe_ep_recv_rows(layer._h, C.byref(rr))
+    rr2 = torch.tensor([int(rr.value)], device=dev, dtype=torch.int64)
+    allrows = [torch.zeros_like(rr2) for _ in range(world)]
+    dist.all_gather(allrows, rr2)
+    layer.update_bias_from_last(1e-3, total_tokens=T * world)
+    bias_after = [float(v) for v in layer.router_bias]
+    gc = gcounts.cpu().numpy().astype(np.float64)
+    out = {"workload": f"config 4: config 3's shapes with a Zipf(1.2)-skewed router (seed 4), {world} GPUs",
+           "ms_per_step": ms, "tokens_per_s": T * world / (ms * 1e-3), "steps": steps,
+           "parity": {"routing_bit_exact": float(tt[0]) == 0.0, "max_rel": float(tt[1]), "logits_max_abs_err": float(tt[2]),
+                      "tokens_checked": int(nn[0]), "tokens_routed": int(nn[1]), "tolerance": 2e-2,
+                      "ok": bool(float(tt[0]) == 0.0 and float(tt[1]) <= 2e-2 and float(tt[2]) <= 1e-3)},
+           "zipf_alpha": ZIPF_ALPHA, "sigma": [float(v) for v in sigma], "top1_share_sample": [float(v) for v in share],
+           "top1_share_target": [float(v) for v in target], "global_counts": [int(v) for v in gc],
+           "imbalance_max_over_mean": float(gc.max() / gc.mean()), "recv_rows_per_gpu": [int(v.item()) for v in allrows],
+           "bias_after_step": bias_after, "gamma": 1e-3}
+    layer.close()
+    return out
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU path (C++ restatement; no Rust toolchain on this image) on the
     host cores, all threads, each step a bounded sample of the workload."""
@@ -225,96 +292,104 @@ def zipf_router(ws_router, seed, n_sample=65536, iters=60):
     return synth.round_bf16((ws_router * sigma[None, :].astype(np.float32))), sigma, share, target
 
 
-def run_decode(args):
-    """Config 2 (decode shape, bandwidth bound): 24 independent MoE layers of the production dimensions, each
-    with its own seeded weights (seed 2 + layer), applied to the same T = 64 tokens; one step = the 24 layer
-    forwards back to back on one stream. Reported as per-step latency and weight-streaming GB/s."""
+def decode_measure(n_layers, steps, warmup, stream_counts, use_graph=True):
+    """Config 2 (decode shape, bandwidth bound): `n_layers` independent MoE layers of the production dimensions, each
+    with its own seeded weights (seed 2 + layer), applied to the same T = 64 tokens; one step = all layer forwards.
+    The layers are independent by the config's definition, so they may be spread over several streams: the small
+    routing kernels of one layer then overlap the weight streaming of others. Measured for every entry of
+    `stream_counts` (1 = all layers back to back on one stream). Returns one dict per stream count."""
     import torch
     from prichs_b200 import MoELayer, _capi, synth
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    T, n_layers = 64, args.layers
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T = 64
     x_host = synth.tokens(2, T, D, bf16=True)
     x = torch.from_numpy(synth.to_bf16_bits(x_host).view(np.int16)).view(torch.bfloat16).to(dev)
     layers = []
     for l in range(n_layers):
-        m = MoELayer.from_weights(synth.layer_weights(2 + l, D, F, E, bf16=True), K, max_tokens=T, device=0)
+        m = MoELayer.from_weights(synth.layer_weights(2 + l, D, F, E, bf16=True), K, max_tokens=T, device=dev.index)
         m.forward(x)  # creates the handle and uploads the weights
         m.router = m.shared_expert = None  # the host copies are not needed any more
         m.experts = []
         layers.append(m)
     L = _capi.lib()
-    st = torch.cuda.current_stream(dev).cuda_stream
-
-    # The layers are independent by the config's definition, so they may be spread over several streams
-    # (--streams, default 4): the small routing kernels of one layer then overlap the weight streaming of others.
-    nstreams = max(1, args.streams)
-    lanes = [torch.cuda.Stream(dev) for _ in range(nstreams)] if nstreams > 1 else []
-    ys = [torch.empty_like(x) for _ in range(max(1, nstreams))]
-
-    def step():
-        if not lanes:
-            for m in layers:
-                rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[0].data_ptr(), _capi.DTYPE_BF16, T, st)
-                assert rc == 0, _capi.last_error()
-            return
-        cur = torch.cuda.current_stream(dev)
-        for ln in lanes:
-            ln.wait_stream(cur)
-        for i, m in enumerate(layers):
-            ln = lanes[i % nstreams]
-            rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[i % nstreams].data_ptr(),
-                                      _capi.DTYPE_BF16, T, ln.cuda_stream)
-            assert rc == 0, _capi.last_error()
-        for ln in lanes:
-            cur.wait_stream(ln)
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize(dev)
-    # the 24 x 6 small launches of a step are replayed as one CUDA graph (the forward neither allocates nor
-    # synchronises, so it can be captured); --no-graph times the plain launches
-    graph = None
-    if not args.no_graph:
-        side = torch.cuda.Stream(dev)
-        with torch.cuda.stream(side):
-            st = side.cuda_stream
-            graph = torch.cuda.CUDAGraph()
-            launches_per_step0 = L.prichs_kernel_launches()
-            with torch.cuda.graph(graph, stream=side):
-                st = torch.cuda.current_stream(dev).cuda_stream
-                step()
-            launches_per_step = int(L.prichs_kernel_launches() - launches_per_step0)
-        torch.cuda.synchronize(dev)
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize(dev)
     peaks = measured_peaks()
-    with ClockSampler(0) as clocks:
-        launches0 = L.prichs_kernel_launches()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            if graph is not None:
-                graph.replay()
-            else:
-                step()
-        e1.record()
-        torch.cuda.synchronize(dev)
-        launches = int(L.prichs_kernel_launches() - launches0) if graph is None else launches_per_step * args.steps
-    ms = e0.elapsed_time(e1) / args.steps
     wbytes = n_layers * 9 * 3 * D * F * 2  # every expert of every layer is hit with probability ~1 at 128 assignments
-    gbs = wbytes / (ms * 1e-3) / 1e9
-    line = {"metric": "MoE-layer tokens/sec", "value": T * n_layers / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+    results = []
+    for nstreams in stream_counts:
+        lanes = [torch.cuda.Stream(dev) for _ in range(nstreams)] if nstreams > 1 else []
+        ys = [torch.empty_like(x) for _ in range(max(1, nstreams))]
+
+        def step():
+            if not lanes:
+                st = torch.cuda.current_stream(dev).cuda_stream
+                for m in layers:
+                    rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[0].data_ptr(), _capi.DTYPE_BF16, T, st)
+                    assert rc == 0, _capi.last_error()
+                return
+            cur = torch.cuda.current_stream(dev)
+            for ln in lanes:
+                ln.wait_stream(cur)
+            for i, m in enumerate(layers):
+                ln = lanes[i % nstreams]
+                rc = L.prichs_moe_forward(m._h, x.data_ptr(), _capi.DTYPE_BF16, None, None, 0, ys[i % nstreams].data_ptr(),
+                                          _capi.DTYPE_BF16, T, ln.cuda_stream)
+                assert rc == 0, _capi.last_error()
+            for ln in lanes:
+                cur.wait_stream(ln)
+
+        for _ in range(max(warmup, 3)):
+            step()
+        torch.cuda.synchronize(dev)
+        # the small launches of a step are replayed as one CUDA graph (the forward neither allocates nor synchronises,
+        # so it can be captured)
+        graph, launches_per_step = None, None
+        if use_graph:
+            side = torch.cuda.Stream(dev)
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                l0 = L.prichs_kernel_launches()
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+                launches_per_step = int(L.prichs_kernel_launches() - l0)
+            torch.cuda.synchronize(dev)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(dev)
+        with ClockSampler(dev.index) as clocks:
+            l0 = L.prichs_kernel_launches()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                graph.replay() if graph is not None else step()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            launches = int(L.prichs_kernel_launches() - l0) if graph is None else launches_per_step * steps
+        ms = e0.elapsed_time(e1) / steps
+        gbs = wbytes / (ms * 1e-3) / 1e9
+        results.append({"streams": nstreams, "ms_per_step": ms, "us_per_layer": ms * 1e3 / n_layers, "weight_GBps": gbs,
+                        "frac_hbm": gbs / peaks["hbm"], "gpu_launches": launches, "cuda_graph": graph is not None,
+                        "clocks": clocks.summary(), "tokens_per_s": T * n_layers / (ms * 1e-3), "weight_bytes_per_step": wbytes})
+    for m in layers:
+        m.close()
+    return results
+
+
+def run_decode(args):
+    """`--config 2`: the decode configuration as a bench line of its own."""
+    import torch
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    r = decode_measure(args.layers, args.steps, args.warmup, [max(1, args.streams)], use_graph=not args.no_graph)[0]
+    line = {"metric": "MoE-layer tokens/sec", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"config 2: decode, {n_layers} independent MoE layers (seed 2+layer), T=64 tokens each, bf16; "
-                                   f"a step is all layer forwards, spread over {nstreams} stream(s)", "layers": n_layers,
-                       "l2": f"the step streams {wbytes / 1e6:.0f} MB of weights, far more than the 126 MB L2"},
-            "decode": {"ms_per_step": ms, "us_per_layer": ms * 1e3 / n_layers, "weight_GBps": gbs, "frac_hbm": gbs / peaks["hbm"]},
+            "config": {"workload": f"config 2: decode, {args.layers} independent MoE layers (seed 2+layer), T=64 tokens each, bf16; "
+                                   f"a step is all layer forwards, spread over {r['streams']} stream(s)", "layers": args.layers,
+                       "l2": f"the step streams {r['weight_bytes_per_step'] / 1e6:.0f} MB of weights, far more than the 126 MB L2"},
+            "decode": {k: r[k] for k in ("ms_per_step", "us_per_layer", "weight_GBps", "frac_hbm")},
             "roofline": {"kernel": "whole decode step (weight streaming through the grouped GEMMs)", "bound": "hbm",
-                         "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None},
-            "gpu_launches": launches, "cuda_graph": graph is not None, "streams": nstreams, "clocks": clocks.summary()}
+                         "achieved": r["weight_GBps"], "peak": peaks["hbm"], "unit": "GB/s", "frac": r["frac_hbm"], "traffic": None},
+            "gpu_launches": r["gpu_launches"], "cuda_graph": r["cuda_graph"], "streams": r["streams"], "clocks": r["clocks"]}
     print(json.dumps(line))
 
 
@@ -334,6 +409,8 @@ def main():
     ap.add_argument("--layers", type=int, default=24, help="layers of the decode config")
     ap.add_argument("--no-graph", action="store_true", help="decode config: plain launches instead of a CUDA graph")
     ap.add_argument("--streams", type=int, default=8, help="decode config: streams the independent layers are spread over")
+    ap.add_argument("--no-decode", action="store_true", help="one GPU: skip the decode object (config 2) after the headline run")
+    ap.add_argument("--no-skew", action="store_true", help="several GPUs: skip the skewed-routing object (config 4) after the headline run")
     ap.add_argument("--no-same-t", action="store_true", help="several GPUs: skip rank 0's one-GPU run at the same T")
     ap.add_argument("--ep-nccl-barriers", type=int, default=0, choices=[0, 1], help="1 = NCCL all-gathers as barriers instead of readiness flags")
     ap.add_argument("--ep-dispatch-kernel", type=int, default=0, choices=[0, 1], help="0 = bulk-copy dispatch, 1 = warp-per-token dispatch")
@@ -595,6 +672,23 @@ def main():
                         "recv_rows_per_gpu": [int(t.item()) for t in allrows],
                         "bias_after_step": [float(v) for v in layer.router_bias], "gamma": 1e-3}
         line["config"]["workload"] = line["config"]["workload"].replace("config 3", "config 4 (Zipf(1.2)-skewed router, seed 4)")
+    if world > 1 and args.config != 4 and not args.no_skew:
+        layer.close()
+        del xs, y
+        torch.cuda.empty_cache()
+        line["skew"] = skew_measure(args, dist, dev, rank, world, local_rank)
+    if n_gpus == 1 and not args.no_decode and not args.tokens:
+        # config 2 (decode) after the headline measurement, as a short object of the same line: 8 streams and 1 stream
+        layer.close()
+        del xs, y
+        torch.cuda.empty_cache()
+        dec = decode_measure(24, 30, 5, [8, 1])
+        line["decode"] = {"workload": "config 2: 24 independent MoE layers (seed 2+layer), T=64 tokens each, bf16, CUDA-graph replay; "
+                                      "weight-streaming GB/s = weight bytes of a step / time",
+                          "ms_per_step": dec[0]["ms_per_step"], "weight_GBps": dec[0]["weight_GBps"], "frac_hbm": dec[0]["frac_hbm"],
+                          "streams": dec[0]["streams"], "one_stream_ms": dec[1]["ms_per_step"], "one_stream_frac_hbm": dec[1]["frac_hbm"],
+                          "weight_bytes_per_step": dec[0]["weight_bytes_per_step"], "steps": 30,
+                          "gpu_launches_per_step": dec[0]["gpu_launches"] // 30}
     if rank == 0:
         if not args.no_cpu_baseline and n_gpus == 1:
             line["cpu_baseline"] = cpu_baseline(ws, bias, xs_host[0])
@@ -603,6 +697,8 @@ def main():
         dist.destroy_process_group()
     if "parity" in line and not line["parity"]["ok"]:
         raise SystemExit("parity check against the CPU oracle failed: " + json.dumps(line["parity"]))
+    if "skew" in line and not line["skew"]["parity"]["ok"]:
+        raise SystemExit("parity check of the skewed configuration failed: " + json.dumps(line["skew"]["parity"]))
 
 
 if __name__ == "__main__":

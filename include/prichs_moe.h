@@ -38,6 +38,7 @@ extern "C" {
 #define PRICHS_ERR_COMM (-4)      /* expert-parallel exchange failed or is not initialised                */
 #define PRICHS_ERR_TIMEOUT (-5)   /* a bounded device-side wait gave up (status word set by a kernel)     */
 #define PRICHS_ERR_BAD_ARG (-6)   /* null pointer, unknown dtype, weights not uploaded, ...               */
+#define PRICHS_ERR_BOUNDS (-7)    /* checking build only: a kernel computed a row index outside its buffer  */
 
 /* element types at the boundary (activations x / residual / y) */
 #define PRICHS_DTYPE_F32 0
@@ -85,6 +86,8 @@ typedef struct prichs_moe_config {
                              wave's (default), 1 = all, 2 = none                                                   */
     int ep_dispatch_kernel; /* expert parallel: 0 = rows travel as bulk copies through shared memory on the reserved SMs,
                              1 = one warp per token with 16-byte loads and stores                                  */
+    int ep_timeout_ms;    /* expert parallel: how long prichs_moe_sync_status waits for a forward before it aborts the
+                             communicators and returns PRICHS_ERR_COMM (0 = 60 s)                                  */
     int ep_nccl_barriers; /* expert parallel: 1 = "rows landed" / "outputs ready" are NCCL all-gathers used as barriers
                              (0: readiness flags the ranks write into each other's memory over NVLink)           */
 } prichs_moe_config_t;
@@ -283,6 +286,15 @@ PRICHS_API int prichs_moe_ep_unique_id(void* id_bytes);
 PRICHS_API int prichs_moe_ep_export(prichs_moe_t* h, void* blob128);
 PRICHS_API int prichs_moe_ep_init(prichs_moe_t* h, const void* id_bytes, const void* all_blobs);
 
+/* Host-side watchdog of the control plane (no counterpart in the reference, which has no communication). Polls
+ * query(ctx) -- 0 = finished, 1 = still running, anything else = failed -- every poll_us microseconds for at most
+ * timeout_ms milliseconds; when the time runs out it calls abort_fn(ctx) once (may be null) and returns PRICHS_ERR_COMM.
+ * prichs_moe_sync_status uses it for expert-parallel handles with a query on the forward's stream and the
+ * communicators' asynchronous error state, and an abort function that calls ncclCommAbort, so that a peer which
+ * never joins a collective costs ep_timeout_ms, not the process. After such an abort the handle refuses further
+ * forwards with PRICHS_ERR_COMM. Needs no GPU: the tests drive it with CPU ranks. */
+PRICHS_API int prichs_ep_wait_or_abort(int (*query)(void*), void (*abort_fn)(void*), void* ctx, int timeout_ms, int poll_us);
+
 /* Rows this rank's experts received in the last forward (expert-parallel load), host value. */
 PRICHS_API int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows);
 
@@ -290,6 +302,12 @@ PRICHS_API int prichs_moe_ep_recv_rows(prichs_moe_t* h, int64_t* rows);
 
 /* Message of the last error on the calling thread ("" if none). */
 PRICHS_API const char* prichs_last_error(void);
+
+/* 1 when this library was built with -DPRICHS_BOUNDS_CHECK (libprichs_moe_check.so): the routing-side kernels then
+ * compare every row index they compute with the extent of its buffer before a scatter or gather, record a violation
+ * in the status word (PRICHS_ERR_BOUNDS from prichs_moe_sync_status) and skip the access. The reference has no
+ * sanitizer use at all; this build stands in for a memory checker where none may be run. */
+PRICHS_API int prichs_bounds_checking(void);
 
 /* Number of kernels this library has launched since it was loaded (all handles). */
 PRICHS_API int64_t prichs_kernel_launches(void);

@@ -9,9 +9,12 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libprichs_moe.so")
+# PRICHS_B200_LIB selects another build of the same library for a whole process (the tests run the ragged cases
+# against the index-checking build, libprichs_moe_check.so, this way). Read here, on the Python side; the C library
+# itself reads no environment variable.
+LIB_PATH = os.environ.get("PRICHS_B200_LIB") or os.path.join(_PKG, "libprichs_moe.so")
 
-OK, ERR_BAD_SHAPE, ERR_CAPACITY, ERR_CUDA, ERR_COMM, ERR_TIMEOUT, ERR_BAD_ARG = 0, -1, -2, -3, -4, -5, -6
+OK, ERR_BAD_SHAPE, ERR_CAPACITY, ERR_CUDA, ERR_COMM, ERR_TIMEOUT, ERR_BAD_ARG, ERR_BOUNDS = 0, -1, -2, -3, -4, -5, -6, -7
 DTYPE_F32, DTYPE_BF16 = 0, 1
 MODE_BF16, MODE_F32 = 0, 1
 
@@ -22,10 +25,10 @@ class Config(C.Structure):
                                        # tuning (0 = default): see prichs_moe_config_t
                                        "route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl",
                                        "host_chunk_tokens", "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms",
-                                       "ep_combine_mode", "ep_dispatch_kernel", "ep_nccl_barriers")]
+                                       "ep_combine_mode", "ep_dispatch_kernel", "ep_timeout_ms", "ep_nccl_barriers")]
 
 TUNING_FIELDS = ("route_kernel", "scan_placement", "separate_prenorm", "gemm_kernel", "pdl", "host_chunk_tokens",
-                 "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms", "ep_combine_mode", "ep_dispatch_kernel", "ep_nccl_barriers")
+                 "router_ctas_per_sm", "ep_reserve_sms", "ep_shared_copy_sms", "ep_combine_mode", "ep_dispatch_kernel", "ep_timeout_ms", "ep_nccl_barriers")
 
 
 # name -> (restype, argtypes); the full export list of include/prichs_moe.h
@@ -53,8 +56,10 @@ SYMBOLS = {
     "prichs_moe_ep_unique_id": (C.c_int, [C.c_void_p]),
     "prichs_moe_ep_export": (C.c_int, [C.c_void_p, C.c_void_p]),
     "prichs_moe_ep_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "prichs_ep_wait_or_abort": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "prichs_moe_ep_recv_rows": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
     "prichs_last_error": (C.c_char_p, []),
+    "prichs_bounds_checking": (C.c_int, []),
     "prichs_kernel_launches": (C.c_int64, []),
     "prichs_moe_enable_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "prichs_moe_get_stage_ms": (C.c_int, [C.c_void_p, _fp]),

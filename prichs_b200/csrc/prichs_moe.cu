@@ -19,8 +19,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <mutex>
+#include <thread>
 #include <type_traits>
 #include <vector>
 
@@ -247,6 +249,8 @@ struct NcclApi {
     AllGatherFn all_gather = nullptr;
     CommDestroyFn comm_destroy = nullptr;
     GetErrorStringFn error_string = nullptr;
+    int (*comm_abort)(void*) = nullptr;             // optional: frees a collective that a missing peer keeps waiting
+    int (*comm_async_error)(void*, int*) = nullptr;  // optional: ncclCommGetAsyncError
     bool ok = false;
 };
 constexpr int NCCL_INT32 = 2;  // ncclInt32 in nccl.h
@@ -264,6 +268,8 @@ NcclApi& nccl() {
             api.all_gather = reinterpret_cast<NcclApi::AllGatherFn>(dlsym(lib, "ncclAllGather"));
             api.comm_destroy = reinterpret_cast<NcclApi::CommDestroyFn>(dlsym(lib, "ncclCommDestroy"));
             api.error_string = reinterpret_cast<NcclApi::GetErrorStringFn>(dlsym(lib, "ncclGetErrorString"));
+            api.comm_abort = reinterpret_cast<int (*)(void*)>(dlsym(lib, "ncclCommAbort"));
+            api.comm_async_error = reinterpret_cast<int (*)(void*, int*)>(dlsym(lib, "ncclCommGetAsyncError"));
             api.ok = api.get_unique_id && api.comm_init_rank && api.all_gather && api.comm_destroy && api.error_string;
         }
     }
@@ -346,6 +352,8 @@ struct prichs_moe {
                          // GEMM CTA leaves free, so these kernels only run on the reserved SMs (0 = share SMs)
     int* ep_flags;             // readiness flags written by the peers (tail of the expert-output allocation)
     void* flag_peer[route::MAX_RANKS];  // the same array of every rank
+    int ep_timeout_ms;         // host-side limit on waiting for an expert-parallel forward (prichs_moe_sync_status)
+    bool ep_broken;            // the communicators were aborted after such a wait ran out: the group must be rebuilt
     int ep_seq;                // sequence number of the expert-parallel forward being enqueued
     int ep_skip_signal;        // test knob: 1 + kind * 4 + wave of a signal this rank does not send (0: none)
     int ep_barrier_mode;       // 0: readiness flags over NVLink; 1: NCCL all-gathers as barriers
@@ -413,6 +421,7 @@ int translate_status(int s) {
     switch (s) {
         case 0: return PRICHS_OK;
         case -2: return fail(PRICHS_ERR_CAPACITY, "an expert received more rows than the permuted region holds");
+        case -7: return fail(PRICHS_ERR_BOUNDS, "an index check of the checking build failed: a kernel computed a row outside its buffer (the access was skipped)");
         case -5: return fail(PRICHS_ERR_TIMEOUT, "a bounded device-side wait gave up (expert GEMM or single-pass routing kernel)");
         default: return fail(PRICHS_ERR_CUDA, "device status word %d", s);
     }
@@ -520,7 +529,7 @@ int launch_combine(prichs_moe* h, const void* y_shared, const route::PeerPtrs& y
     const int res = !resid_dev ? 0 : (rdt == PRICHS_DTYPE_BF16 ? 1 : 2);
     const bool of32 = y_dtype == PRICHS_DTYPE_F32;
 #define COMBINE(YF, OF, RS) \
-    LAUNCH_K(pdl, (route::combine_kernel<YF, OF, RS>), grid, 256, dyn_smem, st, y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El)
+    LAUNCH_K(pdl, (route::combine_kernel<YF, OF, RS>), grid, 256, dyn_smem, st, y_shared, y_peers, routed_base_rows, sel, gates, pos, resid_dev, y_dev, T, h->d, h->El, h->Rcap, h->status)
     if (h->mode == PRICHS_MODE_F32) {
         if (of32) { if (res == 0) COMBINE(true, true, 0); else if (res == 1) COMBINE(true, true, 1); else COMBINE(true, true, 2); }
         else      { if (res == 0) COMBINE(true, false, 0); else if (res == 1) COMBINE(true, false, 1); else COMBINE(true, false, 2); }
@@ -692,10 +701,10 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
             // bulk copies through shared memory on the SMs the GEMMs leave free (its ring does not fit beside a GEMM CTA)
             const int grid = std::max(1, std::min((tn + route::TILE_TOKENS - 1) / route::TILE_TOKENS, std::max(2, h->ep_reserve_sms)));
             route::dispatch_bulk_kernel<<<grid, route::DB_THREADS, route::db_smem_bytes(h->K1 * 2, h->db_stages), ws>>>(
-                a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos, h->db_stages, h->rd_wait_cycles, h->status);
+                a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos, h->Rw, h->db_stages, h->rd_wait_cycles, h->status);
             LAUNCH_CHECK("dispatch");
         } else if (tn > 0) {
-            route::dispatch_kernel<<<std::min((tn + 7) / 8, 2 * h->sm_count), 256, h->ep_copy_smem, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos);
+            route::dispatch_kernel<<<std::min((tn + 7) / 8, 2 * h->sm_count), 256, h->ep_copy_smem, ws>>>(a_shared + (size_t)t0 * h->K1, h->K1, tn, sel, tprefix, wv.meta, xp_peers, h->El, pos, h->Rw, h->status);
             LAUNCH_CHECK("dispatch");
         }
         if (tl) cudaEventRecord(wv.tl[2], ws);
@@ -752,6 +761,13 @@ int forward_ep(prichs_moe* h, const void* x_dev, int x_dtype, const void* resid_
 extern "C" {
 
 const char* prichs_last_error(void) { return g_err; }
+int prichs_bounds_checking(void) {
+#ifdef PRICHS_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
 int64_t prichs_kernel_launches(void) { return (int64_t)g_launches.load(); }
 
 int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle) {
@@ -918,6 +934,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
         h->pdl = cfg->pdl != 2;
         h->ep_combine_mode = cfg->ep_combine_mode == 1 ? 0 : (cfg->ep_combine_mode == 2 ? 2 : 1);
         h->ep_barrier_mode = cfg->ep_nccl_barriers ? 1 : 0;
+        h->ep_timeout_ms = cfg->ep_timeout_ms > 0 ? cfg->ep_timeout_ms : 60000;
         h->db_stages = std::min(route::DB_MAX_STAGES, (200 * 1024) / (route::TILE_TOKENS * h->K1 * 2));
         h->ep_bulk_dispatch = world > 1 && cfg->ep_dispatch_kernel != 1 && h->db_stages >= 2 && h->ep_reserve_sms >= 2;
         if (h->ep_bulk_dispatch && rc == PRICHS_OK &&
@@ -1087,6 +1104,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         return fail(PRICHS_ERR_BAD_ARG, "the fp32-fidelity mode takes fp32 activations");
     if (n_concept < 0 || (n_concept > 0 && !concept_bias)) return fail(PRICHS_ERR_BAD_ARG, "concept bias length without data");
     if (h->world > 1 && !h->ep_ready) return fail(PRICHS_ERR_COMM, "expert-parallel exchange is not initialised");
+    if (h->ep_broken) return fail(PRICHS_ERR_COMM, "the expert-parallel group was aborted after a peer stopped answering: destroy the handles and connect again");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     h->last_stream = st;
     h->last_T = T;
@@ -1194,7 +1212,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     route::PeerPtrs xp_peers;
     for (int i = 0; i < route::MAX_RANKS; ++i) xp_peers.p[i] = h->xp;
     LAUNCH_K(pdl, route::dispatch_kernel, (T + 7) / 8, 256, 0, st, a_shared, h->K1, T, (const int*)sel, (const int*)h->tile_prefix,
-             (const route::RouteMeta*)h->meta, xp_peers, h->El, pos);
+             (const route::RouteMeta*)h->meta, xp_peers, h->El, pos, h->Rcap, h->status);
     LAUNCH_CHECK("dispatch");
     mark();
     }
@@ -1395,9 +1413,63 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     return translate_status(sdev);
 }
 
+// Host-side watchdog of the control plane. `query` says whether the awaited work has finished (0 = done, 1 = still
+// running, anything else = failed); it is polled every poll_us microseconds for at most timeout_ms milliseconds.
+// When the time runs out `abort_fn` (may be null) is called once -- the library passes a function that aborts its
+// NCCL communicators, which releases a collective that a peer never joined -- and PRICHS_ERR_COMM is returned.
+// Exported so that the policy can be exercised without a GPU (the tests drive it with gloo ranks one of which
+// never posts its counts).
+int prichs_ep_wait_or_abort(int (*query)(void*), void (*abort_fn)(void*), void* ctx, int timeout_ms, int poll_us) {
+    if (!query || timeout_ms < 0) return fail(PRICHS_ERR_BAD_ARG, "null query function or negative timeout");
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const int q = query(ctx);
+        if (q == 0) return PRICHS_OK;
+        if (q != 1) return fail(PRICHS_ERR_COMM, "the awaited work failed (query returned %d)", q);
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= timeout_ms) {
+            if (abort_fn) abort_fn(ctx);
+            return fail(PRICHS_ERR_COMM, "no answer from the expert-parallel group within %d ms: a peer never joined a collective; the communicators were aborted", timeout_ms);
+        }
+        if (poll_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(poll_us));
+    }
+}
+
+}  // extern "C"
+
+namespace {
+int ep_query_stream(void* ctx) {
+    prichs_moe* h = static_cast<prichs_moe*>(ctx);
+    const cudaError_t e = cudaStreamQuery(h->last_stream);
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorNotReady) return 2;
+    for (int w = 0; w < h->n_waves; ++w) {  // a communicator that reports an asynchronous error will not finish either
+        int st = 0;
+        if (h->wave[w].comm && nccl().comm_async_error && nccl().comm_async_error(h->wave[w].comm, &st) == 0 && st != 0) return 3;
+    }
+    return 1;
+}
+void ep_abort_comms(void* ctx) {
+    prichs_moe* h = static_cast<prichs_moe*>(ctx);
+    for (int w = 0; w < MAX_WAVES; ++w)
+        if (h->wave[w].comm && nccl().comm_abort) {
+            nccl().comm_abort(h->wave[w].comm);
+            h->wave[w].comm = nullptr;
+        }
+    h->ep_broken = true;
+}
+}  // namespace
+
+extern "C" {
+
 int prichs_moe_sync_status(prichs_moe_t* h) {
     if (!h) return fail(PRICHS_ERR_BAD_ARG, "null handle");
     DeviceGuard guard(h->device);
+    if (h->world > 1 && h->ep_ready) {
+        // an expert-parallel forward holds collectives: wait with a limit instead of blocking for ever on a lost peer
+        const int rc = prichs_ep_wait_or_abort(ep_query_stream, ep_abort_comms, h, h->ep_timeout_ms, 50);
+        if (rc != PRICHS_OK) return rc;
+    }
     CUDA_TRY(cudaStreamSynchronize(h->last_stream));
     int s = 0;
     CUDA_TRY(cudaMemcpy(&s, h->status, sizeof(int), cudaMemcpyDeviceToHost));

@@ -17,6 +17,17 @@
 
 #include "ptx_sm100.cuh"
 
+// Index checking build (-DPRICHS_BOUNDS_CHECK, libprichs_moe_check.so): every row index the routing-side kernels
+// compute before a scatter or a gather is compared with the extent of its buffer; a violation records -7 in the
+// status word (PRICHS_ERR_BOUNDS) and the access is skipped -- no trap, no fault. The product build compiles the
+// checks away. Stands in for a memory checker on machines where none may be run.
+#ifdef PRICHS_BOUNDS_CHECK
+#define PRICHS_ROW_OK(idx, limit, status) \
+    (((long long)(idx) >= 0 && (long long)(idx) < (long long)(limit)) ? true : (atomicExch((status), -7), false))
+#else
+#define PRICHS_ROW_OK(idx, limit, status) true
+#endif
+
 namespace route {
 
 constexpr int MAX_E = 8;      // routed experts supported by the 8-column router MMA
@@ -728,11 +739,13 @@ route_dispatch_kernel(const __grid_constant__ RouteDispatchArgs a, const Concept
                     e1 = (rs.i1 == e) ? run[e] : e1;
                     e2 = (rs.i2 == e) ? run[e] : e2;
                 }
-                const int p1 = rs.i1 * a.seg_stride + e1 + rs.r1;
-                const int p2 = rs.i2 >= 0 ? rs.i2 * a.seg_stride + e2 + rs.r2 : -1;
+                int p1 = rs.i1 * a.seg_stride + e1 + rs.r1;
+                int p2 = rs.i2 >= 0 ? rs.i2 * a.seg_stride + e2 + rs.r2 : -1;
+                if (!PRICHS_ROW_OK(e1 + rs.r1, a.seg_stride, a.status)) p1 = -1;
+                if (p2 >= 0 && !PRICHS_ROW_OK(e2 + rs.r2, a.seg_stride, a.status)) p2 = -1;
                 *reinterpret_cast<int2*>(a.pos + (size_t)row * 2) = make_int2(p1, p2);
                 const uint8_t* src = stage + (size_t)lrow * rowb;
-                ptx::bulk_store_1d(a.xp + (size_t)p1 * d, src, (uint32_t)(2 * d));
+                if (p1 >= 0) ptx::bulk_store_1d(a.xp + (size_t)p1 * d, src, (uint32_t)(2 * d));
                 if (p2 >= 0) ptx::bulk_store_1d(a.xp + (size_t)p2 * d, src, (uint32_t)(2 * d));
                 ptx::bulk_commit();
                 ptx::bulk_wait_read<0>();
@@ -1032,7 +1045,7 @@ plan_kernel(RouteMeta* meta, int* __restrict__ mtile_slot, int E, int El, int wo
 __global__ void __launch_bounds__(256)
 dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, const int* __restrict__ sel,
                 const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
-                int* __restrict__ pos) {
+                int* __restrict__ pos, int cap_rows, int* __restrict__ status) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
@@ -1047,6 +1060,7 @@ dispatch_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, cons
             const int e = s & 0xff, lr = s >> 8;
             my_row = meta->seg_base[e] + meta->src_off[e] + tile_prefix[(size_t)(t / TILE_TOKENS) * MAX_E + e] + lr;
             my_owner = e / El;
+            if (!PRICHS_ROW_OK(my_row, cap_rows, status)) my_row = -1;
             pos[(size_t)t * 2 + lane] = my_row;
         } else {
             pos[(size_t)t * 2 + lane] = -1;
@@ -1083,7 +1097,7 @@ __host__ __device__ inline int db_smem_bytes(int row_bytes, int stages) { return
 __global__ void __launch_bounds__(DB_THREADS, 1)
 dispatch_bulk_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T, const int* __restrict__ sel,
                      const int* __restrict__ tile_prefix, const RouteMeta* __restrict__ meta, const __grid_constant__ PeerPtrs dst, int El,
-                     int* __restrict__ pos, int stages, long long wait_cycles, int* __restrict__ status) {
+                     int* __restrict__ pos, int cap_rows, int stages, long long wait_cycles, int* __restrict__ status) {
     extern __shared__ __align__(128) uint8_t dsm[];
     const int row_bytes = row_elems * 2;
     const int stage_bytes = TILE_TOKENS * row_bytes;
@@ -1146,6 +1160,8 @@ dispatch_bulk_kernel(const __nv_bfloat16* __restrict__ xs, int row_elems, int T,
                     row1 = meta->seg_base[e] + meta->src_off[e] + tile_prefix[(size_t)tile * MAX_E + e] + (s2.y >> 8);
                     own1 = e / El;
                 }
+                if (row0 >= 0 && !PRICHS_ROW_OK(row0, cap_rows, status)) row0 = -1;
+                if (row1 >= 0 && !PRICHS_ROW_OK(row1, cap_rows, status)) row1 = -1;
                 *reinterpret_cast<int2*>(pos + (size_t)t * 2) = make_int2(row0, row1);
             }
             if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&full_bar[warp], (uint32_t)(n & 1), abort_flag, wait_cycles))) break;
@@ -1217,7 +1233,7 @@ template <bool YF32, bool OUTF32, int RES>
 __global__ void __launch_bounds__(256)
 combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtrs y_peers, long long routed_base_rows,
                const int* __restrict__ sel, const float* __restrict__ gates, const int* __restrict__ pos,
-               const void* __restrict__ resid, void* __restrict__ out, int T, int d, int El) {
+               const void* __restrict__ resid, void* __restrict__ out, int T, int d, int El, int cap_rows, int* __restrict__ status) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
@@ -1234,6 +1250,9 @@ combine_kernel(const void* __restrict__ y_local, const __grid_constant__ PeerPtr
         const float tf = ga; ga = gb; gb = tf;
     }
     const bool has_b = eb >= 0;
+#ifdef PRICHS_BOUNDS_CHECK
+    if (!PRICHS_ROW_OK(pa, cap_rows, status) || (has_b && !PRICHS_ROW_OK(pb, cap_rows, status)) || ea / El >= MAX_RANKS) continue;
+#endif
     using YT = typename std::conditional<YF32, float, __nv_bfloat16>::type;
     const YT* ys = reinterpret_cast<const YT*>(y_local) + (size_t)t * d;
     const YT* ya = reinterpret_cast<const YT*>(y_peers.p[ea / El]) + (size_t)(routed_base_rows + pa) * d;

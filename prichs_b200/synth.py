@@ -68,19 +68,28 @@ def from_bf16_bits(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << np.uint32(16)).view(np.float32)
 
 
-def layer_weights(seed: int, d: int, f: int, E: int, std: float = 0.02, bf16: bool = False):
+def layer_weights(seed: int, d: int, f: int, E: int, std: float = 0.02, bf16: bool = False, threads: int = 0):
     """Weights of one MoE layer in the reference's parameter order (crates/prichs-model/src/model.rs:353-361):
-    [router [d,E], shared gate [d,f], up [d,f], down [f,d], expert0 gate, up, down, ...], all ~ N(0, std)."""
-    ws = [normal(seed, 1, (d, E), 0.0, std)]
+    [router [d,E], shared gate [d,f], up [d,f], down [f,d], expert0 gate, up, down, ...], all ~ N(0, std).
+    The tensors are independent streams of the counter-based generator, so they are generated on a thread pool
+    (numpy releases the interpreter lock inside its array operations); the values do not depend on `threads`."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    jobs = [(1, (d, E))]
     tid = 2
     for _ in range(1 + E):
-        ws.append(normal(seed, tid, (d, f), 0.0, std))
-        ws.append(normal(seed, tid + 1, (d, f), 0.0, std))
-        ws.append(normal(seed, tid + 2, (f, d), 0.0, std))
+        jobs += [(tid, (d, f)), (tid + 1, (d, f)), (tid + 2, (f, d))]
         tid += 3
-    if bf16:
-        ws = [round_bf16(w) for w in ws]
-    return ws
+
+    def make(job):
+        w = normal(seed, job[0], job[1], 0.0, std)
+        return round_bf16(w) if bf16 else w
+
+    n = threads or min(len(jobs), os.cpu_count() or 1)
+    if n <= 1:
+        return [make(j) for j in jobs]
+    with ThreadPoolExecutor(max_workers=n) as pool:
+        return list(pool.map(make, jobs))
 
 
 def tokens(seed: int, T: int, d: int, bf16: bool = False) -> np.ndarray:

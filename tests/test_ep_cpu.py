@@ -120,3 +120,68 @@ def test_plan_properties():
             assert all(int(pl["seg_base"][e]) == int(plans[o]["seg_base"][e]) for pl in plans)
             assert plans[o]["seg_base"][e] % 256 == 0
         assert sum(pl["recv_rows"] for pl in plans) == int(cmat.sum())
+
+
+# ---- failure detection on the host: a rank that never posts its counts -------------------------------------------
+def _lost_peer_worker(rank, world, port, ret):
+    """Rank 0 starts the counts all-gather of a wave and waits for it under the library's watchdog
+    (prichs_ep_wait_or_abort through the C-ABI); rank 1 takes part in the first exchange and then stops answering
+    (it never posts the counts of the second one). Rank 0 must get PRICHS_OK for the first, PRICHS_ERR_COMM for the
+    second after the timeout, with its abort callback called exactly once. No GPU is involved."""
+    sys.path.insert(0, ROOT)
+    import ctypes as C
+    import time
+    import torch
+    import torch.distributed as dist
+    from prichs_b200 import _capi
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    L = _capi.lib()
+    QUERY = C.CFUNCTYPE(C.c_int, C.c_void_p)
+    ABORT = C.CFUNCTYPE(None, C.c_void_p)
+    state = {"work": None, "aborted": 0}
+    query = QUERY(lambda ctx: 0 if state["work"].is_completed() else 1)
+
+    def _abort(ctx):
+        state["aborted"] += 1
+    abort = ABORT(_abort)
+
+    def gather_counts(counts):
+        out = [torch.zeros(8, dtype=torch.int32) for _ in range(world)]
+        state["work"] = dist.all_gather(out, torch.tensor(counts, dtype=torch.int32), async_op=True)
+        return out
+
+    # healthy exchange: both ranks post
+    out = gather_counts([rank + 1] * 8)
+    rc_ok = L.prichs_ep_wait_or_abort(C.cast(query, C.c_void_p), C.cast(abort, C.c_void_p), None, 20000, 200)
+    healthy = rc_ok == _capi.OK and int(out[1 - rank][0]) == (1 - rank) + 1 and state["aborted"] == 0
+    if rank == 1:
+        # the lost peer: it never posts its counts of the next wave
+        ret[rank] = bool(healthy)
+        time.sleep(4.0)
+        os._exit(0)
+    gather_counts([7] * 8)
+    t0 = time.time()
+    rc = L.prichs_ep_wait_or_abort(C.cast(query, C.c_void_p), C.cast(abort, C.c_void_p), None, 500, 200)
+    waited = time.time() - t0
+    msg = _capi.last_error()
+    ret[rank] = bool(healthy and rc == _capi.ERR_COMM and state["aborted"] == 1 and 0.4 <= waited < 3.0 and "never joined" in msg)
+    # a query that reports failure ends the wait at once, without the abort callback
+    failed = QUERY(lambda ctx: 5)
+    ret["failed_query"] = L.prichs_ep_wait_or_abort(C.cast(failed, C.c_void_p), C.cast(abort, C.c_void_p), None, 500, 200) == _capi.ERR_COMM \
+        and state["aborted"] == 1
+    os._exit(0)  # the process group still holds the collective that will never finish: leave without tearing it down
+
+
+def test_rank_that_never_posts_its_counts_is_detected_by_the_watchdog():
+    import time
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29810 + os.getpid() % 150
+    ctx = mp.spawn(_lost_peer_worker, args=(world, port, ret), nprocs=world, join=False)
+    deadline = time.time() + 120
+    while not ctx.join(timeout=2):
+        assert time.time() < deadline, "ranks did not finish"
+    assert dict(ret) == {0: True, 1: True, "failed_query": True}
