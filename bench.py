@@ -292,7 +292,7 @@ def zipf_router(ws_router, seed, n_sample=65536, iters=60):
     return synth.round_bf16((ws_router * sigma[None, :].astype(np.float32))), sigma, share, target
 
 
-def decode_measure(n_layers, steps, warmup, stream_counts, use_graph=True):
+def decode_measure(n_layers, steps, warmup, stream_counts, use_graph=True, **tuning):
     """Config 2 (decode shape, bandwidth bound): `n_layers` independent MoE layers of the production dimensions, each
     with its own seeded weights (seed 2 + layer), applied to the same T = 64 tokens; one step = all layer forwards.
     The layers are independent by the config's definition, so they may be spread over several streams: the small
@@ -306,7 +306,7 @@ def decode_measure(n_layers, steps, warmup, stream_counts, use_graph=True):
     x = torch.from_numpy(synth.to_bf16_bits(x_host).view(np.int16)).view(torch.bfloat16).to(dev)
     layers = []
     for l in range(n_layers):
-        m = MoELayer.from_weights(synth.layer_weights(2 + l, D, F, E, bf16=True), K, max_tokens=T, device=dev.index)
+        m = MoELayer.from_weights(synth.layer_weights(2 + l, D, F, E, bf16=True), K, max_tokens=T, device=dev.index, **tuning)
         m.forward(x)  # creates the handle and uploads the weights
         m.router = m.shared_expert = None  # the host copies are not needed any more
         m.experts = []
@@ -379,7 +379,8 @@ def run_decode(args):
     import torch
     torch.cuda.set_device(0)
     peaks = measured_peaks()
-    r = decode_measure(args.layers, args.steps, args.warmup, [max(1, args.streams)], use_graph=not args.no_graph)[0]
+    r = decode_measure(args.layers, args.steps, args.warmup, [max(1, args.streams)], use_graph=not args.no_graph,
+                       route_kernel=args.route_kernel, pdl=args.pdl, gemm_kernel=args.gemm_kernel)[0]
     line = {"metric": "MoE-layer tokens/sec", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",

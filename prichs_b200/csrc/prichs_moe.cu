@@ -1150,6 +1150,11 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     const int ntiles = (T + route::TILE_TOKENS - 1) / route::TILE_TOKENS;
     mark();
     const bool pdl = h->pdl;
+    // Granularity of the GEMM tile table. The CTA-pair kernel walks 256-row tile pairs, so a segment's rows are
+    // rounded up to 256. A small batch runs on the one-CTA kernel (128-row tiles): rounding to 128 leaves no tile of
+    // padding rows in the table, so the few tiles of a decode step spread evenly over the SMs (with 256 a CTA that
+    // draws a padding tile idles while another works through two real ones).
+    const int tile_pad = (h->pair_gemm && !h->small_batch) ? SEG_PAD : 128;
     // Routing stage. Single pass (one kernel routes, places and dispatches) when the rows are bf16 as they arrive:
     // from 1024 tokens up by default, always / never with route_kernel = 1 / 2. Otherwise three launches.
     const int rd_stages = h->rd_stages[h->rt_nsplit == 1 ? 0 : 1];
@@ -1165,7 +1170,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         ra.logits = logits; ra.sel = sel; ra.gates = gates; ra.pos = pos;
         ra.tile_counts = h->tile_counts; ra.tile_prefix = h->tile_prefix;
         ra.tile_state = h->tile_state; ra.ctl = h->rd_ctl;
-        ra.xp = h->xp; ra.seg_stride = h->seg_stride; ra.pad_rows = SEG_PAD;
+        ra.xp = h->xp; ra.seg_stride = h->seg_stride; ra.pad_rows = tile_pad;
         ra.meta = h->meta; ra.mtile_slot = h->mtile_slot; ra.mtile_row = h->mtile_row;
         ra.status = h->status;
         ra.wait_cycles = h->rd_wait_cycles;
@@ -1195,7 +1200,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         tail.mtile_row = h->mtile_row;
         tail.El = h->El;
         tail.cap_rows = h->Rcap;
-        tail.pad_rows = SEG_PAD;
+        tail.pad_rows = tile_pad;
         tail.seg_stride = h->seg_stride;
         tail.status = h->status;
     }
@@ -1204,7 +1209,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
     mark();
     if (!scan_in_router) {
         LAUNCH_K(pdl, route::scan_kernel, 1, 1024, 0, st, (const int*)h->tile_counts, h->tile_prefix, ntiles, h->meta, h->mtile_slot, h->mtile_row,
-                 E, h->El, 1, 0, h->Rcap, 1, SEG_PAD, h->seg_stride, h->status);
+                 E, h->El, 1, 0, h->Rcap, 1, tile_pad, h->seg_stride, h->status);
         LAUNCH_CHECK("scan");
     }
     mark();
@@ -1376,6 +1381,15 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     cudaStream_t st = h->own_stream;
     const size_t row = (size_t)h->d;
     int rc = PRICHS_OK;
+    // Chunk forwards are short and interleaved with copies on two other streams; measured on B200, kernels that are
+    // launched early (programmatic dependent launch) and then wait on the SMs slow this pipeline down by a tenth,
+    // while they gain a little on the device-resident path. So the chunks are launched without it.
+    struct PdlOff {
+        prichs_moe* h;
+        bool saved;
+        explicit PdlOff(prichs_moe* hh) : h(hh), saved(hh->pdl) { h->pdl = false; }
+        ~PdlOff() { h->pdl = saved; }
+    } pdl_off(h);
     for (int c = 0; c < nchunks && rc == PRICHS_OK; ++c) {
         const int t0 = bound(c), tc = bound(c + 1) - t0;
         const size_t off = (size_t)t0 * row, bytes = (size_t)tc * row * sizeof(float);
