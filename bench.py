@@ -170,7 +170,7 @@ def skew_measure(args, dist, dev, rank, world, local_rank, steps=20):
     bias = np.zeros(E, np.float32)
     layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves,
                                   ep_nccl_barriers=args.ep_nccl_barriers, ep_reserve_sms=args.ep_reserve_sms,
-                                  ep_dispatch_kernel=args.ep_dispatch_kernel)
+                                  ep_dispatch_kernel=args.ep_dispatch_kernel, ep_shared_copy_sms=args.ep_shared_copy_sms)
     for e in range(E):
         if e // (E // world) != rank:
             layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
@@ -415,6 +415,7 @@ def main():
     ap.add_argument("--no-same-t", action="store_true", help="several GPUs: skip rank 0's one-GPU run at the same T")
     ap.add_argument("--ep-nccl-barriers", type=int, default=0, choices=[0, 1], help="1 = NCCL all-gathers as barriers instead of readiness flags")
     ap.add_argument("--ep-dispatch-kernel", type=int, default=0, choices=[0, 1], help="0 = bulk-copy dispatch, 1 = warp-per-token dispatch")
+    ap.add_argument("--ep-shared-copy-sms", type=int, default=0, choices=[0, 1], help="1 = dispatch / combine may share SMs with GEMM CTAs")
     ap.add_argument("--ep-reserve-sms", type=int, default=0, help="SMs the expert-parallel GEMM launches leave free (0 = default, -1 = none)")
     ap.add_argument("--route-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="single GPU: 0 = library default, 1 = single-pass routing kernel, 2 = router / scan / dispatch launches")
@@ -486,7 +487,7 @@ def main():
             torch.cuda.empty_cache()
         layer = MoELayer.from_weights(ws, K, max_tokens=T, device=local_rank, ep_world=world, ep_rank=rank, ep_waves=args.ep_waves,
                                       ep_nccl_barriers=args.ep_nccl_barriers, ep_reserve_sms=args.ep_reserve_sms,
-                                      ep_dispatch_kernel=args.ep_dispatch_kernel)
+                                      ep_dispatch_kernel=args.ep_dispatch_kernel, ep_shared_copy_sms=args.ep_shared_copy_sms)
         for e in range(E):  # only the experts this rank owns are uploaded
             if e // (E // world) != rank:
                 layer.experts[e].gate_proj = layer.experts[e].up_proj = layer.experts[e].down_proj = None
@@ -569,7 +570,14 @@ def main():
     layer.sync_status()
 
     ms_step = ms_total / args.steps
+    # host link rate each rank saw in its own end-to-end loop (bytes of one direction / its wall time)
+    my_gbs = T * D * 4 * e2e_steps / e2e_dt / 1e9
+    rank_gbs = [my_gbs]
     if world > 1:
+        g = torch.tensor([my_gbs], device=dev, dtype=torch.float64)
+        allg = [torch.zeros_like(g) for _ in range(world)]
+        dist.all_gather(allg, g)
+        rank_gbs = [float(v[0]) for v in allg]
         t = torch.tensor([ms_step, e2e_dt], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_dt = float(t[0]), float(t[1])
@@ -633,8 +641,9 @@ def main():
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(n_gpus) if not args.tokens else {"workload": f"NOT the baseline config: T={T} override for profiling"},
-        "e2e": {"value": tokens * e2e_steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 4,
-                "d2h_bytes_per_step": T * D * 4, "steps": e2e_steps,
+        "e2e": {"value": tokens * e2e_steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * 4 * n_gpus,
+                "d2h_bytes_per_step": T * D * 4 * n_gpus, "bytes_per_rank_and_direction": T * D * 4, "steps": e2e_steps,
+                "h2d_gbs": [round(v, 2) for v in rank_gbs], "d2h_gbs": [round(v, 2) for v in rank_gbs],
                 "api": "MoELayer.forward(numpy fp32 [T,d]) -> prichs_moe_forward_host, pinned host buffers"},
         "gpu_launches": launches, "roofline": roofline, "stages": stages, "ep_timeline": timeline,
         "layer_tflops": tokens * FLOPS_PER_TOKEN / (ms_step * 1e-3) / 1e12,

@@ -97,12 +97,22 @@ struct Expert {
     }
 };
 
-// Routing part of moe.rs:44-53; the activation stashes of the backward pass are not produced by this
-// forward-only library. expert_token_counts are the lengths of the expert bins (moe.rs:121,140).
+// moe.rs:32-42: what one routed expert contributes to the stash (experts without tokens have no entry).
+struct ExpertForwardStash {
+    size_t expert_idx = 0;
+    std::vector<size_t> token_indices;  // ascending
+    std::vector<float> weights;         // gate weights of those tokens
+    std::vector<float> x, gate, up, act, out;  // [n, d], [n, f], [n, f], [n, f], [n, d]
+};
+
+// moe.rs:44-53. expert_token_counts are the lengths of the expert bins (moe.rs:121,140). The activation vectors are
+// filled by forward_train (they are downloaded from the device stash the training forward keeps).
 struct MoEStash {
     std::vector<float> router_logits;       // [T, E]
     std::vector<size_t> selected_experts;   // [T * k], slot order = descending selection logit
     std::vector<float> gating_weights;      // [T * k]
+    std::vector<float> shared_gate, shared_up, shared_act, shared_out;  // [T, f] x 3, [T, d]
+    std::vector<ExpertForwardStash> routed_stashes;
     std::vector<size_t> expert_token_counts;  // [E]
 };
 
@@ -155,19 +165,52 @@ class MoELayer {
         return y;
     }
 
-    // moe.rs:93-211
+    // moe.rs:93-211. Runs the engine-shaped call sequence (the order of model.rs:1327-1408): one grouped training
+    // forward on the device, then views of its result.
     std::pair<Tensor, MoEStash> forward_train(const Tensor& x, const std::vector<float>* starkdb_concept_bias) {
-        Tensor y = forward_with_memory(x, starkdb_concept_bias);
+        if (starkdb_concept_bias || mode_ != PRICHS_MODE_BF16) {  // the engine call shape has no concept bias argument
+            Tensor y0 = forward_with_memory(x, starkdb_concept_bias);
+            return {std::move(y0), routing_stash()};
+        }
+        if (x.dims().size() != 2 || x.dims()[1] != hidden_)
+            throw Error(PRICHS_ERR_BAD_SHAPE, "Incompatible shapes for matmul: x must be [seq_len, hidden_dim]");
+        const size_t T = x.dims()[0], E = experts.size();
+        ensure(T);
+        check(prichs_moe_set_bias(h_, router_bias.data(), (int)router_bias.size()));
         MoEStash st;
-        const size_t T = last_T_, E = experts.size();
+        st.shared_gate.resize(T * inter_);
+        st.shared_up.resize(T * inter_);
+        st.shared_act.resize(T * inter_);
+        st.shared_out.resize(T * hidden_);
+        check(prichs_engine_moe_forward_shared(h_, x.as_f32_slice(), 0, PRICHS_DTYPE_F32, T, st.shared_gate.data(), st.shared_up.data(),
+                                               st.shared_act.data(), st.shared_out.data()));
+        last_T_ = T;
         st.router_logits.resize(T * E);
+        st.selected_experts.resize(T * top_k);
         st.gating_weights.resize(T * top_k);
-        std::vector<int32_t> sel(T * top_k);
-        if (T) check(prichs_moe_get_routing(h_, st.router_logits.data(), sel.data(), st.gating_weights.data(), (int)T));
-        st.selected_experts.assign(sel.begin(), sel.end());
-        std::vector<int64_t> counts(E, 0);
-        check(prichs_moe_get_counts(h_, counts.data(), (int)E));
-        st.expert_token_counts.assign(counts.begin(), counts.end());
+        check(prichs_engine_moe_routing(h_, st.router_logits.data(), st.selected_experts.data(), st.gating_weights.data(), T));
+        st.expert_token_counts.assign(E, 0);
+        for (size_t e = 0; e < E; ++e) {
+            size_t n = 0;
+            check(prichs_engine_moe_forward_expert(h_, (int)e, nullptr, nullptr, 0, &n, nullptr, nullptr, nullptr, nullptr, nullptr));
+            st.expert_token_counts[e] = n;
+            if (n == 0) continue;  // model.rs:1366
+            ExpertForwardStash es;
+            es.expert_idx = e;
+            std::vector<int32_t> idx(n);
+            es.weights.resize(n);
+            es.x.resize(n * hidden_);
+            es.out.resize(n * hidden_);
+            es.gate.resize(n * inter_);
+            es.up.resize(n * inter_);
+            es.act.resize(n * inter_);
+            check(prichs_engine_moe_forward_expert(h_, (int)e, idx.data(), es.weights.data(), n, &n, es.x.data(), es.gate.data(),
+                                                   es.up.data(), es.act.data(), es.out.data()));
+            es.token_indices.assign(idx.begin(), idx.end());
+            st.routed_stashes.push_back(std::move(es));
+        }
+        Tensor y = Tensor::zeros({T, hidden_});
+        check(prichs_engine_moe_finalize_forward(h_, y.as_f32_slice_mut(), T * hidden_));
         return {std::move(y), std::move(st)};
     }
 
@@ -182,6 +225,20 @@ class MoELayer {
     }
 
    private:
+    MoEStash routing_stash() {
+        MoEStash st;
+        const size_t T = last_T_, E = experts.size();
+        st.router_logits.resize(T * E);
+        st.gating_weights.resize(T * top_k);
+        std::vector<int32_t> sel(T * top_k);
+        if (T) check(prichs_moe_get_routing(h_, st.router_logits.data(), sel.data(), st.gating_weights.data(), (int)T));
+        st.selected_experts.assign(sel.begin(), sel.end());
+        std::vector<int64_t> counts(E, 0);
+        check(prichs_moe_get_counts(h_, counts.data(), (int)E));
+        st.expert_token_counts.assign(counts.begin(), counts.end());
+        return st;
+    }
+
     void ensure(size_t T) {
         if (!h_ || T > cap_) {
             if (h_) prichs_moe_destroy(h_);

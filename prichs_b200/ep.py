@@ -70,3 +70,42 @@ def connect(layer, dist, max_tokens: int):
     if rc != 0:
         raise RuntimeError(_capi.last_error())
     layer._ep_connected = True
+
+
+class FlagBoard:
+    """Host restatement of the readiness flags of the expert-parallel exchange (route::ep_signal_kernel /
+    ep_wait_kernel) over any key-value store with `set` / `get`: slot [kind][wave][source] of rank `dst`'s flag array
+    holds the sequence number of the last forward whose part `kind` of `wave` rank `source` has finished. Tests use it to
+    exercise the protocol (ordering, growing sequence numbers, bounded wait) on CPU ranks; it is not on the data path."""
+    OK, TIMEOUT = 0, -5
+
+    def __init__(self, store, rank: int, world: int):
+        self.store, self.rank, self.world = store, rank, world
+
+    @staticmethod
+    def _key(dst, kind, wave, src):
+        return f"flag/{dst}/{kind}/{wave}/{src}"
+
+    @staticmethod
+    def reached(value: int, seq: int) -> bool:
+        """`value - seq >= 0` in 32-bit wrap-around arithmetic, as the device compares sequence numbers."""
+        diff = (value - seq) & 0xFFFFFFFF
+        return diff < 0x80000000
+
+    def signal(self, kind: int, wave: int, seq: int, dst: int):
+        self.store.set(self._key(dst, kind, wave, self.rank), str(seq))
+
+    def wait(self, kind: int, wave: int, seq: int, budget_s: float) -> int:
+        import time
+        deadline = time.time() + budget_s
+        pending = set(range(self.world))
+        while pending:
+            for src in list(pending):
+                key = self._key(self.rank, kind, wave, src)
+                if self.store.check([key]) and self.reached(int(self.store.get(key).decode()), seq):
+                    pending.discard(src)
+            if pending and time.time() > deadline:
+                return self.TIMEOUT
+            if pending:
+                time.sleep(0.002)
+        return self.OK

@@ -62,6 +62,20 @@ int main() {
     }
     REQUIRE(stash.expert_token_counts == (std::vector<size_t>{T, T}));
     REQUIRE(std::fabs(stash.router_logits[0] - 256 * 0.5f * 0.1f) < 1e-3f);
+    // the activation stash (moe.rs:32-53): lengths as the reference's test expects them, values from the closed form
+    REQUIRE(stash.shared_gate.size() == T * f && stash.shared_up.size() == T * f && stash.shared_act.size() == T * f);
+    REQUIRE(stash.shared_out.size() == T * d && stash.routed_stashes.size() == E);
+    for (float v : stash.shared_gate) REQUIRE(std::fabs(v - 0.2f) <= 2e-3f);
+    for (float v : stash.shared_act) REQUIRE(std::fabs(v - act) <= 2e-2 * act);
+    for (float v : stash.shared_out) REQUIRE(std::fabs(v - row) <= 2e-2 * row);
+    for (size_t e = 0; e < E; ++e) {
+        const prichs::ExpertForwardStash& es = stash.routed_stashes[e];
+        REQUIRE(es.expert_idx == e && es.token_indices == (std::vector<size_t>{0, 1}) && es.weights.size() == T);
+        REQUIRE(es.x.size() == T * d && es.gate.size() == T * f && es.up.size() == T * f && es.out.size() == T * d);
+        for (float v : es.x) REQUIRE(v == 0.5f);
+        for (float v : es.up) REQUIRE(std::fabs(v - 0.2f) <= 2e-3f);
+        for (float v : es.out) REQUIRE(std::fabs(v - row) <= 2e-2 * row);
+    }
 
     // forward == forward_with_memory(None); a concept bias only moves the selection (moe.rs:128-132)
     Tensor out2 = layer.forward(x);

@@ -185,3 +185,59 @@ def test_rank_that_never_posts_its_counts_is_detected_by_the_watchdog():
     while not ctx.join(timeout=2):
         assert time.time() < deadline, "ranks did not finish"
     assert dict(ret) == {0: True, 1: True, "failed_query": True}
+
+
+# ---- readiness-flag protocol on CPU ranks ---------------------------------------------------------------------------
+def _flag_worker(rank, world, port, ret):
+    """Host model of the expert-parallel exchange's readiness flags (route::ep_signal_kernel / ep_wait_kernel) with the
+    process group's key-value store standing in for peer-mapped memory: "store rows into the owner's receive region,
+    then store the forward's sequence number into slot [kind][wave][source] of the owner's flag array"; the owner polls
+    its own slots with a budget and only then reads the rows. Three forwards of two waves: the rows a rank reads after a
+    successful wait belong to that forward or a later one, never an earlier one (sequence numbers only grow, nothing is
+    reset); a withheld signal makes every rank's wait run out and report a timeout, and the next forward works again;
+    a signal of an older forward never satisfies a wait for a newer one."""
+    sys.path.insert(0, ROOT)
+    import time
+    import torch.distributed as dist
+    from prichs_b200 import ep
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    board = ep.FlagBoard(store, rank, world)
+    ok = True
+    for seq in (1, 2, 3):
+        for wave in (0, 1):
+            for dst in range(world):  # "dispatch": this rank's rows of the wave land in every owner's region ...
+                store.set(f"rows/{dst}/{wave}/{rank}", f"{seq}:{rank}")
+                withheld = seq == 2 and wave == 1 and rank == 1
+                if not withheld:          # ... and only then the signal is stored
+                    board.signal(0, wave, seq, dst)
+            status = board.wait(0, wave, seq, budget_s=0.5 if seq == 2 else 20.0)
+            if seq == 2 and wave == 1:
+                ok = ok and status == ep.FlagBoard.TIMEOUT  # every rank misses rank 1's signal
+            else:
+                ok = ok and status == ep.FlagBoard.OK
+                for src in range(world):  # the rows seen after the wait are at least this forward's
+                    s_, r_ = store.get(f"rows/{rank}/{wave}/{src}").decode().split(":")
+                    ok = ok and int(s_) >= seq and int(r_) == src
+        dist.barrier()
+    # a signal from an OLDER forward never satisfies a wait for a newer one; a newer one does (wrap-safe comparison)
+    ok = ok and board.wait(0, 0, 4, budget_s=0.2) == ep.FlagBoard.TIMEOUT
+    ok = ok and ep.FlagBoard.reached(5 - 2 ** 32, 2 ** 31 - 3 - 2 ** 32) is False and ep.FlagBoard.reached(-2 ** 31 + 1, 2 ** 31 - 1) is True
+    ret[rank] = bool(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_readiness_flag_protocol_gloo():
+    import time
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29400 + os.getpid() % 150
+    ctx = mp.spawn(_flag_worker, args=(world, port, ret), nprocs=world, join=False)
+    deadline = time.time() + 120
+    while not ctx.join(timeout=2):
+        assert time.time() < deadline, "ranks did not finish"
+    assert dict(ret) == {0: True, 1: True}
