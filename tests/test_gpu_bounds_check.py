@@ -51,3 +51,37 @@ def test_ragged_cases_under_the_index_checking_build():
     sys.stdout.write(res.stdout[-2000:])
     sys.stderr.write(res.stderr[-4000:])
     assert res.returncode == 0 and "BOUNDS_OK" in res.stdout
+
+
+@pytest.mark.parametrize("T,route_kernel", [(129, 2), (1100, 1), (5000, 1)])
+def test_canaries_around_the_callers_buffers_stay_intact(T, route_kernel):
+    """The caller's x, residual and y sit inside larger allocations whose guard zones carry a bit pattern: the forward
+    must read nothing it depends on from them (the result is unchanged when the pattern changes) and write nothing
+    into them (the pattern is intact afterwards). Product build."""
+    import numpy as np
+    import torch
+    from prichs_b200 import MoELayer, synth
+    d, f, E, k, G = 256, 128, 8, 2, 4096  # G guard elements on each side
+    ws = synth.layer_weights(600 + T, d, f, E, std=0.05, bf16=True)
+    x = synth.round_bf16(synth.normal(601 + T, 0, (T, d)))
+    r = synth.round_bf16(synth.normal(602 + T, 0, (T, d)))
+    m = MoELayer.from_weights(ws, k, route_kernel=route_kernel)
+    outs = []
+    for pattern in (0x7FC1, 0x4242):  # a NaN pattern, then an ordinary number
+        bufs = []
+        for src in (x, r, None):
+            big = torch.full((T * d + 2 * G,), 0, dtype=torch.int16, device="cuda")
+            big[:] = pattern if pattern < 0x8000 else pattern - 0x10000
+            view = big[G:G + T * d].view(torch.bfloat16).view(T, d)
+            if src is not None:
+                view.copy_(torch.from_numpy(src).cuda().bfloat16())
+            bufs.append((big, view))
+        (bx, vx), (br, vr), (by, vy) = bufs
+        m.forward_with_memory(vx, None, residual=vr, out=vy)
+        m.sync_status()
+        for big, _ in bufs:
+            guard = torch.cat([big[:G], big[G + T * d:]]).cpu().numpy().astype(np.uint16)
+            assert (guard == pattern).all(), "a guard zone was written"
+        outs.append(vy.float().cpu().numpy())
+    assert np.array_equal(outs[0], outs[1]), "the result depends on memory outside the caller's buffers"
+    assert np.isfinite(outs[0]).all()
