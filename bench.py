@@ -622,7 +622,7 @@ def main():
                     "bound": "tensor", "achieved": gu_tf, "peak": peaks["tf"], "unit": "TFLOP/s", "frac": gu_tf / peaks["tf"],
                     # dram__bytes_read + dram__bytes_write of one launch at this size, from the one-pass ncu capture
                     # summarised in profiles/traffic_config1_full_size.md (bytes); only valid for config 1
-                    "traffic": 330.4e6 if not args.tokens else None,
+                    "traffic": 328.0e6 if not args.tokens else None,
                     "peak_source": f"{peaks['source']} bf16_tflops (burst; the timed region lasts well under a second)",
                     "frac_of_sustained_peak": gu_tf / peaks["tf_sustained"] if peaks["tf_sustained"] else None,
                     "algorithmic_flops_per_launch": gu_flops}
