@@ -161,7 +161,8 @@ PRICHS_API int prichs_moe_get_expert_assignments(prichs_moe_t* h, int expert, in
  * (crates/prichs-cuda/src/engine.rs:1917-2239) and for forward_gemm(router) + the host top-k loop between them, to
  * be called in the order of crates/prichs-model/src/model.rs:1327-1408 (training) or :1124-1182 (forward_gpu_only):
  *   1. prichs_engine_moe_forward_shared  takes normed2 [seq_len,d] (host fp32 slice as in the reference, or a device
- *      pointer with on_device = 1) and enqueues the WHOLE layer as a training forward: router and top-2 on the device,
+ *      pointer with on_device = 1; the work then goes to the legacy default stream, where the reference's engine does
+ *      all of its work) and enqueues the WHOLE layer as a training forward: router and top-2 on the device,
  *      shared and routed experts as grouped GEMMs, combine. Optional outputs: the shared expert's stash vectors.
  *   2. prichs_engine_moe_routing         router_logits [seq_len,E], selected_experts [seq_len,k] (usize), gating
  *      weights [seq_len,k]: what the reference computes with an Sgemm round trip and top_k_gating_unbiased on the host.

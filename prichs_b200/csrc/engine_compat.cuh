@@ -123,7 +123,7 @@ extern "C" {
 // call enqueues the WHOLE layer (router and top-2 on the device, shared and routed experts as grouped GEMMs, combine)
 // as a training forward, so that every stash the later calls hand out exists. `normed2` is [seq_len, d] fp32 on the
 // host (the reference's slice) or, with on_device != 0, a device pointer of element type dtype -- then nothing
-// crosses PCIe. The four outputs (host, any may be null) are the shared expert's stash vectors.
+// crosses PCIe; the work is then enqueued on the legacy default stream, like all of the reference engine's work. The four outputs (host, any may be null) are the shared expert's stash vectors.
 int prichs_engine_moe_forward_shared(prichs_moe_t* h, const void* normed2, int on_device, int dtype, size_t seq_len, float* shared_gate,
                                      float* shared_up, float* shared_act, float* shared_out) {
     if (!h || !normed2) return fail(PRICHS_ERR_BAD_ARG, "null handle or input");
@@ -132,7 +132,10 @@ int prichs_engine_moe_forward_shared(prichs_moe_t* h, const void* normed2, int o
     int rc = host_path_setup(h);
     if (rc != PRICHS_OK) return rc;
     const int T = (int)seq_len;
-    cudaStream_t st = h->own_stream;
+    // Host input: the library's own stream, after its own upload. Device input: the legacy default stream, the one the
+    // reference's engine does all its work on (engine.rs passes a null stream everywhere), so the forward is ordered
+    // after whatever produced the rows there.
+    cudaStream_t st = on_device ? nullptr : h->own_stream;
     const void* x_dev = normed2;
     int x_dtype = dtype;
     if (!on_device) {

@@ -1212,7 +1212,7 @@ __global__ void ep_wait_kernel(const int* __restrict__ flags, int kind, int wave
         for (;;) {
             int v;
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
-            if (v - seq >= 0) break;  // wrap-safe comparison of sequence numbers
+            if ((int)((unsigned)v - (unsigned)seq) >= 0) break;  // wrap-safe comparison of sequence numbers
             if (clock64() - t0 > budget_cycles) {
                 atomicExch(status, -5);
                 break;
