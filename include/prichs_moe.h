@@ -192,7 +192,9 @@ PRICHS_API int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, 
  * is used (f32 row-major slices, tensor.rs:14-29): copies x (and resid) to the device, runs the forward,
  * copies y back and waits for it. Pinned host memory makes the copies asynchronous; pageable memory works.
  * Batches of 4096 tokens or more are fed through in chunks on three streams (upload, kernels, download
- * overlap); the results, the routing stash and the counts are identical to one pass. */
+ * overlap); the results, the routing stash and the counts are identical to one pass. An expert-parallel handle cuts
+ * every rank's batch into max_tokens / 8192 (at most 8) chunks, each a collective forward: every rank runs the same
+ * number of chunks whatever its own T, which must be at least 16 tokens per chunk. */
 PRICHS_API int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* resid_host,
                             const float* concept_bias, int n_concept, float* y_host, int T);
 
