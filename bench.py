@@ -419,7 +419,7 @@ def main():
     ap.add_argument("--ep-reserve-sms", type=int, default=0, help="SMs the expert-parallel GEMM launches leave free (0 = default, -1 = none)")
     ap.add_argument("--route-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="single GPU: 0 = library default, 1 = single-pass routing kernel, 2 = router / scan / dispatch launches")
-    ap.add_argument("--gemm-kernel", type=int, default=0, choices=[0, 1], help="0 = CTA-pair kernel, 1 = one-CTA kernel")
+    ap.add_argument("--gemm-kernel", type=int, default=0, choices=[0, 1, 2], help="0 = CTA-pair kernel (small batches: one-CTA kernel), 1 = one-CTA kernel, 2 = as 0 with 128-column down tiles for small batches")
     ap.add_argument("--pdl", type=int, default=0, choices=[0, 1, 2], help="programmatic dependent launch: 0/1 = on (default), 2 = off")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -74,7 +74,10 @@ typedef struct prichs_moe_config {
     int scan_placement;   /* three-launch path: 0 = prefix sums at the router's tail under 1024 tokens, else a
                              launch of their own; 1 = always at the tail; 2 = always their own launch          */
     int separate_prenorm; /* block entry point: 1 = the RMSNorm runs as its own launch (0: folded into the router)  */
-    int gemm_kernel;      /* 0 = CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles), 1 = one-CTA kernel          */
+    int gemm_kernel;      /* 0 = CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles; batches under 1024 tokens run
+                             on the one-CTA kernel), 1 = one-CTA kernel for every batch size, 2 = as 0 with the down
+                             projection of small batches on 128-column tiles (faster for one stream of dependent
+                             layers, slower when several layers overlap)                                           */
     int pdl;              /* programmatic dependent launch between the kernels of a single-GPU forward (a kernel's
                              set-up overlaps the tail of its predecessor): 0 / 1 = on, 2 = off                     */
     int host_chunk_tokens;/* host-buffer entry point: tokens per pipelined chunk (0 = choose from T)                */

@@ -42,7 +42,7 @@
 namespace egemm {
 
 constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BN = 256;  // default tile width (the kernels' template parameter of the same name shadows it)
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
@@ -116,11 +116,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int EPI>
+// BN: output columns of a tile. 256 everywhere but for the plain epilogue on small batches, where 128-column tiles
+// (tiled B only: a tile then loads one 128-row half of a 256 x 64 weight block, a contiguous 16 KB run) double the number
+// of tiles, so that a decode step's down projection (54 tiles of 256 columns for nine experts) spreads over the SMs.
+template <int BN>
+struct GemmShape {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
+};
+
+template <int EPI, int BN = 256>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid_constant__ CUtensorMap tm_a_routed,
                    const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_out,
                    const Args args) {
+    static_assert(BN == 256 || (BN == 128 && EPI == EPI_PLAIN), "128-column tiles exist for the plain epilogue only");
+    constexpr int STAGES = GemmShape<BN>::STAGES;
+    constexpr int STAGE_BYTES = GemmShape<BN>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle atoms.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -184,7 +198,9 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                 const int a_row = (is_shared ? mt : args.a_routed_tile_off + rt) * BM;
                 const int slot = is_shared ? 0 : 1 + args.mtile_slot[mt - args.shared_mtiles];
                 const int b_row = slot * args.w_rows + nt * BN;
-                const int b_blk0 = (slot * (args.w_rows / BN) + nt) * args.b_nkt;  // first box of this n-tile (tiled B)
+                // tiled B: first 256 x 64 block of this n-tile's K run, and the tile's row offset inside such a block
+                const int b_blk0 = (slot * (args.w_rows / 256) + (nt * BN) / 256) * args.b_nkt;
+                const int b_half = (nt * BN) % 256;
                 for (int pass = 0; ok && pass < npass; ++pass) {
                     // pass 0: hi.hi, pass 1: lo.hi, pass 2: hi.lo
                     const int a_col0 = (pass == 1) ? k_elems : 0;
@@ -199,7 +215,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_a_shared, const __grid
                         ptx::mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
                         ptx::tma_load_2d(sa, tm_a, a_col0 + kb * BK, a_row, &full_bar[stage]);
                         if (args.b_nkt > 0)
-                            ptx::tma_load_2d(sb, &tm_b, 0, (b_blk0 + b_col0 / BK + kb) * BN, &full_bar[stage]);
+                            ptx::tma_load_2d(sb, &tm_b, 0, (b_blk0 + b_col0 / BK + kb) * 256 + b_half, &full_bar[stage]);
                         else
                             ptx::tma_load_2d(sb, &tm_b, b_col0 + kb * BK, b_row, &full_bar[stage]);
                         ++issued;

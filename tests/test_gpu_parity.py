@@ -593,3 +593,21 @@ def test_reference_ffi_kernels(torch_cuda):
     L.launch_swiglu_forward(a.data_ptr(), b.data_ptr(), o.data_ptr(), 0, st)  # zero size returns at once
     torch.cuda.synchronize()
     assert torch.allclose(o, torch.nn.functional.silu(a) * b, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("T", [64, 333, 1000])
+def test_gemm_kernel_variants_are_bit_identical(torch_cuda, T):
+    """gemm_kernel = 1 (one-CTA kernel for every batch size) and 2 (128-column tiles for the down projection of small
+    batches) accumulate every output element over K in the same order as the default: the outputs are bit-identical."""
+    import torch
+    from prichs_b200 import MoELayer, synth
+    d, f, E, k = 512, 256, 8, 2
+    ws = synth.layer_weights(97, d, f, E, std=0.05, bf16=True)
+    x = synth.round_bf16(synth.normal(98, 0, (T, d)))
+    outs = []
+    for gk in (0, 1, 2):
+        m = MoELayer.from_weights(ws, k, max_tokens=2048, gemm_kernel=gk)
+        m.router_bias = synth.router_bias(97, E, -0.1, 0.1)
+        outs.append(_to_host(m.forward(_to_dev(torch, x, "bf16"))))
+        m.sync_status()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
