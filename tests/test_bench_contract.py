@@ -51,3 +51,55 @@ def test_roofline_sum_arithmetic():
     comm = 2 * T * 2 * 1536 * 2 * 7 / 8 / 900e9 * 1e3
     assert abs(r8["comm_ms"] - comm) < 1e-9
     assert abs(r8["ms_overlapped"] - max(gemm + hbm, comm)) < 1e-9
+
+
+def test_parity_check_of_the_bench_line_detects_a_wrong_result(oracle):
+    """`parity` of the bench line is computed by bench.parity_check from the layer's own forward. With a stand-in layer
+    that returns the oracle's result the check passes; with a wrong selection, a wrong count or a wrong output row it
+    reports it (bench.py then exits non-zero). No GPU is involved."""
+    import importlib.util
+    import numpy as np
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    from prichs_b200 import synth
+    from prichs_b200.moe import MoEStash
+    spec = importlib.util.spec_from_file_location("bench_mod2", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    D, F, E, K = bench.D, bench.F, bench.E, bench.K
+    T = 48
+    ws = synth.layer_weights(11, D, F, E, bf16=True)
+    bias = synth.router_bias(11, E, -0.1, 0.1)
+    x = synth.tokens(11, T, D, bf16=True)
+    ref = oracle.moe_forward_train(ws, bias, K, x)
+
+    class StandIn:
+        def __init__(self, out, sel, counts):
+            self.out, self.sel, self.counts = out, sel, counts
+
+        def forward(self, _x):
+            return torch.from_numpy(self.out)
+
+        def sync_status(self):
+            pass
+
+        def last_stash(self):
+            return MoEStash(ref["logits"], self.sel.reshape(-1), ref["gating"].reshape(-1), self.counts)
+
+    def run(out, sel, counts):
+        p = bench.parity_check(StandIn(out, sel, counts), ws, bias, x, None, 32, 5)
+        p["ok"] = bool(p["routing_bit_exact"] and p["max_rel"] <= 2e-2 and p["logits_max_abs_err"] <= 1e-3)
+        return p
+
+    good = run(ref["out"], ref["selected"], ref["counts"])
+    assert good["ok"] and good["routing_bit_exact"] and good["max_rel"] == 0.0 and good["tokens_checked"] == 32
+    swapped = ref["selected"].copy()
+    swapped[3] = swapped[3][::-1]
+    assert not run(ref["out"], swapped, ref["counts"])["routing_bit_exact"]
+    wrong_counts = ref["counts"].copy()
+    wrong_counts[0] += 1
+    assert not run(ref["out"], ref["selected"], wrong_counts)["routing_bit_exact"]
+    bad = ref["out"] * np.float32(1.1)
+    r = run(bad, ref["selected"], ref["counts"])
+    assert r["routing_bit_exact"] and not r["ok"] and r["max_rel"] > 2e-2
