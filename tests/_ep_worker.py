@@ -29,6 +29,7 @@ def main():
              (512, 384, 8, 2, 2500, None, 2, True),
              (512, 384, 8, 2, 40, (-0.1, 0.1), 4, False),       # fewer tokens than waves x 16: some waves are empty
              (512, 384, 8, 2, 700, (-0.1, 0.1), 2, "f32"),      # fp32-fidelity mode across ranks
+             (512, 384, world, 2, 1800, (-0.1, 0.1), 3, False),   # one expert per rank, whatever the group size
              # the multi-GPU configurations of the baseline at their real size: T = 32768 tokens per GPU, production
              # dimensions, default waves; uniform routing and the Zipf(1.2)-skewed router. Routing is checked on every
              # token, outputs on a seeded sample of 1024 tokens per rank.
@@ -76,12 +77,12 @@ def main():
         hp = ep.plan(cmat, rank)
         meta = m.debug_buffer(5, 4 * 100).view(np.int32)
         if waves == 1:  # with several waves every wave has a plan of its own; the summary keeps the sums
-            assert np.array_equal(meta[8:16], hp["seg_base"]), (meta[8:16], hp["seg_base"])
-            assert np.array_equal(meta[16:24], hp["src_off"])
+            assert np.array_equal(meta[8:8 + E], hp["seg_base"]), (meta[8:16], hp["seg_base"])
+            assert np.array_equal(meta[16:16 + E], hp["src_off"])
             assert meta[32] == hp["n_mtiles"]
-        assert np.array_equal(meta[24:32], hp["total"])
+        assert np.array_equal(meta[24:24 + E], hp["total"])
         assert meta[33] == hp["recv_rows"] and meta[34] == 0
-        assert np.array_equal(meta[36:36 + 8 * world].reshape(world, 8), cmat)
+        assert np.array_equal(meta[36:36 + 8 * world].reshape(world, 8)[:, :E], cmat)
         # outputs against the oracle of the whole layer on this rank's tokens
         mask = None
         if big:

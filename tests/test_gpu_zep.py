@@ -21,4 +21,4 @@ def test_expert_parallel_parity():
     sys.stdout.write(res.stdout[-4000:])
     sys.stderr.write(res.stderr[-4000:])
     assert res.returncode == 0
-    assert res.stdout.count("EP_OK") == 11 * world
+    assert res.stdout.count("EP_OK") == 12 * world
