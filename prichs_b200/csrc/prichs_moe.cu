@@ -1327,6 +1327,8 @@ int prichs_moe_block_forward(prichs_moe_t* h, const void* x_res_dev, int x_dtype
 }  // extern "C"
 
 namespace {
+int ep_query_stream(void* ctx);   // watchdog callbacks, defined next to prichs_moe_sync_status
+void ep_abort_comms(void* ctx);
 constexpr int HOST_MAX_CHUNKS = 64;
 // Staging buffers, streams and events of the entry points that take host buffers; every resource is created only
 // if it is still missing, so a call that failed half way can be repeated.
@@ -1441,6 +1443,11 @@ int prichs_moe_forward_host(prichs_moe_t* h, const float* x_host, const float* r
     h->last_T = T;
     h->last_stream = st;
     h->last_chunked = nchunks > 1;
+    if (rc == PRICHS_OK && h->world > 1) {
+        // the forwards hold collectives: wait for them under the watchdog, not for ever (see prichs_moe_sync_status)
+        const int wrc = prichs_ep_wait_or_abort(ep_query_stream, ep_abort_comms, h, h->ep_timeout_ms, 50);
+        if (wrc != PRICHS_OK) return wrc;
+    }
     cudaError_t e1 = cudaStreamSynchronize(h->in_stream), e2 = cudaStreamSynchronize(st), e3 = cudaStreamSynchronize(h->out_stream);
     if (rc != PRICHS_OK) return rc;
     if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
