@@ -352,7 +352,9 @@ PRICHS_API int prichs_moe_debug_copy(prichs_moe_t* h, int which, size_t offset_b
  * and the forward reports PRICHS_ERR_TIMEOUT through prichs_moe_sync_status (-1 = none, the default). key 1: budget
  * of that kernel's bounded waits, and of the expert-parallel readiness waits, in clock cycles (default 4e9, about two
  * seconds). key 2: 1 + kind * 4 + wave of a readiness signal this rank does not send in the following expert-parallel
- * forwards (kind 0 rows landed, 1 outputs ready; 0 = none), so that the other ranks' bounded wait for it runs out. */
+ * forwards (kind 0 rows landed, 1 outputs ready; 0 = none), so that the other ranks' bounded wait for it runs out.
+ * key 3: nanoseconds a warp of the single-pass routing kernel pauses before it looks again at tiles that have not
+ * published their counts yet (default 100; 0 = poll back to back). */
 PRICHS_API int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value);
 
 /* ---- routing without any allocation ---------------------------------------------------------------

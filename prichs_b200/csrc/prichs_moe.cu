@@ -327,6 +327,7 @@ struct prichs_moe {
     int* rd_ctl;          // single-pass kernel: ticket and exit counters, zero between launches
     long long rd_wait_cycles;  // budget of the single-pass kernel's bounded waits
     int rd_stall_tile;    // test knob (prichs_moe_debug_set): the tile that never publishes its counts, -1 none
+    int rd_poll_sleep_ns; // pause between two polls of a look-back window
     void* ybuf;
     size_t y_bytes;  // bytes of the expert outputs inside the allocation (the flags follow)
     float *logits, *gates;
@@ -816,6 +817,7 @@ int prichs_moe_create(const prichs_moe_config_t* cfg, prichs_moe_t** out_handle)
     h->router_ctas_per_sm = cfg->router_ctas_per_sm == 0 ? -1 : std::max(0, cfg->router_ctas_per_sm);
     h->host_chunk = cfg->host_chunk_tokens > 0 ? std::max(256, cfg->host_chunk_tokens / 16 * 16) : 0;
     h->rd_stall_tile = -1;
+    h->rd_poll_sleep_ns = 100;  // measured on B200: 46.2 against 47.2 us for the routing stage at 16384 tokens without the pause
     h->rd_wait_cycles = 4000000000LL;  // ~2 s, like the GEMM's waits
     h->n_waves = 1;
     if (world > 1) {
@@ -1188,6 +1190,7 @@ int prichs_moe_forward(prichs_moe_t* h, const void* x_dev, int x_dtype, const vo
         ra.status = h->status;
         ra.wait_cycles = h->rd_wait_cycles;
         ra.stall_tile = h->rd_stall_tile;
+        ra.poll_sleep_ns = h->rd_poll_sleep_ns;
         const int grid = std::min(ntiles, h->sm_count);
         if (h->rt_nsplit == 1)
             LAUNCH_K(pdl, route::route_dispatch_kernel<1>, grid, route::RD_THREADS, route::rd_smem_bytes(h->d, 1, rd_stages), st, ra, cb);
@@ -2036,6 +2039,7 @@ int prichs_moe_debug_set(prichs_moe_t* h, int key, long long value) {
             h->rd_wait_cycles = value;
             return PRICHS_OK;
         case 2: h->ep_skip_signal = (int)value; return PRICHS_OK;
+        case 3: h->rd_poll_sleep_ns = (int)std::max<long long>(0, std::min<long long>(value, 10000)); return PRICHS_OK;
         default: return fail(PRICHS_ERR_BAD_ARG, "unknown debug key %d", key);
     }
 }

@@ -451,6 +451,7 @@ struct RouteDispatchArgs {
     int* status;
     long long wait_cycles;
     int stall_tile;  // test knob: this tile never publishes its counts, so its successors' look-back runs out (-1: none)
+    int poll_sleep_ns;  // pause between two looks at a window whose tiles have not all published yet
 };
 
 __device__ __forceinline__ uint4 ld_relaxed_16(const void* p) {
@@ -704,6 +705,7 @@ route_dispatch_kernel(const __grid_constant__ RouteDispatchArgs a, const Concept
                             ok = false;
                             break;
                         }
+                        if (a.poll_sleep_ns > 0) __nanosleep(a.poll_sleep_ns);
                         continue;
                     }
 #pragma unroll
