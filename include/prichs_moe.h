@@ -255,7 +255,10 @@ PRICHS_API int prichs_moe_block_backward(prichs_moe_t* h, const void* x_res_dev,
 
 /* MoELayer::update_aux_free_bias(expert_token_counts, total_tokens, gamma) (moe.rs:228-245) with host
  * counts, as the reference's call sites pass them (model.rs:786-792,1541-1548):
- *   b_i += gamma * (top_k/E - counts[i]/total_tokens);   no-op when total_tokens == 0. */
+ *   b_i += gamma * (top_k/E - counts[i]/total_tokens);   no-op when total_tokens == 0.
+ * The counts travel as kernel arguments: no allocation, no copy, no device-wide synchronisation. The one-warp kernel is
+ * enqueued on the stream of the handle's last forward (after the router that read the bias, before the next forward
+ * there); prichs_moe_get_bias waits for it. */
 PRICHS_API int prichs_moe_update_aux_free_bias(prichs_moe_t* h, const size_t* expert_token_counts, int n,
                                     size_t total_tokens, float gamma);
 
