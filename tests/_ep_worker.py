@@ -19,6 +19,7 @@ def main():
     from _util import assert_close
 
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    O.set_num_threads(max(1, (os.cpu_count() or 8) // world))  # the ranks share the host's cores for the oracle
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     # (d, f, E, k, T, bias range, waves): the last two cases cut the batch into token waves
